@@ -1,0 +1,202 @@
+/*
+ * sdq -- C ABI of the B200 (sm_100a) int8 quantized-linear path.
+ *
+ * This is the boundary a host program binds to replace the CPU implementation
+ * of the int8 linear in JasonHonKL/Self-evolve-diffusion-cpp: dynamic per-row
+ * int8 activation quantization + s8 x s8 -> s32 GEMM + fp32 rescale
+ * (sd::qgemm), the two weight quantizers, and the .sdcpp pack reader/writer.
+ * Plain pointers and sizes only; every function returns an sdq_status and the
+ * text of the last failure on the calling thread is in sdq_last_error().
+ *
+ * One process drives one GPU: call sdq_init(device) first.  There is no CPU
+ * fallback: without a usable sm_100 device every compute entry point fails
+ * with SDQ_ERR_CUDA / SDQ_ERR_NOT_INIT.
+ *
+ * Each declaration cites the reference interface it replaces (file:line in
+ * the reference project).
+ */
+#ifndef SDQ_H
+#define SDQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SDQ_VERSION 1
+
+#if defined(__GNUC__)
+#define SDQ_API __attribute__((visibility("default")))
+#else
+#define SDQ_API
+#endif
+
+typedef enum sdq_status {
+  SDQ_OK = 0,
+  SDQ_ERR_INVALID = 1,        /* bad argument (null pointer, negative size, wrong handle) */
+  SDQ_ERR_CUDA = 2,           /* a CUDA runtime/driver call failed */
+  SDQ_ERR_NOT_INIT = 3,       /* sdq_init has not succeeded in this process */
+  SDQ_ERR_IO = 4,             /* file cannot be opened / read / written / mapped */
+  SDQ_ERR_FORMAT = 5,         /* malformed .sdcpp or .safetensors content */
+  SDQ_ERR_DEVICE_TIMEOUT = 6, /* a bounded wait inside a kernel gave up; output is invalid */
+  SDQ_ERR_NOT_FOUND = 7,
+  SDQ_ERR_NOMEM = 8
+} sdq_status;
+
+/* Opaque handle of an int8 weight matrix [N,K] + fp32 scales [N] resident in HBM. 0 = none. */
+typedef uint64_t sdq_weight_t;
+
+/* ---- flags of the compute entry points ---- */
+#define SDQ_A_HOST 0x1u      /* A is host memory: it is copied to the device inside the call */
+#define SDQ_OUT_HOST 0x2u    /* out is host memory: the result is copied back inside the call */
+#define SDQ_GELU_TANH 0x4u   /* apply GELU (tanh form) after the bias in the epilogue */
+#define SDQ_FORCE_SIMT 0x8u  /* use the portable CUDA-core kernel instead of tcgen05 */
+#define SDQ_SYNC 0x10u       /* wait for the stream before returning */
+
+/* source element types of sdq_quantize_rows (the packer's SRC table,
+ * tools/quantize/pack_sdcpp.py:26-35) */
+#define SDQ_F32 0
+#define SDQ_BF16 1
+#define SDQ_F16 2
+
+/* rounding recipe of sdq_quantize_rows */
+#define SDQ_MODE_PACKER 0  /* quant_rows, tools/quantize/pack_sdcpp.py:45-51 */
+#define SDQ_MODE_ROWWISE 1 /* sd::quantize_rowwise, src/core/tensor.cpp:63-78 */
+
+#define SDQ_SRC_HOST 0x1u /* sdq_quantize_rows / sdq_dequant_rows: src is host memory */
+#define SDQ_DST_HOST 0x2u /* ... q/scale (or w) are host memory */
+
+/* ---- process / device ---- */
+
+/* Binds this process to CUDA device `device` and creates the context state
+ * (replaces nothing in the reference: it has no device).  Idempotent for the
+ * same device. */
+SDQ_API int sdq_init(int device);
+SDQ_API int sdq_shutdown(void);
+SDQ_API int sdq_device(void); /* -1 before sdq_init */
+SDQ_API int sdq_version(void);
+SDQ_API const char* sdq_last_error(void);
+/* Number of kernels this library has launched since sdq_init (monotonic). */
+SDQ_API int64_t sdq_launch_count(void);
+
+/* Device / pinned-host memory and copies for callers that do not link the CUDA
+ * runtime themselves.  `stream` is a cudaStream_t (NULL = default stream). */
+SDQ_API int sdq_malloc(void** dptr, size_t bytes);
+SDQ_API int sdq_free(void* dptr);
+SDQ_API int sdq_malloc_host(void** hptr, size_t bytes);
+SDQ_API int sdq_free_host(void* hptr);
+SDQ_API int sdq_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+SDQ_API int sdq_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+SDQ_API int sdq_memset(void* dst, int value, size_t bytes, void* stream);
+SDQ_API int sdq_stream_sync(void* stream);
+
+/* ---- weights ---- */
+
+/* Copies one packed weight -- int8 [N,K] row-major (torch Linear [out,in], the
+ * layout sd::qgemm takes as Bq, src/core/tensor.h:48-52) and its N fp32 scales
+ * -- into 256-byte-aligned device memory, once, and remembers the host address
+ * so that sdq_weight_lookup(q_host) finds it again.  The host pointers may have
+ * any alignment (the .sdcpp blob has no padding, src/serde/sdcpp.cpp:107-124). */
+SDQ_API int sdq_weight_upload(const int8_t* q_host, const float* scale_host, int64_t N, int64_t K,
+                      sdq_weight_t* out);
+/* Wraps device-resident int8 weights without copying (caller keeps them alive). */
+SDQ_API int sdq_weight_wrap_device(const int8_t* q_dev, const float* scale_dev, int64_t N, int64_t K,
+                           sdq_weight_t* out);
+/* Finds the weight uploaded from host address `q_host` (the key the reference's
+ * caller has in hand: blk::Linear::w.data, src/model/ovi_dit.cpp:66-70). */
+SDQ_API int sdq_weight_lookup(const void* q_host, sdq_weight_t* out);
+SDQ_API int sdq_weight_info(sdq_weight_t w, int64_t* N, int64_t* K, const int8_t** q_dev,
+                    const float** scale_dev);
+SDQ_API int sdq_weight_release(sdq_weight_t w);
+
+/* ---- the hot path ---- */
+
+/* out[M,N] = qgemm(A[M,K], W)  -- replaces sd::qgemm (src/core/tensor.h:52,
+ * src/core/qgemm.cpp:73-142): per-row absmax int8 quantization of the fp32
+ * activations, s8 x s8 -> s32 dot products against the weight rows, then
+ * out = (float)acc * (a_scale[i] * w_scale[j]).  `bias` (fp32 [N], device
+ * memory, may be NULL) fuses the y[i,j] += b[j] pass the reference's caller
+ * runs afterwards (src/model/ovi_dit.cpp:71-79); SDQ_GELU_TANH fuses the
+ * activation between the two FFN linears (src/model/ovi_dit.cpp:132-142,
+ * 214-222).  A and out are device memory unless SDQ_A_HOST / SDQ_OUT_HOST.
+ * M == 0 is a no-op (src/core/qgemm.cpp:76); a weight always has N >= 1 and K >= 1. */
+SDQ_API int sdq_qgemm(sdq_weight_t w, const float* A, int64_t M, float* out, const float* bias,
+              uint32_t flags, void* stream);
+
+/* First half of sd::qgemm alone (src/core/qgemm.cpp:82-96): aq int8 [M,K] and
+ * a_scale fp32 [M], all device memory. */
+SDQ_API int sdq_quantize_activations(const float* A_dev, int64_t M, int64_t K, int8_t* aq_dev,
+                             float* a_scale_dev, void* stream);
+
+/* Second half of sd::qgemm (src/core/qgemm.cpp:98-138) on activations that are
+ * already quantized: lets a caller quantize x once and run the q, k and v
+ * projections on it (the reference re-quantizes x three times,
+ * src/model/ovi_dit.cpp:176-188).  `acc_dump_dev` (int32 [M,N], may be NULL)
+ * also receives the raw s32 accumulators. */
+SDQ_API int sdq_qgemm_prequantized(sdq_weight_t w, const int8_t* aq_dev, const float* a_scale_dev,
+                           int64_t M, float* out_dev, const float* bias_dev,
+                           int32_t* acc_dump_dev, uint32_t flags, void* stream);
+
+/* ---- weight quantizers ---- */
+
+/* Quantizes `rows` rows of `last` elements to int8 with one fp32 scale per row.
+ * SDQ_MODE_PACKER is byte-identical to quant_rows of the .sdcpp packer
+ * (tools/quantize/pack_sdcpp.py:38-51: x*(127/amax), round half even, clip,
+ * scale amax/127 and 0 for an all-zero row); SDQ_MODE_ROWWISE to
+ * sd::quantize_rowwise (src/core/tensor.h:55, src/core/tensor.cpp:63-78:
+ * x/(amax/127), round half away, scale 1 for an all-zero row; fp32 source only). */
+SDQ_API int sdq_quantize_rows(const void* src, int src_dtype, int64_t rows, int64_t last, int mode,
+                      int8_t* q, float* scale, uint32_t flags, void* stream);
+
+/* w[r,c] = q[r,c] * scale[r] -- replaces dequant_pack (src/model/ovi_dit.cpp:53-63). */
+SDQ_API int sdq_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last, float* w,
+                     uint32_t flags, void* stream);
+
+/* ---- .sdcpp packs ---- */
+
+/* Offline packer -- replaces tools/quantize/pack_sdcpp.py main() (lines 54-124):
+ * reads a .safetensors file, quantizes every float tensor with numel >= 65536
+ * that is not excluded (row = last dim) on the GPU, keeps the rest as raw fp32,
+ * and writes a .sdcpp v1 file that is byte-identical to the python packer's.
+ * `only`: comma-separated name prefixes ("" = all); `dtype_preserve`:
+ * colon-separated source dtypes kept raw ("" = none). */
+SDQ_API int sdq_pack_sdcpp(const char* safetensors_in, const char* sdcpp_out, const char* only,
+                   const char* dtype_preserve);
+
+typedef struct sdq_pack sdq_pack; /* an open .sdcpp file */
+
+#define SDQ_DT_F32 0 /* codes of sdq_entry.dtype: sd::DType values (src/core/tensor.h:13) */
+#define SDQ_DT_I8 2
+
+typedef struct sdq_entry {
+  const char* name;    /* NUL-terminated, owned by the pack */
+  int32_t dtype;       /* SDQ_DT_I8 or SDQ_DT_F32 */
+  int32_t ndim;
+  int64_t dims[8];
+  const void* data;    /* view into the file mapping (host) */
+  uint64_t nbytes;
+  uint64_t file_offset; /* of `data` from the start of the file */
+  sdq_weight_t weight; /* device copy of an I8 entry when the pack was opened with
+                          SDQ_PACK_UPLOAD, viewed as [numel/last, last]; else 0 */
+} sdq_entry;
+
+#define SDQ_PACK_UPLOAD 0x1u /* upload every I8 entry (+ scales) to the device at open */
+
+/* Opens and validates a .sdcpp v1 file -- replaces sd::load_sdcpp
+ * (src/serde/sdcpp.h:18-19, src/serde/sdcpp.cpp:47-133).  Entries appear as the
+ * reference's map does: a quantized tensor as `name` (I8, original shape) plus
+ * `name.scale` (F32 [rows]), a raw tensor as `name` (F32).  Failures carry the
+ * reference's messages ("sdcpp: bad magic", "sdcpp: truncated file", ...). */
+SDQ_API int sdq_pack_open(const char* path, uint32_t flags, sdq_pack** out);
+SDQ_API int64_t sdq_pack_count(const sdq_pack* p);
+SDQ_API int sdq_pack_entry(const sdq_pack* p, int64_t index, sdq_entry* out);
+SDQ_API int sdq_pack_find(const sdq_pack* p, const char* name, sdq_entry* out);
+/* Unmaps the file and releases the device copies made at open. */
+SDQ_API int sdq_pack_close(sdq_pack* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SDQ_H */

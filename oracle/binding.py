@@ -1,0 +1,202 @@
+"""ctypes/numpy bindings for the CPU oracle -- TEST INFRASTRUCTURE ONLY.
+
+`oracle` is the plain-C restatement (liboracle.so, built from qgemm_oracle.c);
+`ref` is the reference's own code compiled from its sources (_ref/libsdref.so),
+present wherever it was built or carried along.  Nothing under the product
+package imports this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_ORACLE_SO = os.path.join(HERE, "liboracle.so")
+_REF_SO = os.path.join(HERE, "_ref", "libsdref.so")
+
+i64, f32p, i8p, i32p, u16p = C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p
+
+
+def build(quiet=True):
+    """Compile liboracle.so (and _ref/libsdref.so where the reference tree is mounted)."""
+    out = subprocess.run(["make", "-C", HERE], capture_output=True, text=True)
+    if out.returncode != 0:
+        raise RuntimeError("oracle build failed:\n" + out.stdout + out.stderr)
+    if not quiet:
+        print(out.stdout)
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    a = np.ascontiguousarray(a, dtype=dt)
+    return a
+
+
+class Oracle:
+    def __init__(self):
+        if not os.path.exists(_ORACLE_SO):
+            build()
+        L = self.lib = C.CDLL(_ORACLE_SO)
+        L.orc_threads.restype = C.c_int
+        for name in ("orc_act_quant_rows", "orc_dot_s32", "orc_rescale", "orc_qgemm",
+                     "orc_bias_add", "orc_gelu_tanh", "orc_quantize_rowwise",
+                     "orc_quant_rows_packer", "orc_dequant_rows", "orc_f32_to_bf16",
+                     "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads"):
+            getattr(L, name).restype = None
+
+    def threads(self):
+        return int(self.lib.orc_threads())
+
+    def set_threads(self, n):
+        self.lib.orc_set_threads(C.c_int(n))
+
+    def act_quant_rows(self, A):
+        A = _c(A, np.float32)
+        M, K = A.shape
+        aq = np.empty((M, K), np.int8)
+        sc = np.empty((M,), np.float32)
+        self.lib.orc_act_quant_rows(_ptr(A), i64(M), i64(K), _ptr(aq), _ptr(sc))
+        return aq, sc
+
+    def dot_s32(self, aq, bq):
+        aq, bq = _c(aq, np.int8), _c(bq, np.int8)
+        M, K = aq.shape
+        N = bq.shape[0]
+        acc = np.empty((M, N), np.int32)
+        self.lib.orc_dot_s32(_ptr(aq), _ptr(bq), i64(M), i64(N), i64(K), _ptr(acc))
+        return acc
+
+    def rescale(self, acc, a_scale, b_scale):
+        acc, a_scale, b_scale = _c(acc, np.int32), _c(a_scale, np.float32), _c(b_scale, np.float32)
+        M, N = acc.shape
+        out = np.empty((M, N), np.float32)
+        self.lib.orc_rescale(_ptr(acc), _ptr(a_scale), _ptr(b_scale), i64(M), i64(N), _ptr(out))
+        return out
+
+    def qgemm(self, A, Bq, bs):
+        A, Bq, bs = _c(A, np.float32), _c(Bq, np.int8), _c(bs, np.float32)
+        M, K = A.shape
+        N = Bq.shape[0]
+        out = np.zeros((M, N), np.float32)
+        self.lib.orc_qgemm(_ptr(A), _ptr(Bq), _ptr(bs), i64(M), i64(N), i64(K), _ptr(out))
+        return out
+
+    def bias_add(self, y, b):
+        y = np.array(y, dtype=np.float32, order="C", copy=True)
+        b = _c(b, np.float32)
+        self.lib.orc_bias_add(_ptr(y), _ptr(b), i64(y.shape[0]), i64(y.shape[1]))
+        return y
+
+    def gelu_tanh(self, x):
+        x = np.array(x, dtype=np.float32, order="C", copy=True)
+        self.lib.orc_gelu_tanh(_ptr(x), i64(x.size))
+        return x
+
+    def quantize_rowwise(self, W):
+        W = _c(W, np.float32)
+        N, K = W.shape
+        q = np.empty((N, K), np.int8)
+        s = np.empty((N,), np.float32)
+        self.lib.orc_quantize_rowwise(_ptr(W), i64(N), i64(K), _ptr(q), _ptr(s))
+        return q, s
+
+    def quant_rows_packer(self, x):
+        x = _c(x, np.float32)
+        rows, last = x.shape
+        q = np.empty((rows, last), np.int8)
+        s = np.empty((rows,), np.float32)
+        self.lib.orc_quant_rows_packer(_ptr(x), i64(rows), i64(last), _ptr(q), _ptr(s))
+        return q, s
+
+    def dequant_rows(self, q, scale):
+        q, scale = _c(q, np.int8), _c(scale, np.float32)
+        rows, last = q.shape
+        w = np.empty((rows, last), np.float32)
+        self.lib.orc_dequant_rows(_ptr(q), _ptr(scale), i64(rows), i64(last), _ptr(w))
+        return w
+
+    def f32_to_bf16(self, x):
+        x = _c(x, np.float32)
+        o = np.empty(x.shape, np.uint16)
+        self.lib.orc_f32_to_bf16(_ptr(x), _ptr(o), i64(x.size))
+        return o
+
+    def bf16_to_f32(self, b):
+        b = _c(b, np.uint16)
+        o = np.empty(b.shape, np.float32)
+        self.lib.orc_bf16_to_f32(_ptr(b), _ptr(o), i64(b.size))
+        return o
+
+    def f16_to_f32(self, h):
+        h = _c(h, np.uint16)
+        o = np.empty(h.shape, np.float32)
+        self.lib.orc_f16_to_f32(_ptr(h), _ptr(o), i64(h.size))
+        return o
+
+
+class Reference:
+    """The reference's own compiled code (sd::qgemm etc.) behind C wrappers."""
+
+    @staticmethod
+    def available():
+        return os.path.exists(_REF_SO)
+
+    def __init__(self):
+        if not os.path.exists(_REF_SO):
+            raise FileNotFoundError(_REF_SO)
+        L = self.lib = C.CDLL(_REF_SO)
+        L.sdref_nthreads.restype = C.c_int
+        L.sdref_set_nthreads.restype = None
+        L.sdref_qgemm.restype = C.c_int64
+        L.sdref_qgemm_time.restype = C.c_double
+        L.sdref_quantize_rowwise.restype = None
+        L.sdref_to_bf16.restype = None
+        L.sdref_load_sdcpp_listing.restype = C.c_int64
+
+    def nthreads(self):
+        return int(self.lib.sdref_nthreads())
+
+    def set_nthreads(self, n):
+        self.lib.sdref_set_nthreads(C.c_int(n))
+
+    def qgemm(self, A, Bq, bs):
+        A, Bq, bs = _c(A, np.float32), _c(Bq, np.int8), _c(bs, np.float32)
+        M, K = A.shape
+        N = Bq.shape[0]
+        out = np.zeros((M, N), np.float32)
+        self.lib.sdref_qgemm(_ptr(A), i64(M), i64(K), _ptr(Bq), i64(N), _ptr(bs), _ptr(out))
+        return out
+
+    def qgemm_time(self, A, Bq, bs, reps=1):
+        A, Bq, bs = _c(A, np.float32), _c(Bq, np.int8), _c(bs, np.float32)
+        M, K = A.shape
+        N = Bq.shape[0]
+        return float(self.lib.sdref_qgemm_time(_ptr(A), i64(M), i64(K), _ptr(Bq), i64(N),
+                                               _ptr(bs), C.c_int(reps)))
+
+    def quantize_rowwise(self, W):
+        W = _c(W, np.float32)
+        N, K = W.shape
+        q = np.empty((N, K), np.int8)
+        s = np.empty((N,), np.float32)
+        self.lib.sdref_quantize_rowwise(_ptr(W), i64(N), i64(K), _ptr(q), _ptr(s))
+        return q, s
+
+    def to_bf16(self, x):
+        x = _c(x, np.float32)
+        o = np.empty(x.shape, np.uint16)
+        self.lib.sdref_to_bf16(_ptr(x), _ptr(o), i64(x.size))
+        return o
+
+    def load_sdcpp_listing(self, path):
+        """(count, listing) or raises RuntimeError with the loader's message."""
+        buf = C.create_string_buffer(1 << 20)
+        n = self.lib.sdref_load_sdcpp_listing(path.encode(), buf, i64(len(buf)))
+        text = buf.value.decode()
+        if n < 0:
+            raise RuntimeError(text)
+        return int(n), text

@@ -1,0 +1,66 @@
+/*
+ * CPU oracle for the int8 quantized-linear path.  TEST INFRASTRUCTURE ONLY:
+ * the tests, the smoke check and the benchmark's CPU-baseline leg link this;
+ * the product library never does.
+ *
+ * Every function restates, in plain C, the arithmetic of one piece of the
+ * reference (JasonHonKL/Self-evolve-diffusion-cpp); the .c file cites the
+ * reference file:line each one follows.  Parity status: PINNED -- the
+ * restatement is checked bit-for-bit against the reference's own sd::qgemm /
+ * sd::quantize_rowwise compiled from source (oracle/_ref) and against
+ * tools/quantize/pack_sdcpp.py (fixtures under tests/golden/).
+ */
+#ifndef QGEMM_ORACLE_H
+#define QGEMM_ORACLE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* bf16 <-> f32 (src/core/tensor.cpp:39-47): RNE on the way down, <<16 up. */
+void orc_f32_to_bf16(const float* src, uint16_t* dst, int64_t n);
+void orc_bf16_to_f32(const uint16_t* src, float* dst, int64_t n);
+/* IEEE binary16 -> f32, the packer's np.float16 -> np.float32 cast. */
+void orc_f16_to_f32(const uint16_t* src, float* dst, int64_t n);
+
+/* Dynamic per-row activation quantization (src/core/qgemm.cpp:82-96). */
+void orc_act_quant_rows(const float* A, int64_t M, int64_t K, int8_t* aq, float* as);
+
+/* s8 x s8 -> s32 accumulators, acc[i*N+j] = sum_k aq[i,k]*bq[j,k]
+ * (src/core/qgemm.cpp:22-59; both M branches give the same sums). */
+void orc_dot_s32(const int8_t* aq, const int8_t* bq, int64_t M, int64_t N, int64_t K,
+                 int32_t* acc);
+
+/* out = (float)acc * (as[i] * bs[j])   (src/core/qgemm.cpp:123-124,135). */
+void orc_rescale(const int32_t* acc, const float* as, const float* bs, int64_t M, int64_t N,
+                 float* out);
+
+/* The whole sd::qgemm (src/core/qgemm.cpp:73-142). */
+void orc_qgemm(const float* A, const int8_t* Bq, const float* bs, int64_t M, int64_t N,
+               int64_t K, float* out);
+
+/* y[i,j] += b[j]  (src/model/ovi_dit.cpp:71-79). */
+void orc_bias_add(float* y, const float* b, int64_t M, int64_t N);
+
+/* GELU, tanh form, in place (src/model/ovi_dit.cpp:132-142). */
+void orc_gelu_tanh(float* x, int64_t n);
+
+/* C++ weight quantizer sd::quantize_rowwise (src/core/tensor.cpp:63-78). */
+void orc_quantize_rowwise(const float* W, int64_t N, int64_t K, int8_t* q, float* scale);
+
+/* .sdcpp packer's quantizer quant_rows (tools/quantize/pack_sdcpp.py:45-51). */
+void orc_quant_rows_packer(const float* x, int64_t rows, int64_t last, int8_t* q, float* scale);
+
+/* w = q * scale[row]  (src/model/ovi_dit.cpp:53-63). */
+void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last, float* w);
+
+/* Threads used by the loops above (OpenMP); <=0 restores the default. */
+void orc_set_threads(int n);
+int orc_threads(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

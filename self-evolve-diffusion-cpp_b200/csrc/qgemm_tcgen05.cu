@@ -1,0 +1,468 @@
+// int8 x int8 -> int32 GEMM on the Blackwell tensor cores (tcgen05, kind::i8)
+// with the fp32 rescale / bias / GELU epilogue of the quantized linear.
+//
+//   acc[i,j] = sum_k aq[i,k] * bq[j,k]          (reference src/core/qgemm.cpp:22-59)
+//   out[i,j] = (float)acc * (a_scale[i]*b_scale[j])   (src/core/qgemm.cpp:123-124,135)
+//
+// Both operands are K-major ("TN"): aq is [M,K] row-major, bq is the .sdcpp
+// weight [N,K] row-major as stored in the file -- no repack.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0, one lane : TMA producer.  Per k-block it loads a 128 x 128 B tile
+//                      of aq and a BLOCK_N x 128 B tile of bq (SWIZZLE_128B)
+//                      into a ring of shared-memory stages.
+//   warp 1, one lane : MMA issuer.  4 x tcgen05.mma (M=128, N=BLOCK_N, K=32)
+//                      per stage into one of two TMEM accumulator buffers;
+//                      tcgen05.commit releases the stage / publishes the tile.
+//   warps 2..5       : epilogue.  tcgen05.ld the finished accumulator (each warp
+//                      owns the 32 TMEM lanes of its quarter), rescale, store.
+//                      The second TMEM buffer lets tile t's epilogue overlap
+//                      tile t+1's main loop.
+// Integer accumulation is exact and order-free, so any tiling gives the
+// reference's sums bit for bit.
+//
+// Every wait on an mbarrier is bounded: after ~2 s it records a code in the
+// status word, raises a CTA-wide abort flag, and all roles fall through to the
+// common exit, which frees the tensor memory.
+#include <cuda.h>
+
+#include <cstdio>
+
+#include "epilogue.cuh"
+#include "sdq_internal.h"
+
+namespace sdq {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;  // int8 elements = bytes: one 128-byte swizzle row
+constexpr int UMMA_K = 32;    // K of one kind::i8 instruction
+constexpr int kNumThreads = 192;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+template <int BLOCK_N>
+struct Cfg {
+  static constexpr int kStages = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
+  static constexpr int kABytes = BLOCK_M * BLOCK_K;
+  static constexpr int kBBytes = BLOCK_N * BLOCK_K;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BLOCK_N;  // two accumulator buffers; a power of two >= 32
+  // stages + barriers/bookkeeping + slack to realign the dynamic base to 1024 B
+  static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
+  // instruction descriptor: D=s32 (2<<4), A=s8 (1<<7), B=s8 (1<<10), both K-major,
+  // N>>3 at bit 17, M>>4 at bit 24
+  static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) |
+                                     ((uint32_t)(BLOCK_N >> 3) << 17) |
+                                     ((uint32_t)(BLOCK_M >> 4) << 24);
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false when it gave up (or another role already did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        __threadfence_system();
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, s8 x s8 -> s32.
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread t receives lane (base_lane+t).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes,
+// written by TMA with SWIZZLE_128B: 8-row groups are 1024 bytes apart (SBO),
+// descriptor version 1 (Blackwell), layout type 2 (128-byte swizzle).  The
+// leading-byte-offset field is not used by swizzled K-major layouts; it is set
+// to 1 (16 bytes) as the canonical encoding does.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// ---------------------------------------------------------------- the kernel
+template <int BLOCK_N>
+__global__ void __launch_bounds__(kNumThreads, 1)
+    qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, GemmArgs g) {
+  using C = Cfg<BLOCK_N>;
+  extern __shared__ uint8_t smem_raw[];
+  // SWIZZLE_128B atoms (8 rows x 128 B) must start on 1024-byte boundaries.
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = base + C::kStages * C::kABytes;
+  uint8_t* book = smem + C::kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(book);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m_blocks = (int)((g.M + BLOCK_M - 1) / BLOCK_M);
+  const int num_n_blocks = (int)((g.N + BLOCK_N - 1) / BLOCK_N);
+  const int num_k_blocks = (int)((g.K + BLOCK_K - 1) / BLOCK_K);
+  const int num_tiles = num_m_blocks * num_n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; s++) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------ TMA producer
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m_blk = tile / num_n_blocks, n_blk = tile % num_n_blocks;
+        for (int kb = 0; kb < num_k_blocks; kb++) {
+          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x100 | 1);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, C::kStageBytes);
+          tma_load_2d(smem_a + stage * C::kABytes, &tmap_a, full, kb * BLOCK_K, m_blk * BLOCK_M);
+          tma_load_2d(smem_b + stage * C::kBBytes, &tmap_b, full, kb * BLOCK_K, n_blk * BLOCK_N);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------ MMA issuer
+      uint32_t stage = 0, phase = 0, abuf = 0, aphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        ok = mbar_wait(bar_tempty + 8 * abuf, aphase ^ 1u, abort_flag, g.status, 0x200 | 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + abuf * BLOCK_N;
+        for (int kb = 0; kb < num_k_blocks; kb++) {
+          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x200 | 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_a + stage * C::kABytes);
+          const uint64_t bdesc = make_smem_desc(smem_b + stage * C::kBBytes);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+            // stepping K by 32 bytes inside the swizzle atom = +2 in the 16-byte address field
+            umma_i8(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)),
+                    bdesc + (uint64_t)(k * (UMMA_K >> 4)), C::kIdesc, (uint32_t)((kb | k) != 0));
+          }
+          umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(bar_tfull + 8 * abuf);  // accumulator complete
+        abuf ^= 1u;
+        if (abuf == 0) aphase ^= 1u;
+      }
+    }
+  } else {
+    // -------------------------------------------------- epilogue (4 warps)
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
+    const bool gelu = (g.flags & SDQ_GELU_TANH) != 0;
+    const bool vec_ok = (g.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0);
+    uint32_t abuf = 0, aphase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      const int m_blk = tile / num_n_blocks, n_blk = tile % num_n_blocks;
+      ok = mbar_wait(bar_tfull + 8 * abuf, aphase, abort_flag, g.status, 0x300 | 1);
+      // all 32 lanes poll the same barrier, so `ok` is warp-uniform in practice; make it so
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = (int64_t)m_blk * BLOCK_M + quarter * 32 + lane;
+      const bool row_ok = row < g.M;
+      const float a_s = row_ok ? g.a_scale[row] : 0.0f;
+      float* out_row = g.out + row * g.N;
+      int32_t* dump_row = g.acc_dump ? g.acc_dump + row * g.N : nullptr;
+      const int64_t n0 = (int64_t)n_blk * BLOCK_N;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; c++) {
+        const int64_t nc = n0 + c * 32;
+        if (nc >= g.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + abuf * BLOCK_N + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+        tmem_ld_wait();
+        if (row_ok) {
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (nc + j < g.N) {  // N % 4 == 0: a group of 4 is wholly inside or outside
+                const float4 bs = __ldg(reinterpret_cast<const float4*>(g.b_scale + nc + j));
+                float4 o;
+                if (g.bias) {
+                  const float4 bb = __ldg(reinterpret_cast<const float4*>(g.bias + nc + j));
+                  o.x = epilogue_value((int)r[j + 0], a_s, bs.x, &bb.x, gelu);
+                  o.y = epilogue_value((int)r[j + 1], a_s, bs.y, &bb.y, gelu);
+                  o.z = epilogue_value((int)r[j + 2], a_s, bs.z, &bb.z, gelu);
+                  o.w = epilogue_value((int)r[j + 3], a_s, bs.w, &bb.w, gelu);
+                } else {
+                  o.x = epilogue_value((int)r[j + 0], a_s, bs.x, nullptr, gelu);
+                  o.y = epilogue_value((int)r[j + 1], a_s, bs.y, nullptr, gelu);
+                  o.z = epilogue_value((int)r[j + 2], a_s, bs.z, nullptr, gelu);
+                  o.w = epilogue_value((int)r[j + 3], a_s, bs.w, nullptr, gelu);
+                }
+                *reinterpret_cast<float4*>(out_row + nc + j) = o;
+                if (dump_row)
+                  *reinterpret_cast<int4*>(dump_row + nc + j) =
+                      make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              if (nc + j < g.N) {
+                out_row[nc + j] = epilogue_value((int)r[j], a_s, __ldg(g.b_scale + nc + j),
+                                                 g.bias ? g.bias + nc + j : nullptr, gelu);
+                if (dump_row) dump_row[nc + j] = (int)r[j];
+              }
+            }
+          }
+        }
+      }
+      // hand the accumulator buffer back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * abuf);
+      abuf ^= 1u;
+      if (abuf == 0) aphase ^= 1u;
+    }
+  }
+
+  // ---------------------------------------------------- common exit
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*abort_flag) {
+    // give bulk copies that may still be in flight time to land before the CTA's
+    // shared memory is released (bounded: ~1 ms)
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();  // the dealloc is a warp-wide (.sync.aligned) instruction
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// [rows, K] int8 row-major, box = box_rows x 128 bytes, 128-byte swizzle, zero fill outside.
+bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows,
+               std::string* why) {
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};  // bytes between rows
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (why) *why = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);
+    return false;
+  }
+  return true;
+}
+
+template <int BLOCK_N>
+cudaError_t launch_t(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
+  using C = Cfg<BLOCK_N>;
+  CUtensorMap ta, tb;
+  if (!make_tmap(&ta, g.aq, g.M, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;
+  if (!make_tmap(&tb, g.bq, g.N, g.K, BLOCK_N, why)) return cudaErrorInvalidValue;
+  const int64_t tiles = ((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + BLOCK_N - 1) / BLOCK_N);
+  const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+  count_launch();
+  qgemm_tc_kernel<BLOCK_N><<<grid, kNumThreads, C::kSmemBytes, s>>>(ta, tb, g);
+  return cudaGetLastError();
+}
+
+template <int BLOCK_N>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(qgemm_tc_kernel<BLOCK_N>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Cfg<BLOCK_N>::kSmemBytes);
+}
+
+}  // namespace
+
+int qgemm_tc_setup(std::string* why) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+    if (why) *why = "cuTensorMapEncodeTiled is not available from this driver";
+    return SDQ_ERR_CUDA;
+  }
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  cudaError_t a = set_smem_attr<256>();
+  if (a == cudaSuccess) a = set_smem_attr<128>();
+  if (a == cudaSuccess) a = set_smem_attr<64>();
+  if (a == cudaSuccess) a = set_smem_attr<32>();
+  if (a != cudaSuccess) {
+    if (why) *why = std::string("cudaFuncSetAttribute(max dynamic smem): ") + cudaGetErrorString(a);
+    return SDQ_ERR_CUDA;
+  }
+  return SDQ_OK;
+}
+
+bool qgemm_tc_supported(const GemmArgs& g) {
+  return g_encode != nullptr && g.M > 0 && g.N > 0 && g.K > 0 && (g.K % 16 == 0) &&
+         ((reinterpret_cast<uintptr_t>(g.aq) & 15) == 0) &&
+         ((reinterpret_cast<uintptr_t>(g.bq) & 15) == 0) && g.M < (int64_t(1) << 31) &&
+         g.N < (int64_t(1) << 31) && g.K < (int64_t(1) << 31) &&
+         ((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + 31) / 32) < (int64_t(1) << 31);
+}
+
+cudaError_t launch_qgemm_tc(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
+  // Largest N tile that still gives every SM a tile; small problems take narrower
+  // tiles so that more SMs pull weight bytes from HBM at once.
+  const int64_t mb = (g.M + BLOCK_M - 1) / BLOCK_M;
+  auto tiles = [&](int bn) { return mb * ((g.N + bn - 1) / bn); };
+  if (tiles(256) >= sm_count) return launch_t<256>(g, sm_count, s, why);
+  if (tiles(128) >= sm_count) return launch_t<128>(g, sm_count, s, why);
+  if (tiles(64) >= sm_count) return launch_t<64>(g, sm_count, s, why);
+  return launch_t<32>(g, sm_count, s, why);
+}
+
+}  // namespace sdq

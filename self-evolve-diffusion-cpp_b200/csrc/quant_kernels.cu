@@ -1,0 +1,280 @@
+// Row quantization kernels: HBM-bound, one pass over the source.
+//
+// Activation rows (first half of sd::qgemm, reference src/core/qgemm.cpp:82-96),
+// weight rows in the two recipes of the reference (tools/quantize/pack_sdcpp.py:45-51
+// and src/core/tensor.cpp:63-78), and the row dequantizer (src/model/ovi_dit.cpp:53-63).
+//
+// Every fp32 operation that decides an output bit uses an explicit
+// round-to-nearest intrinsic (__fdiv_rn, __fmul_rn) so that the compiler can
+// neither fuse nor approximate it: the results are bit-identical to the CPU.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <climits>
+
+#include "sdq_internal.h"
+
+namespace sdq {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide max of non-negative, non-NaN values.  `red` holds kThreads/32 floats.
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // protects `red` against the previous row's readers
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < kThreads / 32) ? red[lane] : 0.0f;
+  return warp_max(r);
+}
+
+// |x| folded into a running max the way std::max(mx, fabs(x)) does: a NaN is skipped.
+__device__ __forceinline__ float fold_abs(float mx, float x) { return fmaxf(mx, fabsf(x)); }
+
+// The reference rounds with cvtss2si (src/core/qgemm.cpp:62-69): nearest-even, and
+// INT_MIN for NaN or anything outside 32 bits, then clamps to [-127,127].
+__device__ __forceinline__ int act_round(float p) {
+  int v = (fabsf(p) < 2147483648.0f) ? __float2int_rn(p) : INT_MIN;
+  return max(-127, min(127, v));
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
+         ((uint32_t)(d & 0xff) << 24);
+}
+
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+
+// ---- activations: a row lives in registers between the max and the rounding ----
+// Requires K % 4 == 0, 16-byte aligned A, K <= kThreads * 4 * VPT.
+template <int VPT>
+__global__ void __launch_bounds__(kThreads) act_quant_regs(const float* __restrict__ A, int64_t M,
+                                                           int64_t K, int8_t* __restrict__ aq,
+                                                           float* __restrict__ a_scale) {
+  __shared__ float red[kThreads / 32];
+  const int k4 = (int)(K >> 2);
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float4* src = reinterpret_cast<const float4*>(A + row * K);
+    float4 v[VPT];
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < k4) {
+        v[i] = ld_stream(src + idx);
+        mx = fold_abs(fold_abs(fold_abs(fold_abs(mx, v[i].x), v[i].y), v[i].z), v[i].w);
+      }
+    }
+    mx = block_max(mx, red);
+    float sc = __fdiv_rn(mx, 127.0f);
+    if (sc == 0.0f) sc = 1.0f;
+    if (threadIdx.x == 0) a_scale[row] = sc;
+    const float inv = __fdiv_rn(1.0f, sc);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(aq + row * K);
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < k4)
+        dst[idx] = pack4(act_round(__fmul_rn(v[i].x, inv)), act_round(__fmul_rn(v[i].y, inv)),
+                         act_round(__fmul_rn(v[i].z, inv)), act_round(__fmul_rn(v[i].w, inv)));
+    }
+  }
+}
+
+// Any K and alignment: two sweeps over the row (the second is served by L1/L2).
+__global__ void __launch_bounds__(kThreads) act_quant_generic(const float* __restrict__ A,
+                                                              int64_t M, int64_t K,
+                                                              int8_t* __restrict__ aq,
+                                                              float* __restrict__ a_scale) {
+  __shared__ float red[kThreads / 32];
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float* src = A + row * K;
+    float mx = 0.0f;
+    for (int64_t k = threadIdx.x; k < K; k += kThreads) mx = fold_abs(mx, src[k]);
+    mx = block_max(mx, red);
+    float sc = __fdiv_rn(mx, 127.0f);
+    if (sc == 0.0f) sc = 1.0f;
+    if (threadIdx.x == 0) a_scale[row] = sc;
+    const float inv = __fdiv_rn(1.0f, sc);
+    int8_t* dst = aq + row * K;
+    for (int64_t k = threadIdx.x; k < K; k += kThreads)
+      dst[k] = (int8_t)act_round(__fmul_rn(src[k], inv));
+  }
+}
+
+// ---- weights ----
+template <int DT>
+__device__ __forceinline__ float load_src(const void* p, int64_t i);
+template <>
+__device__ __forceinline__ float load_src<SDQ_F32>(const void* p, int64_t i) {
+  return static_cast<const float*>(p)[i];
+}
+template <>
+__device__ __forceinline__ float load_src<SDQ_BF16>(const void* p, int64_t i) {
+  // bits << 16, exactly the packer's widening (tools/quantize/pack_sdcpp.py:40-41)
+  return __uint_as_float((uint32_t) static_cast<const uint16_t*>(p)[i] << 16);
+}
+template <>
+__device__ __forceinline__ float load_src<SDQ_F16>(const void* p, int64_t i) {
+  return __half2float(static_cast<const __half*>(p)[i]);  // exact widening
+}
+
+// Round one element under the chosen recipe, given the row's absmax.
+template <int MODE>
+struct RowRecipe {
+  float mul;  // PACKER: 127/safe ; ROWWISE: the divisor sc
+  float scale;
+  __device__ explicit RowRecipe(float amax) {
+    if (MODE == SDQ_MODE_PACKER) {
+      const float safe = amax > 0.0f ? amax : 1.0f;
+      mul = __fdiv_rn(127.0f, safe);
+      scale = __fdiv_rn(amax, 127.0f);
+    } else {
+      float sc = __fdiv_rn(amax, 127.0f);
+      if (sc == 0.0f) sc = 1.0f;
+      mul = sc;
+      scale = sc;
+    }
+  }
+  __device__ __forceinline__ int q(float x) const {
+    if (MODE == SDQ_MODE_PACKER) {
+      // np.rint (half to even), then np.clip(-127,127), then astype(int8)
+      float r = rintf(__fmul_rn(x, mul));
+      r = fminf(fmaxf(r, -127.0f), 127.0f);
+      return (int)r;
+    } else {
+      // std::lround: half away from zero; the int8 cast of the reference does not clamp
+      return (int)(int8_t)lroundf(__fdiv_rn(x, mul));
+    }
+  }
+};
+
+// One block per row (grid-stride), two sweeps.  `last` any size.
+template <int DT, int MODE>
+__global__ void __launch_bounds__(kThreads) quant_rows_block(const void* __restrict__ src,
+                                                             int64_t rows, int64_t last,
+                                                             int8_t* __restrict__ q,
+                                                             float* __restrict__ scale) {
+  __shared__ float red[kThreads / 32];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int64_t base = row * last;
+    float mx = 0.0f;
+    for (int64_t k = threadIdx.x; k < last; k += kThreads) {
+      const float f = fabsf(load_src<DT>(src, base + k));
+      // PACKER: np.abs(x).max() ; ROWWISE: std::max(mx, std::abs(w)) -- equal for finite rows
+      mx = fmaxf(mx, f);
+    }
+    mx = block_max(mx, red);
+    const RowRecipe<MODE> rr(mx);
+    if (threadIdx.x == 0) scale[row] = rr.scale;
+    for (int64_t k = threadIdx.x; k < last; k += kThreads)
+      q[base + k] = (int8_t)rr.q(load_src<DT>(src, base + k));
+  }
+}
+
+// One warp per row for short rows (last <= 64), e.g. conv kernels with rows of 7 or 2.
+template <int DT, int MODE>
+__global__ void __launch_bounds__(kThreads) quant_rows_warp(const void* __restrict__ src,
+                                                            int64_t rows, int64_t last,
+                                                            int8_t* __restrict__ q,
+                                                            float* __restrict__ scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_per_grid = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t row = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); row < rows;
+       row += warps_per_grid) {
+    const int64_t base = row * last;
+    float mx = 0.0f;
+    for (int64_t k = lane; k < last; k += 32) mx = fmaxf(mx, fabsf(load_src<DT>(src, base + k)));
+    mx = warp_max(mx);
+    const RowRecipe<MODE> rr(mx);
+    if (lane == 0) scale[row] = rr.scale;
+    for (int64_t k = lane; k < last; k += 32)
+      q[base + k] = (int8_t)rr.q(load_src<DT>(src, base + k));
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) dequant_rows_kernel(const int8_t* __restrict__ q,
+                                                                const float* __restrict__ scale,
+                                                                int64_t numel, int64_t last,
+                                                                float* __restrict__ w) {
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < numel;
+       i += (int64_t)gridDim.x * kThreads)
+    w[i] = __fmul_rn((float)q[i], scale[i / last]);
+}
+
+template <int DT, int MODE>
+cudaError_t launch_quant_t(const void* src, int64_t rows, int64_t last, int8_t* q, float* scale,
+                           int sm_count, cudaStream_t s) {
+  if (last <= 64) {
+    int64_t blocks = (rows + kThreads / 32 - 1) / (kThreads / 32);
+    if (blocks > (int64_t)sm_count * 32) blocks = (int64_t)sm_count * 32;
+    quant_rows_warp<DT, MODE><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
+  } else {
+    int64_t blocks = rows < (int64_t)sm_count * 8 ? rows : (int64_t)sm_count * 8;
+    quant_rows_block<DT, MODE><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, float* a_scale,
+                             int sm_count, cudaStream_t s) {
+  if (M <= 0 || K <= 0) return cudaSuccess;
+  // 8 resident blocks of 256 threads fill an SM; rows beyond that are strided over.
+  int64_t blocks = M < (int64_t)sm_count * 8 ? M : (int64_t)sm_count * 8;
+  const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(aq) & 3) == 0);
+  const int64_t per_thread = (K / 4 + kThreads - 1) / kThreads;  // float4 per thread
+  count_launch();
+  if (vec && per_thread <= 3) {
+    act_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
+  } else if (vec && per_thread <= 6) {
+    act_quant_regs<6><<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
+  } else if (vec && per_thread <= 14) {
+    act_quant_regs<14><<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
+  } else if (vec && per_thread <= 18) {
+    act_quant_regs<18><<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
+  } else {
+    act_quant_generic<<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_rows(const void* src, int src_dtype, int64_t rows, int64_t last,
+                                 int mode, int8_t* q, float* scale, int sm_count,
+                                 cudaStream_t s) {
+  if (rows <= 0 || last <= 0) return cudaSuccess;
+  count_launch();
+  if (mode == SDQ_MODE_ROWWISE) {
+    if (src_dtype != SDQ_F32) return cudaErrorInvalidValue;
+    return launch_quant_t<SDQ_F32, SDQ_MODE_ROWWISE>(src, rows, last, q, scale, sm_count, s);
+  }
+  switch (src_dtype) {
+    case SDQ_F32: return launch_quant_t<SDQ_F32, SDQ_MODE_PACKER>(src, rows, last, q, scale, sm_count, s);
+    case SDQ_BF16: return launch_quant_t<SDQ_BF16, SDQ_MODE_PACKER>(src, rows, last, q, scale, sm_count, s);
+    case SDQ_F16: return launch_quant_t<SDQ_F16, SDQ_MODE_PACKER>(src, rows, last, q, scale, sm_count, s);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last,
+                                float* w, int sm_count, cudaStream_t s) {
+  const int64_t numel = rows * last;
+  if (numel <= 0) return cudaSuccess;
+  int64_t blocks = (numel + kThreads - 1) / kThreads;
+  if (blocks > (int64_t)sm_count * 16) blocks = (int64_t)sm_count * 16;
+  count_launch();
+  dequant_rows_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(q, scale, numel, last, w);
+  return cudaGetLastError();
+}
+
+}  // namespace sdq

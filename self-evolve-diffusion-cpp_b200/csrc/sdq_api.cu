@@ -1,0 +1,424 @@
+// C-ABI entry points of libsdq: process/device state, memory helpers, the
+// weight registry, and the dispatch of sd::qgemm's two halves onto the kernels.
+#include <algorithm>
+#include <atomic>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "sdq_internal.h"
+
+namespace sdq {
+namespace {
+
+thread_local std::string t_last_error;
+std::atomic<int64_t> g_launches{0};
+
+struct Weight {
+  const int8_t* q = nullptr;   // device [N,K]
+  const float* scale = nullptr;  // device [N]
+  int64_t N = 0, K = 0;
+  bool owned = false;          // q/scale were allocated by sdq_weight_upload
+  const void* host_key = nullptr;
+  bool live = false;
+};
+
+// Scratch of one stream: quantized activations, their scales, and the staging
+// buffers of the host-pointer path.  Grown on demand, never shrunk.
+struct Workspace {
+  int8_t* aq = nullptr; size_t aq_bytes = 0;
+  float* a_scale = nullptr; size_t a_scale_bytes = 0;
+  float* a_stage = nullptr; size_t a_stage_bytes = 0;
+  float* out_stage = nullptr; size_t out_stage_bytes = 0;
+};
+
+struct Context {
+  int device = -1;
+  int sm_count = 0;
+  int* status = nullptr;  // device word written by a kernel whose bounded wait gave up
+  std::mutex mu;
+  std::vector<Weight> weights;                       // handle = index + 1
+  std::unordered_map<const void*, sdq_weight_t> by_host;
+  std::unordered_map<cudaStream_t, Workspace> ws;
+};
+Context* g_ctx = nullptr;
+std::mutex g_init_mu;
+
+template <typename T>
+int grow(T** p, size_t* have, size_t need) {
+  if (need <= *have) return SDQ_OK;
+  if (*p) SDQ_CUDA(cudaFree(*p));
+  *p = nullptr; *have = 0;
+  // round up so that a slowly growing M does not reallocate every call
+  size_t bytes = (need + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(p), bytes);
+  if (e != cudaSuccess) return fail(SDQ_ERR_NOMEM, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+  *have = bytes;
+  return SDQ_OK;
+}
+
+int need_ctx() {
+  if (!g_ctx) return fail(SDQ_ERR_NOT_INIT, "sdq_init has not been called (no CPU fallback exists)");
+  return SDQ_OK;
+}
+
+Weight* get_weight(sdq_weight_t h) {
+  if (!g_ctx || h == 0 || h > g_ctx->weights.size()) return nullptr;
+  Weight* w = &g_ctx->weights[h - 1];
+  return w->live ? w : nullptr;
+}
+
+int check_status_word() {
+  int st = 0;
+  SDQ_CUDA(cudaMemcpy(&st, g_ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(g_ctx->status, 0, sizeof(int));
+    char buf[96];
+    snprintf(buf, sizeof buf, "a bounded wait inside the GEMM kernel gave up (code 0x%x)", st);
+    return fail(SDQ_ERR_DEVICE_TIMEOUT, buf);
+  }
+  return SDQ_OK;
+}
+
+int run_gemm(const Weight& w, const int8_t* aq, const float* a_scale, int64_t M, float* out,
+             const float* bias, int32_t* acc_dump, uint32_t flags, cudaStream_t s) {
+  GemmArgs g;
+  g.aq = aq; g.a_scale = a_scale; g.bq = w.q; g.b_scale = w.scale; g.bias = bias; g.out = out;
+  g.acc_dump = acc_dump; g.M = M; g.N = w.N; g.K = w.K; g.flags = flags & SDQ_GELU_TANH;
+  g.status = g_ctx->status;
+  if (!(flags & SDQ_FORCE_SIMT) && qgemm_tc_supported(g)) {
+    std::string why;
+    cudaError_t e = launch_qgemm_tc(g, g_ctx->sm_count, s, &why);
+    if (e != cudaSuccess) return fail(SDQ_ERR_CUDA, why.empty() ? std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e) : why);
+    return SDQ_OK;
+  }
+  cudaError_t e = launch_qgemm_simt(g, s);
+  if (e != cudaSuccess) return fail(SDQ_ERR_CUDA, std::string("SIMT GEMM launch: ") + cudaGetErrorString(e));
+  return SDQ_OK;
+}
+
+}  // namespace
+
+int fail(int code, const std::string& msg) { t_last_error = msg; return code; }
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(SDQ_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// used by the pack loader (sdcpp_file.cpp)
+int context_sm_count() { return g_ctx ? g_ctx->sm_count : 0; }
+
+}  // namespace sdq
+
+using namespace sdq;
+
+extern "C" {
+
+int sdq_version(void) { return SDQ_VERSION; }
+const char* sdq_last_error(void) { return t_last_error.c_str(); }
+int sdq_device(void) { return g_ctx ? g_ctx->device : -1; }
+int64_t sdq_launch_count(void) { return g_launches.load(); }
+
+int sdq_init(int device) {
+  std::lock_guard<std::mutex> lk(g_init_mu);
+  if (g_ctx) {
+    if (g_ctx->device == device) return SDQ_OK;
+    return fail(SDQ_ERR_INVALID, "sdq_init: this process is already bound to another device");
+  }
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return fail(SDQ_ERR_CUDA, std::string("no CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "count is 0"));
+  if (device < 0 || device >= n) return fail(SDQ_ERR_INVALID, "sdq_init: device index out of range");
+  SDQ_CUDA(cudaSetDevice(device));
+  cudaDeviceProp p;
+  SDQ_CUDA(cudaGetDeviceProperties(&p, device));
+  if (p.major != 10)
+    return fail(SDQ_ERR_CUDA, "sdq_init: this library is built for sm_100a (B200) only; device is sm_" +
+                                  std::to_string(p.major) + std::to_string(p.minor));
+  Context* c = new Context;
+  c->device = device;
+  c->sm_count = p.multiProcessorCount;
+  e = cudaMalloc(reinterpret_cast<void**>(&c->status), sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
+  if (e != cudaSuccess) { delete c; return cuda_fail(e, "status word"); }
+  std::string why;
+  int rc = qgemm_tc_setup(&why);
+  if (rc != SDQ_OK) { cudaFree(c->status); delete c; return fail(rc, why); }
+  g_ctx = c;
+  return SDQ_OK;
+}
+
+int sdq_shutdown(void) {
+  std::lock_guard<std::mutex> lk(g_init_mu);
+  if (!g_ctx) return SDQ_OK;
+  cudaDeviceSynchronize();
+  for (auto& w : g_ctx->weights)
+    if (w.live && w.owned) { cudaFree(const_cast<int8_t*>(w.q)); cudaFree(const_cast<float*>(w.scale)); }
+  for (auto& kv : g_ctx->ws) {
+    cudaFree(kv.second.aq); cudaFree(kv.second.a_scale);
+    cudaFree(kv.second.a_stage); cudaFree(kv.second.out_stage);
+  }
+  cudaFree(g_ctx->status);
+  delete g_ctx;
+  g_ctx = nullptr;
+  return SDQ_OK;
+}
+
+int sdq_malloc(void** dptr, size_t bytes) {
+  if (int rc = need_ctx()) return rc;
+  if (!dptr) return fail(SDQ_ERR_INVALID, "sdq_malloc: null out pointer");
+  *dptr = nullptr;
+  if (bytes == 0) return SDQ_OK;
+  cudaError_t e = cudaMalloc(dptr, bytes);
+  if (e != cudaSuccess) return fail(SDQ_ERR_NOMEM, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+  return SDQ_OK;
+}
+int sdq_free(void* dptr) {
+  if (int rc = need_ctx()) return rc;
+  if (dptr) SDQ_CUDA(cudaFree(dptr));
+  return SDQ_OK;
+}
+int sdq_malloc_host(void** hptr, size_t bytes) {
+  if (int rc = need_ctx()) return rc;
+  if (!hptr) return fail(SDQ_ERR_INVALID, "sdq_malloc_host: null out pointer");
+  *hptr = nullptr;
+  if (bytes == 0) return SDQ_OK;
+  cudaError_t e = cudaHostAlloc(hptr, bytes, cudaHostAllocDefault);
+  if (e != cudaSuccess) return fail(SDQ_ERR_NOMEM, std::string("cudaHostAlloc: ") + cudaGetErrorString(e));
+  return SDQ_OK;
+}
+int sdq_free_host(void* hptr) {
+  if (int rc = need_ctx()) return rc;
+  if (hptr) SDQ_CUDA(cudaFreeHost(hptr));
+  return SDQ_OK;
+}
+int sdq_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (bytes) SDQ_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return SDQ_OK;
+}
+int sdq_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (bytes) SDQ_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return SDQ_OK;
+}
+int sdq_memset(void* dst, int value, size_t bytes, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (bytes) SDQ_CUDA(cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream));
+  return SDQ_OK;
+}
+int sdq_stream_sync(void* stream) {
+  if (int rc = need_ctx()) return rc;
+  SDQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return check_status_word();
+}
+
+// ---- weights ----
+static int register_weight(const Weight& w, sdq_weight_t* out) {
+  std::lock_guard<std::mutex> lk(g_ctx->mu);
+  g_ctx->weights.push_back(w);
+  *out = (sdq_weight_t)g_ctx->weights.size();
+  if (w.host_key) g_ctx->by_host[w.host_key] = *out;
+  return SDQ_OK;
+}
+
+int sdq_weight_upload(const int8_t* q_host, const float* scale_host, int64_t N, int64_t K,
+                      sdq_weight_t* out) {
+  if (int rc = need_ctx()) return rc;
+  if (!q_host || !scale_host || !out || N <= 0 || K <= 0)
+    return fail(SDQ_ERR_INVALID, "sdq_weight_upload: null pointer or non-positive shape");
+  int8_t* dq = nullptr; float* ds = nullptr;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&dq), (size_t)N * K);  // cudaMalloc is >= 256-B aligned
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ds), (size_t)N * 4);
+  if (e == cudaSuccess) e = cudaMemcpy(dq, q_host, (size_t)N * K, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(ds, scale_host, (size_t)N * 4, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) { cudaFree(dq); cudaFree(ds); return cuda_fail(e, "sdq_weight_upload"); }
+  Weight w; w.q = dq; w.scale = ds; w.N = N; w.K = K; w.owned = true; w.host_key = q_host; w.live = true;
+  return register_weight(w, out);
+}
+
+int sdq_weight_wrap_device(const int8_t* q_dev, const float* scale_dev, int64_t N, int64_t K,
+                           sdq_weight_t* out) {
+  if (int rc = need_ctx()) return rc;
+  if (!q_dev || !scale_dev || !out || N <= 0 || K <= 0)
+    return fail(SDQ_ERR_INVALID, "sdq_weight_wrap_device: null pointer or non-positive shape");
+  Weight w; w.q = q_dev; w.scale = scale_dev; w.N = N; w.K = K; w.owned = false; w.live = true;
+  return register_weight(w, out);
+}
+
+int sdq_weight_lookup(const void* q_host, sdq_weight_t* out) {
+  if (int rc = need_ctx()) return rc;
+  if (!out) return fail(SDQ_ERR_INVALID, "sdq_weight_lookup: null out pointer");
+  std::lock_guard<std::mutex> lk(g_ctx->mu);
+  auto it = g_ctx->by_host.find(q_host);
+  if (it == g_ctx->by_host.end()) { *out = 0; return fail(SDQ_ERR_NOT_FOUND, "sdq_weight_lookup: no weight was uploaded from this host address"); }
+  *out = it->second;
+  return SDQ_OK;
+}
+
+int sdq_weight_info(sdq_weight_t h, int64_t* N, int64_t* K, const int8_t** q_dev,
+                    const float** scale_dev) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return fail(SDQ_ERR_INVALID, "sdq_weight_info: bad weight handle");
+  if (N) *N = w->N;
+  if (K) *K = w->K;
+  if (q_dev) *q_dev = w->q;
+  if (scale_dev) *scale_dev = w->scale;
+  return SDQ_OK;
+}
+
+int sdq_weight_release(sdq_weight_t h) {
+  if (int rc = need_ctx()) return rc;
+  std::lock_guard<std::mutex> lk(g_ctx->mu);
+  Weight* w = get_weight(h);
+  if (!w) return fail(SDQ_ERR_INVALID, "sdq_weight_release: bad weight handle");
+  if (w->owned) { cudaFree(const_cast<int8_t*>(w->q)); cudaFree(const_cast<float*>(w->scale)); }
+  if (w->host_key) {
+    auto it = g_ctx->by_host.find(w->host_key);
+    if (it != g_ctx->by_host.end() && it->second == h) g_ctx->by_host.erase(it);
+  }
+  *w = Weight();
+  return SDQ_OK;
+}
+
+// ---- hot path ----
+int sdq_quantize_activations(const float* A_dev, int64_t M, int64_t K, int8_t* aq_dev,
+                             float* a_scale_dev, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (M < 0 || K < 0) return fail(SDQ_ERR_INVALID, "sdq_quantize_activations: negative shape");
+  if (M == 0 || K == 0) return SDQ_OK;
+  if (!A_dev || !aq_dev || !a_scale_dev) return fail(SDQ_ERR_INVALID, "sdq_quantize_activations: null pointer");
+  SDQ_CUDA(launch_act_quant(A_dev, M, K, aq_dev, a_scale_dev, g_ctx->sm_count, (cudaStream_t)stream));
+  return SDQ_OK;
+}
+
+int sdq_qgemm_prequantized(sdq_weight_t h, const int8_t* aq_dev, const float* a_scale_dev,
+                           int64_t M, float* out_dev, const float* bias_dev,
+                           int32_t* acc_dump_dev, uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm_prequantized: bad weight handle");
+  if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_qgemm_prequantized: negative M");
+  if (M == 0) return SDQ_OK;
+  if (!aq_dev || !a_scale_dev || !out_dev) return fail(SDQ_ERR_INVALID, "sdq_qgemm_prequantized: null pointer");
+  int rc = run_gemm(*w, aq_dev, a_scale_dev, M, out_dev, bias_dev, acc_dump_dev, flags, (cudaStream_t)stream);
+  if (rc == SDQ_OK && (flags & SDQ_SYNC)) rc = sdq_stream_sync(stream);
+  return rc;
+}
+
+int sdq_qgemm(sdq_weight_t h, const float* A, int64_t M, float* out, const float* bias,
+              uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm: bad weight handle");
+  if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_qgemm: negative M");
+  if (M == 0) return SDQ_OK;
+  if (!A || !out) return fail(SDQ_ERR_INVALID, "sdq_qgemm: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t N = w->N, K = w->K;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  if (int rc = grow(&ws->aq, &ws->aq_bytes, (size_t)M * K)) return rc;
+  if (int rc = grow(&ws->a_scale, &ws->a_scale_bytes, (size_t)M * 4)) return rc;
+  const float* A_dev = A;
+  float* out_dev = out;
+  if (flags & SDQ_A_HOST) {
+    if (int rc = grow(&ws->a_stage, &ws->a_stage_bytes, (size_t)M * K * 4)) return rc;
+    SDQ_CUDA(cudaMemcpyAsync(ws->a_stage, A, (size_t)M * K * 4, cudaMemcpyHostToDevice, s));
+    A_dev = ws->a_stage;
+  }
+  if (flags & SDQ_OUT_HOST) {
+    if (int rc = grow(&ws->out_stage, &ws->out_stage_bytes, (size_t)M * N * 4)) return rc;
+    out_dev = ws->out_stage;
+  }
+  SDQ_CUDA(launch_act_quant(A_dev, M, K, ws->aq, ws->a_scale, g_ctx->sm_count, s));
+  if (int rc = run_gemm(*w, ws->aq, ws->a_scale, M, out_dev, bias, nullptr, flags, s)) return rc;
+  if (flags & SDQ_OUT_HOST) {
+    SDQ_CUDA(cudaMemcpyAsync(out, out_dev, (size_t)M * N * 4, cudaMemcpyDeviceToHost, s));
+    // the caller owns `out` when this returns: a host result must be complete
+    return sdq_stream_sync(stream);
+  }
+  if (flags & SDQ_SYNC) return sdq_stream_sync(stream);
+  return SDQ_OK;
+}
+
+// ---- weight quantizers ----
+static size_t src_elem_size(int dt) { return dt == SDQ_F32 ? 4 : 2; }
+
+int sdq_quantize_rows(const void* src, int src_dtype, int64_t rows, int64_t last, int mode,
+                      int8_t* q, float* scale, uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (rows < 0 || last < 0) return fail(SDQ_ERR_INVALID, "sdq_quantize_rows: negative shape");
+  if (src_dtype != SDQ_F32 && src_dtype != SDQ_BF16 && src_dtype != SDQ_F16)
+    return fail(SDQ_ERR_INVALID, "sdq_quantize_rows: unknown source dtype");
+  if (mode != SDQ_MODE_PACKER && mode != SDQ_MODE_ROWWISE)
+    return fail(SDQ_ERR_INVALID, "sdq_quantize_rows: unknown mode");
+  if (mode == SDQ_MODE_ROWWISE && src_dtype != SDQ_F32)
+    return fail(SDQ_ERR_INVALID, "sdq_quantize_rows: the rowwise recipe takes fp32 input only");
+  if (rows == 0 || last == 0) return SDQ_OK;
+  if (!src || !q || !scale) return fail(SDQ_ERR_INVALID, "sdq_quantize_rows: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t numel = (size_t)rows * last, in_bytes = numel * src_elem_size(src_dtype);
+  void* d_src = nullptr; int8_t* d_q = nullptr; float* d_scale = nullptr;
+  const void* k_src = src; int8_t* k_q = q; float* k_scale = scale;
+  int rc = SDQ_OK;
+  cudaError_t e = cudaSuccess;
+  if (flags & SDQ_SRC_HOST) {
+    e = cudaMalloc(&d_src, in_bytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_src, src, in_bytes, cudaMemcpyHostToDevice, s);
+    k_src = d_src;
+  }
+  if (e == cudaSuccess && (flags & SDQ_DST_HOST)) {
+    e = cudaMalloc(reinterpret_cast<void**>(&d_q), numel);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&d_scale), (size_t)rows * 4);
+    k_q = d_q; k_scale = d_scale;
+  }
+  if (e == cudaSuccess)
+    e = launch_quantize_rows(k_src, src_dtype, rows, last, mode, k_q, k_scale, g_ctx->sm_count, s);
+  if (e == cudaSuccess && (flags & SDQ_DST_HOST)) {
+    e = cudaMemcpyAsync(q, d_q, numel, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(scale, d_scale, (size_t)rows * 4, cudaMemcpyDeviceToHost, s);
+  }
+  if (e == cudaSuccess && (flags & (SDQ_SRC_HOST | SDQ_DST_HOST))) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) rc = cuda_fail(e, "sdq_quantize_rows");
+  cudaFree(d_src); cudaFree(d_q); cudaFree(d_scale);
+  return rc;
+}
+
+int sdq_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last, float* w,
+                     uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (rows < 0 || last < 0) return fail(SDQ_ERR_INVALID, "sdq_dequant_rows: negative shape");
+  if (rows == 0 || last == 0) return SDQ_OK;
+  if (!q || !scale || !w) return fail(SDQ_ERR_INVALID, "sdq_dequant_rows: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t numel = (size_t)rows * last;
+  int8_t* d_q = nullptr; float* d_scale = nullptr; float* d_w = nullptr;
+  const int8_t* k_q = q; const float* k_scale = scale; float* k_w = w;
+  cudaError_t e = cudaSuccess;
+  if (flags & SDQ_SRC_HOST) {
+    e = cudaMalloc(reinterpret_cast<void**>(&d_q), numel);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&d_scale), (size_t)rows * 4);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_q, q, numel, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_scale, scale, (size_t)rows * 4, cudaMemcpyHostToDevice, s);
+    k_q = d_q; k_scale = d_scale;
+  }
+  if (e == cudaSuccess && (flags & SDQ_DST_HOST)) {
+    e = cudaMalloc(reinterpret_cast<void**>(&d_w), numel * 4);
+    k_w = d_w;
+  }
+  if (e == cudaSuccess) e = launch_dequant_rows(k_q, k_scale, rows, last, k_w, g_ctx->sm_count, s);
+  if (e == cudaSuccess && (flags & SDQ_DST_HOST)) e = cudaMemcpyAsync(w, d_w, numel * 4, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess && (flags & (SDQ_SRC_HOST | SDQ_DST_HOST))) e = cudaStreamSynchronize(s);
+  int rc = e == cudaSuccess ? SDQ_OK : cuda_fail(e, "sdq_dequant_rows");
+  cudaFree(d_q); cudaFree(d_scale); cudaFree(d_w);
+  return rc;
+}
+
+}  // extern "C"

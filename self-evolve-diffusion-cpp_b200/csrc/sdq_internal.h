@@ -1,0 +1,57 @@
+// Internal declarations shared by the translation units of libsdq.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+#include "sdq.h"
+
+namespace sdq {
+
+// ---- error plumbing (sdq_api.cu) ----
+int fail(int code, const std::string& msg);  // records msg for sdq_last_error, returns code
+int cuda_fail(cudaError_t e, const char* what);
+#define SDQ_CUDA(expr)                                             \
+  do {                                                             \
+    cudaError_t _e = (expr);                                       \
+    if (_e != cudaSuccess) return ::sdq::cuda_fail(_e, #expr);     \
+  } while (0)
+
+void count_launch(int n = 1);
+
+// ---- activation / weight quantization kernels (quant_kernels.cu) ----
+// aq int8 [M,K], a_scale f32 [M]; all device pointers.
+cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, float* a_scale,
+                             int sm_count, cudaStream_t s);
+// src_dtype SDQ_F32/BF16/F16, mode SDQ_MODE_*; all device pointers.
+cudaError_t launch_quantize_rows(const void* src, int src_dtype, int64_t rows, int64_t last,
+                                 int mode, int8_t* q, float* scale, int sm_count, cudaStream_t s);
+cudaError_t launch_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last,
+                                float* w, int sm_count, cudaStream_t s);
+
+// ---- GEMM kernels ----
+struct GemmArgs {
+  const int8_t* aq;       // [M,K]
+  const float* a_scale;   // [M]
+  const int8_t* bq;       // [N,K]
+  const float* b_scale;   // [N]
+  const float* bias;      // [N] or null
+  float* out;             // [M,N]
+  int32_t* acc_dump;      // [M,N] or null
+  int64_t M, N, K;
+  uint32_t flags;         // SDQ_GELU_TANH
+  int* status;            // device word: 0 ok, else a code written by a kernel that gave up
+};
+
+// Portable CUDA-core kernel (any M, N, K): qgemm_simt.cu
+cudaError_t launch_qgemm_simt(const GemmArgs& g, cudaStream_t s);
+
+// tcgen05 kernel: qgemm_tcgen05.cu.  Needs K % 16 == 0 and 16-byte aligned aq / bq.
+bool qgemm_tc_supported(const GemmArgs& g);
+// Returns cudaSuccess or the launch error; `why` receives text on tensor-map failures.
+cudaError_t launch_qgemm_tc(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why);
+// One-time set-up (driver entry point lookup, max-shared-memory attributes).
+int qgemm_tc_setup(std::string* why);
+
+}  // namespace sdq
