@@ -1,0 +1,366 @@
+#!/usr/bin/env python3
+"""Benchmark of the int8 quantized-linear path (one JSON line on stdout).
+
+Workload ("ffn_pair_720p"): the DiT FFN pair at the 720p/121-frame token count,
+per GPU  M = 27280 rows:  x[M,3072] -> int8 linear 3072->14336 (+bias, GELU-tanh)
+-> int8 linear 14336->3072 (+bias).  One step = one pass of that pair: two
+activation-quantization launches and two tcgen05 GEMM launches.  Weights are
+synthetic N(0,0.02) bf16 packed to int8 by the GPU packer; activations N(0,1)*0.5.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]          (torchrun for N > 1)
+  python bench.py --impl reference ...   times the reference's CPU sd::qgemm instead
+
+Multi-GPU: token rows are sharded, weights replicated, no collective in the data
+path (weak scaling: every rank runs M rows).  `value` is the whole-job int8
+throughput in TOPS (2*M*N*K per GEMM, the reference's own formula,
+tests/test_core.cpp:174).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D_MODEL, D_FFN, M_720P = 3072, 14336, 27280
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+INT8_NOMINAL_TOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (the
+# 3072->14336 GEMM at M=27280), from the ncu capture summarised under profiles/; None
+# until that capture exists.
+NCU_TRAFFIC_BYTES = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--rows", type=int, default=M_720P, help="token rows per GPU")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def ffn_ops(rows):
+    return 2.0 * rows * D_MODEL * D_FFN * 2
+
+
+def gemm_bytes(M, K, N, bias=True):
+    """Algorithmic bytes of one quantized linear: fp32 A in, int8 W, scales, fp32 out."""
+    return 4 * M * K + N * K + 4 * N + 4 * M * N + (4 * N if bias else 0)
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """nvidia-smi samples of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        inside = [r for (t, r) in self.rows if t0 - 0.05 <= t <= t1 + 0.15] or [r for _, r in self.rows[-3:]]
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in inside:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ reference arm (CPU)
+def reference_throughput(A, w1, w2, b1, b2, rows, reps=1):
+    """Seconds for the FFN pair on `rows` rows with the reference's own compiled sd::qgemm
+    (all host threads); falls back to the oracle port where oracle/_ref is absent."""
+    from oracle.binding import Oracle, Reference
+    orc = Oracle()
+    if Reference.available():
+        ref, kind, cores = Reference(), "reference", None
+        cores = ref.nthreads()
+        qg = ref.qgemm
+    else:
+        kind, cores, qg = "port", orc.threads(), orc.qgemm
+    best = 1e30
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        h = qg(A[:rows], w1[0], w1[1])
+        h = orc.gelu_tanh(orc.bias_add(h, b1, inplace=True), inplace=True)
+        y = qg(h, w2[0], w2[1])
+        y = orc.bias_add(y, b2, inplace=True)
+        best = min(best, time.perf_counter() - t0)
+    return best, kind, cores
+
+
+def host_problem(rows, seed=42):
+    """Seeded host copy of the workload (weights packed by the oracle's packer arithmetic)."""
+    from oracle.binding import Oracle
+    orc = Oracle()
+    rng = np.random.default_rng(seed)
+    A = (rng.standard_normal((rows, D_MODEL)) * 0.5).astype(np.float32)
+
+    def w(n, k):
+        bits = orc.f32_to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        return orc.quant_rows_packer(orc.bf16_to_f32(bits))
+    w1, w2 = w(D_FFN, D_MODEL), w(D_MODEL, D_FFN)
+    b1 = (rng.standard_normal(D_FFN) * 0.02).astype(np.float32)
+    b2 = (rng.standard_normal(D_MODEL) * 0.02).astype(np.float32)
+    return A, w1, w2, b1, b2
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    probe_rows = 64
+    A, w1, w2, b1, b2 = host_problem(4096)
+    t_probe, kind, cores = reference_throughput(A, w1, w2, b1, b2, probe_rows)
+    # size a step so that warmup+steps take about two minutes of CPU time
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    rows = int(max(32, min(4096, probe_rows * budget / t_probe)))
+    rows -= rows % 8
+    for _ in range(args.warmup):
+        reference_throughput(A, w1, w2, b1, b2, rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        reference_throughput(A, w1, w2, b1, b2, rows)
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = ffn_ops(rows) / dt / 1e12
+    sample = "FFN pair on %d of %d rows per step, all host threads" % (rows, args.rows)
+    line = {"impl": "reference", "metric": "int8_qgemm_throughput", "value": tops, "unit": "TOPS",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8",
+            "data": "synthetic",
+            "config": {"workload": "ffn_pair_720p", "rows_per_gpu": args.rows, "k_n": [D_MODEL, D_FFN],
+                       "device": "host CPU"},
+            "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+    return 0
+
+
+# ------------------------------------------------------------------ B200 arm
+def run_b200(args):
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as ge
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch N>1 with torch.distributed.run" % (args.gpus, world))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = ge.load_package()
+    s = pkg.Sdq(local)
+    S = pkg.sdq
+    lib = s.lib
+    dev = torch.device("cuda", local)
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    M = args.rows
+
+    def ck(rc):
+        s._ck(rc)
+
+    # ---- synthetic problem, resident in HBM before any timing starts
+    g = torch.Generator(device=dev)
+    g.manual_seed(42 + rank)
+    A = torch.randn(M, D_MODEL, device=dev, generator=g, dtype=torch.float32) * 0.5
+
+    def packed(n, k):
+        wb = (torch.randn(n, k, device=dev, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        q = torch.empty(n, k, device=dev, dtype=torch.int8)
+        sc = torch.empty(n, device=dev, dtype=torch.float32)
+        ck(lib.sdq_quantize_rows(wb.data_ptr(), S.BF16, n, k, S.MODE_PACKER, q.data_ptr(), sc.data_ptr(), 0, sp))
+        return q, sc, s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), n, k)
+    q1, s1, w1 = packed(D_FFN, D_MODEL)
+    q2, s2, w2 = packed(D_MODEL, D_FFN)
+    b1 = torch.randn(D_FFN, device=dev, generator=g) * 0.02
+    b2 = torch.randn(D_MODEL, device=dev, generator=g) * 0.02
+    H = torch.empty(M, D_FFN, device=dev, dtype=torch.float32)
+    Y = torch.empty(M, D_MODEL, device=dev, dtype=torch.float32)
+    aq = torch.empty(M * D_FFN, device=dev, dtype=torch.int8)
+    a_s = torch.empty(M, device=dev, dtype=torch.float32)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def step(marks=None):
+        # quantize -> GEMM(+bias+GELU) -> quantize -> GEMM(+bias); `marks` collects events
+        def mark():
+            if marks is not None:
+                e = ev()
+                e.record(stream)
+                marks.append(e)
+        mark()
+        ck(lib.sdq_quantize_activations(A.data_ptr(), M, D_MODEL, aq.data_ptr(), a_s.data_ptr(), sp))
+        mark()
+        ck(lib.sdq_qgemm_prequantized(w1, aq.data_ptr(), a_s.data_ptr(), M, H.data_ptr(), b1.data_ptr(),
+                                      None, S.GELU_TANH, sp))
+        mark()
+        ck(lib.sdq_quantize_activations(H.data_ptr(), M, D_FFN, aq.data_ptr(), a_s.data_ptr(), sp))
+        mark()
+        ck(lib.sdq_qgemm_prequantized(w2, aq.data_ptr(), a_s.data_ptr(), M, Y.data_ptr(), b2.data_ptr(),
+                                      None, 0, sp))
+        mark()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    s.sync(sp)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = s.launches()
+    marks_all = []
+    e0, e1 = ev(), ev()
+    t_wall0 = time.time()
+    e0.record(stream)
+    for _ in range(args.steps):
+        m = []
+        step(m)
+        marks_all.append(m)
+    e1.record(stream)
+    barrier()
+    t_wall1 = time.time()
+    launches = s.launches() - launches0
+    s.sync(sp)                                   # also surfaces a device-side timeout
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+
+    # per-kernel durations (mean over the timed steps), from the events inside the region
+    names = ["act_quant_k3072", "gemm_up_3072x14336", "act_quant_k14336", "gemm_down_14336x3072"]
+    kern_ms = {n: float(np.mean([m[i].elapsed_time(m[i + 1]) for m in marks_all])) for i, n in enumerate(names)}
+
+    # ---- end to end through the host-pointer C ABI call: pinned host in, pinned host out
+    e2e = None
+    if not args.no_e2e:
+        hA = torch.empty(M, D_MODEL, dtype=torch.float32, pin_memory=True)
+        hA.copy_(A)
+        hY = torch.empty(M, D_MODEL, dtype=torch.float32, pin_memory=True)
+
+        def e2e_step():
+            ck(lib.sdq_qgemm(w1, hA.data_ptr(), M, H.data_ptr(), b1.data_ptr(), S.A_HOST | S.GELU_TANH, sp))
+            ck(lib.sdq_qgemm(w2, H.data_ptr(), M, hY.data_ptr(), b2.data_ptr(), S.OUT_HOST, sp))
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        a0, a1 = ev(), ev()
+        a0.record(stream)
+        for _ in range(n_e2e):
+            e2e_step()
+        a1.record(stream)
+        barrier()
+        te = torch.tensor([a0.elapsed_time(a1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te.item()) / n_e2e
+        e2e = {"value": ffn_ops(M) * world / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
+               "h2d_bytes_per_step": 4 * M * D_MODEL, "d2h_bytes_per_step": 4 * M * D_MODEL,
+               "ms_per_step": e2e_ms, "steps": n_e2e}
+        assert torch.isfinite(hY).all()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    pk, pk_kind = peaks()
+    dom = "gemm_up_3072x14336"
+    dom_ops = 2.0 * M * D_MODEL * D_FFN
+    achieved = dom_ops / (kern_ms[dom] * 1e-3) / 1e12
+    peak = float(pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    roofline = {"bound": "tensor", "kernel": "qgemm_tc_kernel<256> " + dom, "achieved": achieved, "peak": peak,
+                "unit": "TFLOP/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                "peak_kind": "dense bf16 sustained, of " + pk_kind + " (no int8 figure is measured on this pool)",
+                "frac_of_nominal_int8_4500": achieved / INT8_NOMINAL_TOPS,
+                "algorithmic_bytes": gemm_bytes(M, D_MODEL, D_FFN),
+                "kernel_ms": kern_ms,
+                "hbm_frac_act_quant_k14336": (5.0 * M * D_FFN + 4 * M) / (kern_ms["act_quant_k14336"] * 1e-3) / 1e9
+                / float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        hostA, hw1, hw2, hb1, hb2 = host_problem(2048)
+        tp, kind, cores = reference_throughput(hostA, hw1, hw2, hb1, hb2, 64)
+        rows = int(max(64, min(2048, 64 * 12.0 / tp)))       # about 12 s of CPU work
+        rows -= rows % 8
+        tt, kind, cores = reference_throughput(hostA, hw1, hw2, hb1, hb2, rows)
+        cpu = {"value": ffn_ops(rows) / tt / 1e12, "unit": "TOPS", "cores": cores, "kind": kind,
+               "sample": "FFN pair on %d of %d rows, one pass, reference sd::qgemm on all host threads" % (rows, M)}
+
+    value = ffn_ops(M) * world / (ms_step * 1e-3) / 1e12
+    line = {"metric": "int8_qgemm_throughput", "value": value, "unit": "TOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8",
+            "data": "synthetic",
+            "config": {"workload": "ffn_pair_720p", "rows_per_gpu": M, "k_n": [D_MODEL, D_FFN],
+                       "parallelism": "rows sharded x%d, weights replicated, no collective" % world,
+                       "l2": "inputs larger than L2 (A 335 MB, intermediate 1.56 GB per GPU)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
+            "cpu_baseline": cpu}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    sys.exit(run_reference(a) if a.impl == "reference" else run_b200(a))

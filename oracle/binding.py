@@ -85,14 +85,14 @@ class Oracle:
         self.lib.orc_qgemm(_ptr(A), _ptr(Bq), _ptr(bs), i64(M), i64(N), i64(K), _ptr(out))
         return out
 
-    def bias_add(self, y, b):
-        y = np.array(y, dtype=np.float32, order="C", copy=True)
+    def bias_add(self, y, b, inplace=False):
+        y = y if inplace else np.array(y, dtype=np.float32, order="C", copy=True)
         b = _c(b, np.float32)
         self.lib.orc_bias_add(_ptr(y), _ptr(b), i64(y.shape[0]), i64(y.shape[1]))
         return y
 
-    def gelu_tanh(self, x):
-        x = np.array(x, dtype=np.float32, order="C", copy=True)
+    def gelu_tanh(self, x, inplace=False):
+        x = x if inplace else np.array(x, dtype=np.float32, order="C", copy=True)
         self.lib.orc_gelu_tanh(_ptr(x), i64(x.size))
         return x
 

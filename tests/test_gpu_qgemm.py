@@ -1,0 +1,150 @@
+"""GPU: sd::qgemm through the C ABI is bit-identical to the reference.
+
+Small cases are compared whole against the golden fixtures (outputs of the
+reference's own compiled sd::qgemm) and the oracle; BASELINE-sized cases are
+compared on sampled rows (rows are independent) and through size-independent
+properties: row-split and column-split invariance, row permutation.
+Tolerance: 0 (bit-exact) for int8 bytes, int32 accumulators and fp32 outputs;
+1e-3 max-abs/max-abs for the fused GELU epilogue (stated where used).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from util import bits_equal, cosine, max_rel_err, packed_weights, sha, weights_bf16
+
+pytestmark = pytest.mark.gpu
+
+GELU_TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def gold(golden_dir):
+    return json.load(open(os.path.join(golden_dir, "golden.json")))
+
+
+def test_golden_small_cases(sdq, golden_dir):
+    z = np.load(os.path.join(golden_dir, "qgemm_small.npz"))
+    for tag in ("m17k31n13", "m64k256n128", "m130k96n200"):
+        w = sdq.weight_upload(z[tag + "_Bq"], z[tag + "_bs"])
+        out = sdq.qgemm_host(w, z[tag + "_A"])
+        assert bits_equal(out, z[tag + "_out"]), tag
+        out = sdq.qgemm_host(w, z[tag + "_A"], force_simt=True)
+        assert bits_equal(out, z[tag + "_out"]), tag + " (simt)"
+        sdq.weight_release(w)
+
+
+def test_golden_digests(sdq, oracle, gold):
+    """config 1 (M=192, K=N=3072), both sides of the reference's M>=2048 branch, FFN-up slice."""
+    for tag, d in gold["qgemm_digests"].items():
+        rng = np.random.default_rng(d["seed"])
+        A = (rng.standard_normal((d["M"], d["K"])) * d["a_mul"]).astype(np.float32)
+        wq, ws = oracle.quant_rows_packer(oracle.bf16_to_f32(weights_bf16(rng, d["N"], d["K"], oracle)))
+        assert sha(A) == d["A_sha256"] and sha(wq) == d["Bq_sha256"]
+        w = sdq.weight_upload(wq, ws)
+        out = sdq.qgemm_host(w, A)
+        assert sha(out) == d["out_sha256"], tag
+        sdq.weight_release(w)
+
+
+@pytest.mark.parametrize("M,K,N", [
+    (1, 16, 1), (1, 256, 3072), (5, 48, 36), (128, 128, 256), (129, 144, 257), (192, 3072, 3072),
+    (200, 512, 384), (256, 1024, 192), (300, 272, 1000), (1000, 64, 4100), (2048, 512, 256),
+    (2500, 3072, 192), (4096, 256, 3072), (19072, 128, 512), (512, 4096, 3072),
+])
+def test_intermediates_match_oracle(sdq, oracle, M, K, N):
+    """aq, a_scale, int32 accumulators and fp32 outputs, all exact, over every tile width."""
+    rng = np.random.default_rng(M * 7 + K * 3 + N)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    wq, ws = packed_weights(rng, N, K, oracle)
+    w = sdq.weight_upload(wq, ws)
+    aq, a_s, acc, out = sdq.qgemm_debug(w, A)
+    aq_c, as_c = oracle.act_quant_rows(A)
+    acc_c = oracle.dot_s32(aq_c, wq)
+    assert bits_equal(aq, aq_c) and bits_equal(a_s, as_c)
+    assert bits_equal(acc, acc_c)
+    assert bits_equal(out, oracle.rescale(acc_c, as_c, ws))
+    sdq.weight_release(w)
+
+
+def test_extreme_accumulators(sdq, oracle):
+    """+-127 everywhere: the largest sums the path can see at the widest DiT K."""
+    K, N, M = 14336, 64, 130
+    A = np.full((M, K), 1.0, np.float32)
+    A[1::2] *= -1
+    wq = np.full((N, K), 127, np.int8)
+    wq[::3] = -127
+    ws = np.full((N,), 1e-3, np.float32)
+    w = sdq.weight_upload(wq, ws)
+    _, _, acc, out = sdq.qgemm_debug(w, A)
+    assert int(np.abs(acc).max()) == 127 * 127 * K
+    assert bits_equal(out, oracle.qgemm(A, wq, ws))
+    sdq.weight_release(w)
+
+
+def test_bias_and_gelu_epilogue(sdq, oracle):
+    rng = np.random.default_rng(21)
+    M, K, N = 300, 512, 640
+    A = (rng.standard_normal((M, K)) * 0.5).astype(np.float32)
+    wq, ws = packed_weights(rng, N, K, oracle)
+    b = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    w = sdq.weight_upload(wq, ws)
+    y = oracle.qgemm(A, wq, ws)
+    yb = oracle.bias_add(y, b)
+    # bias: one IEEE add after the rescale, as the reference's separate pass does -> exact
+    assert bits_equal(sdq.qgemm_host(w, A, bias=b), yb)
+    assert bits_equal(sdq.qgemm_host(w, A, bias=b, force_simt=True), yb)
+    # GELU: tanh is not bit-reproducible across libms; tolerance 1e-3 of the output's max
+    g = sdq.qgemm_host(w, A, bias=b, gelu=True)
+    assert max_rel_err(g, oracle.gelu_tanh(yb)) < GELU_TOL
+    assert max_rel_err(sdq.qgemm_host(w, A, gelu=True), oracle.gelu_tanh(y)) < GELU_TOL
+    sdq.weight_release(w)
+
+
+def test_empty_and_bad_arguments(sdq, pkg, oracle):
+    rng = np.random.default_rng(1)
+    wq, ws = packed_weights(rng, 32, 64, oracle)
+    w = sdq.weight_upload(wq, ws)
+    assert sdq.qgemm_host(w, np.zeros((0, 64), np.float32)).shape == (0, 32)   # M == 0: no-op
+    with pytest.raises(pkg.SdqError) as e:
+        sdq.qgemm(12345, None, 4, None)
+    assert e.value.code == 1 and "handle" in e.value.msg
+    with pytest.raises(pkg.SdqError):
+        sdq.qgemm(w, None, 4, None)
+    with pytest.raises(pkg.SdqError):
+        sdq.weight_upload(np.zeros((0, 8), np.int8), np.zeros((0,), np.float32))
+    sdq.weight_release(w)
+    with pytest.raises(pkg.SdqError):
+        sdq.weight_info(w)
+
+
+def test_weight_registry_lookup(sdq, pkg, oracle):
+    """The reference's caller only has the host pointer of the int8 view in hand."""
+    rng = np.random.default_rng(4)
+    wq, ws = packed_weights(rng, 48, 96, oracle)
+    w = sdq.weight_upload(wq, ws)
+    assert sdq.weight_lookup(wq.ctypes.data) == w
+    N, K, qp, sp = sdq.weight_info(w)
+    assert (N, K) == (48, 96) and qp % 256 == 0 and sp % 256 == 0
+    sdq.weight_release(w)
+    with pytest.raises(pkg.SdqError) as e:
+        sdq.weight_lookup(wq.ctypes.data)
+    assert e.value.code == 7
+
+
+def test_reference_gate_cosine(sdq, oracle):
+    """The reference's own acceptance test: cosine > 0.999 vs fp32 matmul on dequantized
+    weights at (17,31,13) and (64,1024,512)  (tests/test_core.cpp:93-118)."""
+    rng = np.random.default_rng(9)
+    for (M, K, N) in [(17, 31, 13), (64, 1024, 512)]:
+        A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+        W = rng.uniform(-1, 1, (N, K)).astype(np.float32)
+        wq, ws = oracle.quantize_rowwise(W)
+        w = sdq.weight_upload(wq, ws)
+        out = sdq.qgemm_host(w, A)
+        ref = A @ (wq.astype(np.float32) * ws[:, None]).T
+        assert cosine(out, ref) > 0.999
+        assert np.isfinite(out).all() and out.shape == (M, N)
+        sdq.weight_release(w)

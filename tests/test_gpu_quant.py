@@ -1,0 +1,119 @@
+"""GPU: the row quantization kernels are bit-identical to the oracle and the golden fixtures.
+
+Everything goes through the C ABI (sdq_quantize_activations, sdq_quantize_rows,
+sdq_dequant_rows).
+"""
+import os
+
+import numpy as np
+import pytest
+
+from util import bits_equal, weights_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,K", [(1, 4), (17, 31), (3, 33), (64, 256), (192, 3072), (130, 4100),
+                                 (9, 14336), (5, 18432), (4, 20000), (300, 1000)])
+def test_activation_quant_matches_oracle(sdq, oracle, M, K):
+    rng = np.random.default_rng(M * 100003 + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    if M > 2:
+        A[1, :] = 0.0                      # zero row: scale 1, bytes 0
+        A[2, :] *= 1e-30                   # tiny values
+    aq, a_s = sdq.quantize_activations(A)
+    aq_c, as_c = oracle.act_quant_rows(A)
+    assert bits_equal(a_s, as_c)
+    assert bits_equal(aq, aq_c)
+
+
+def test_activation_quant_ties_and_nonfinite(sdq, oracle):
+    A = np.zeros((6, 64), np.float32)
+    A[0, 0] = 127.0
+    A[0, 1:9] = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5, -126.5]   # exact .5 after scaling
+    A[1, :] = 1.0
+    A[1, 3] = np.nan
+    A[2, :] = 2.0
+    A[2, 5] = np.inf
+    A[3, :] = 1e-45
+    A[4, :] = -3.0
+    A[4, 7] = -np.inf
+    A[5, :] = np.float32(3.4e38)
+    aq, a_s = sdq.quantize_activations(A)
+    aq_c, as_c = oracle.act_quant_rows(A)
+    assert bits_equal(a_s, as_c)
+    assert bits_equal(aq, aq_c)
+    assert list(aq[0, 1:9]) == [0, 2, 2, 0, -2, -2, 126, -126]      # round half to even
+
+
+def test_activation_quant_large_rows_sampled(sdq, oracle):
+    # the 720p token count at both DiT widths; the oracle checks a sample of rows
+    rng = np.random.default_rng(5)
+    for K in (3072, 14336):
+        M = 27280 if K == 3072 else 4096
+        A = rng.standard_normal((M, K)).astype(np.float32)
+        aq, a_s = sdq.quantize_activations(A)
+        rows = rng.choice(M, 512, replace=False)
+        aq_c, as_c = oracle.act_quant_rows(A[rows])
+        assert bits_equal(a_s[rows], as_c)
+        assert bits_equal(aq[rows], aq_c)
+        assert int(np.abs(aq).max()) == 127
+
+
+def test_packer_rows_match_golden(sdq, pkg, golden_dir):
+    z = np.load(os.path.join(golden_dir, "packer_rows.npz"))
+    for tag in ("w64x256", "w33x1000", "w8x7"):
+        q, s = sdq.quantize_rows(z[tag + "_bf16"], pkg.sdq.BF16, pkg.sdq.MODE_PACKER)
+        assert bits_equal(q, z[tag + "_q"]), tag
+        assert bits_equal(s, z[tag + "_scale"]), tag
+    q, s = sdq.quantize_rows(z["ties_f32"], pkg.sdq.F32, pkg.sdq.MODE_PACKER)
+    assert bits_equal(q, z["ties_q"]) and bits_equal(s, z["ties_scale"])
+    q, s = sdq.quantize_rows(z["h16x512_f16"], pkg.sdq.F16, pkg.sdq.MODE_PACKER)
+    assert bits_equal(q, z["h16x512_q"]) and bits_equal(s, z["h16x512_scale"])
+
+
+@pytest.mark.parametrize("rows,last", [(3072, 3072), (1000, 14336), (8192, 7), (3072 * 48, 2),
+                                       (257, 65), (5, 64)])
+def test_packer_rows_match_oracle(sdq, pkg, oracle, rows, last):
+    rng = np.random.default_rng(rows + last)
+    bits = weights_bf16(rng, rows, last, oracle)
+    bits[0, :] = 0
+    q, s = sdq.quantize_rows(bits, pkg.sdq.BF16, pkg.sdq.MODE_PACKER)
+    q_c, s_c = oracle.quant_rows_packer(oracle.bf16_to_f32(bits))
+    assert bits_equal(s, s_c)
+    assert bits_equal(q, q_c)
+
+
+def test_rowwise_matches_golden_and_oracle(sdq, pkg, oracle, golden_dir):
+    z = np.load(os.path.join(golden_dir, "qgemm_small.npz"))
+    q, s = sdq.quantize_rows(z["rowwise_W"], pkg.sdq.F32, pkg.sdq.MODE_ROWWISE)
+    assert bits_equal(q, z["rowwise_q"]) and bits_equal(s, z["rowwise_scale"])
+    rng = np.random.default_rng(8)
+    W = rng.uniform(-1, 1, (512, 3072)).astype(np.float32)
+    W[:, 1] = np.float32(0.5) * np.abs(W).max(axis=1) / np.float32(127.0) * 3   # near-tie values
+    q, s = sdq.quantize_rows(W, pkg.sdq.F32, pkg.sdq.MODE_ROWWISE)
+    q_c, s_c = oracle.quantize_rowwise(W)
+    assert bits_equal(q, q_c) and bits_equal(s, s_c)
+    # the two recipes really differ (half-away vs half-even, divide vs multiply)
+    t = np.zeros((1, 64), np.float32)
+    t[0, 0], t[0, 1] = 127.0, 0.5
+    qa, _ = sdq.quantize_rows(t, pkg.sdq.F32, pkg.sdq.MODE_ROWWISE)
+    qb, _ = sdq.quantize_rows(t, pkg.sdq.F32, pkg.sdq.MODE_PACKER)
+    assert qa[0, 1] == 1 and qb[0, 1] == 0
+
+
+def test_rowwise_rejects_non_f32(sdq, pkg):
+    with pytest.raises(pkg.SdqError) as e:
+        sdq.quantize_rows(np.zeros((2, 8), np.uint16), pkg.sdq.BF16, pkg.sdq.MODE_ROWWISE)
+    assert e.value.code == 1
+
+
+def test_dequant_rows(sdq, oracle):
+    rng = np.random.default_rng(2)
+    q = rng.integers(-127, 128, (100, 77)).astype(np.int8)
+    s = rng.uniform(1e-4, 1e-2, 100).astype(np.float32)
+    assert bits_equal(sdq.dequant_rows(q, s), oracle.dequant_rows(q, s))
+    # the reference's own gate for the weight quantizer: |w - q*s| < 1 scale unit
+    W = rng.uniform(-1, 1, (37, 513)).astype(np.float32)
+    qq, ss = sdq.quantize_rows(W, 0, 1)
+    assert np.all(np.abs(sdq.dequant_rows(qq, ss) - W) < ss[:, None])
