@@ -4,14 +4,17 @@
 
 namespace sdq {
 
-// GELU, tanh form (reference src/model/ovi_dit.cpp:132-142).  tanh(u) is
-// evaluated as 1 - 2/(1+exp(2u)); it agrees with libm's tanhf to ~1e-6
-// absolute, far inside the 1e-3 bound this fused activation is held to (the
-// CPU's own std::tanh is not bit-reproducible across libms either).
+// GELU, tanh form (reference src/model/ovi_dit.cpp:132-142):
+//   0.5 v (1 + tanh(u)),  u = 0.79788456 (v + 0.044715 v^3).
+// Since 0.5 (1 + tanh(u)) = 1 / (1 + exp(-2u)), it is evaluated as v * rcp(1 + ex2(-2u log2 e))
+// with the hardware ex2/rcp approximations: ~1e-6 absolute from libm's tanhf, far inside
+// the 1e-3 bound this fused activation is held to (the CPU's own std::tanh is not
+// bit-reproducible across libms either).
 __device__ __forceinline__ float gelu_tanh(float v) {
-  const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-  const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
-  return 0.5f * v * (1.0f + t);
+  const float p = fmaf(0.044715f * v * v, v, v);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(p * (-2.0f * 0.7978845608028654f * 1.4426950408889634f)));
+  return __fdividef(v, 1.0f + e);
 }
 
 // out = (float)acc * (a_scale * b_scale)   (reference src/core/qgemm.cpp:123-124,135):

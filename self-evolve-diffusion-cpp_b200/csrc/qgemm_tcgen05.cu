@@ -7,15 +7,16 @@
 // Both operands are K-major ("TN"): aq is [M,K] row-major, bq is the .sdcpp
 // weight [N,K] row-major as stored in the file -- no repack.
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0, one lane : TMA producer.  Per k-block it loads a 128 x 128 B tile
 //                      of aq and a BLOCK_N x 128 B tile of bq (SWIZZLE_128B)
 //                      into a ring of shared-memory stages.
 //   warp 1, one lane : MMA issuer.  4 x tcgen05.mma (M=128, N=BLOCK_N, K=32)
 //                      per stage into one of two TMEM accumulator buffers;
 //                      tcgen05.commit releases the stage / publishes the tile.
-//   warps 2..5       : epilogue.  tcgen05.ld the finished accumulator (each warp
-//                      owns the 32 TMEM lanes of its quarter), rescale, store.
+//   warps 2..9       : epilogue.  tcgen05.ld the finished accumulator (two warps
+//                      per 32-lane TMEM quarter, alternate 32-column chunks),
+//                      rescale, stage in shared memory, bulk tensor store.
 //                      The second TMEM buffer lets tile t's epilogue overlap
 //                      tile t+1's main loop.
 // Integer accumulation is exact and order-free, so any tiling gives the
@@ -37,7 +38,7 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;  // int8 elements = bytes: one 128-byte swizzle row
 constexpr int UMMA_K = 32;    // K of one kind::i8 instruction
-constexpr int kNumThreads = 192;
+constexpr int kNumThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 template <int BLOCK_N>
@@ -48,7 +49,9 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BLOCK_N;  // two accumulator buffers; a power of two >= 32
   // stages + barriers/bookkeeping + slack to realign the dynamic base to 1024 B
-  static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
+  // epilogue staging: per epilogue warp one 32x32 fp32 box (4 KiB) for TMA stores
+  static constexpr int kStagingBytes = 8 * 4096;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 256 + 1024;
   // instruction descriptor: D=s32 (2<<4), A=s8 (1<<7), B=s8 (1<<10), both K-major,
   // N>>3 at bit 17, M>>4 at bit 24
   static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) |
@@ -115,6 +118,29 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+// Bulk tensor store of a 32x32 fp32 box from shared memory; rows/columns outside the
+// tensor are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -187,11 +213,36 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return d;
 }
 
+// 32 consecutive outputs of one row: rescale (+bias) (+GELU), compile-time specialised.
+template <bool BIAS, bool GELU>
+__device__ __forceinline__ void chunk_values(const uint32_t (&r)[32], float a_s,
+                                             const float* __restrict__ b_scale,
+                                             const float* __restrict__ bias, int64_t nc, int64_t N,
+                                             float (&o)[32]) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    float4 bs = make_float4(0.f, 0.f, 0.f, 0.f), bb = bs;
+    if (nc + j < N) {  // N % 4 == 0 on this path: a group of 4 is wholly inside or outside
+      bs = __ldg(reinterpret_cast<const float4*>(b_scale + nc + j));
+      if (BIAS) bb = __ldg(reinterpret_cast<const float4*>(bias + nc + j));
+    }
+    const float sc[4] = {bs.x, bs.y, bs.z, bs.w}, bi[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      float v = rescale((int)r[j + t], a_s, sc[t]);
+      if (BIAS) v = __fadd_rn(v, bi[t]);
+      if (GELU) v = gelu_tanh(v);
+      o[j + t] = v;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- the kernel
 template <int BLOCK_N>
 __global__ void __launch_bounds__(kNumThreads, 1)
     qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, GemmArgs g) {
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_out, int use_tma_store, GemmArgs g) {
   using C = Cfg<BLOCK_N>;
   extern __shared__ uint8_t smem_raw[];
   // SWIZZLE_128B atoms (8 rows x 128 B) must start on 1024-byte boundaries.
@@ -201,7 +252,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   const uint32_t smem_a = base;
   const uint32_t smem_b = base + C::kStages * C::kABytes;
-  uint8_t* book = smem + C::kStages * C::kStageBytes;
+  const uint32_t smem_staging = base + C::kStages * C::kStageBytes;
+  uint8_t* book = smem + C::kStages * C::kStageBytes + C::kStagingBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(book);
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   const uint32_t bar_full = smem_u32(bars);
@@ -224,13 +276,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, 4);  // one arrival per epilogue warp
+      mbar_init(bar_tempty + 8 * b, 8);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
+    if (use_tma_store) prefetch_tmap(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
@@ -291,10 +344,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       }
     }
   } else {
-    // -------------------------------------------------- epilogue (4 warps)
-    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
-    const bool gelu = (g.flags & SDQ_GELU_TANH) != 0;
-    const bool vec_ok = (g.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0);
+    // -------------------------------------------------- epilogue (8 warps)
+    // Two warps share each TMEM lane quarter (a warp may only read lanes 32*(warp%4)..+31)
+    // and take alternate 32-column chunks of the accumulator.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int mode = (g.bias ? 1 : 0) | ((g.flags & SDQ_GELU_TANH) ? 2 : 0);
+    const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
     uint32_t abuf = 0, aphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
@@ -304,45 +360,46 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int64_t row = (int64_t)m_blk * BLOCK_M + quarter * 32 + lane;
+      const int64_t row0 = (int64_t)m_blk * BLOCK_M + quarter * 32;
+      const int64_t row = row0 + lane;
       const bool row_ok = row < g.M;
       const float a_s = row_ok ? g.a_scale[row] : 0.0f;
-      float* out_row = g.out + row * g.N;
-      int32_t* dump_row = g.acc_dump ? g.acc_dump + row * g.N : nullptr;
       const int64_t n0 = (int64_t)n_blk * BLOCK_N;
+      if (row0 < g.M) {  // warp-uniform: this warp's 32 rows are not all past the end
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; c++) {
-        const int64_t nc = n0 + c * 32;
-        if (nc >= g.N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + abuf * BLOCK_N + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
-        tmem_ld_wait();
-        if (row_ok) {
-          if (vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (nc + j < g.N) {  // N % 4 == 0: a group of 4 is wholly inside or outside
-                const float4 bs = __ldg(reinterpret_cast<const float4*>(g.b_scale + nc + j));
-                float4 o;
-                if (g.bias) {
-                  const float4 bb = __ldg(reinterpret_cast<const float4*>(g.bias + nc + j));
-                  o.x = epilogue_value((int)r[j + 0], a_s, bs.x, &bb.x, gelu);
-                  o.y = epilogue_value((int)r[j + 1], a_s, bs.y, &bb.y, gelu);
-                  o.z = epilogue_value((int)r[j + 2], a_s, bs.z, &bb.z, gelu);
-                  o.w = epilogue_value((int)r[j + 3], a_s, bs.w, &bb.w, gelu);
-                } else {
-                  o.x = epilogue_value((int)r[j + 0], a_s, bs.x, nullptr, gelu);
-                  o.y = epilogue_value((int)r[j + 1], a_s, bs.y, nullptr, gelu);
-                  o.z = epilogue_value((int)r[j + 2], a_s, bs.z, nullptr, gelu);
-                  o.w = epilogue_value((int)r[j + 3], a_s, bs.w, nullptr, gelu);
-                }
-                *reinterpret_cast<float4*>(out_row + nc + j) = o;
-                if (dump_row)
-                  *reinterpret_cast<int4*>(dump_row + nc + j) =
-                      make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
-              }
+        for (int c = half; c < BLOCK_N / 32; c += 2) {
+          const int64_t nc = n0 + c * 32;
+          if (nc >= g.N) break;  // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + abuf * BLOCK_N + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+          tmem_ld_wait();
+          if (use_tma_store) {
+            float o[32];
+            switch (mode) {
+              case 0: chunk_values<false, false>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
+              case 1: chunk_values<true, false>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
+              case 2: chunk_values<false, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
+              default: chunk_values<true, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
             }
-          } else {
+            // The values go through a swizzled 32x32 fp32 box in shared memory; one bulk
+            // tensor store then writes full 128-byte lines and clips rows >= M, columns >= N.
+            if (lane == 0) bulk_wait_read<0>();  // the previous store has finished reading the box
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)  // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+              st_shared_v4(box + (uint32_t)(lane * 128 + (((j >> 2) ^ (lane & 7)) << 4)),
+                           make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]));
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_out, box, (int)nc, (int)row0);
+              bulk_commit();
+            }
+          } else if (row_ok) {
+            // per-thread stores: odd N, unaligned out, or the accumulator dump is wanted
+            float* out_row = g.out + row * g.N;
+            int32_t* dump_row = g.acc_dump ? g.acc_dump + row * g.N : nullptr;
+            const bool gelu = (mode & 2) != 0;
 #pragma unroll
             for (int j = 0; j < 32; j++) {
               if (nc + j < g.N) {
@@ -364,6 +421,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   }
 
   // ---------------------------------------------------- common exit
+  if (warp >= 2 && lane == 0) bulk_wait_read<0>();  // staged boxes fully read by the stores
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -404,16 +462,41 @@ bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int b
   return true;
 }
 
+// out [M,N] fp32 row-major, box = 32 rows x 32 columns (128 bytes), 128-byte swizzle.
+bool make_out_tmap(CUtensorMap* map, float* out, int64_t M, int64_t N, std::string* why) {
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (why) *why = "cuTensorMapEncodeTiled(out) failed with CUresult " + std::to_string((int)r);
+    return false;
+  }
+  return true;
+}
+
 template <int BLOCK_N>
 cudaError_t launch_t(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
   using C = Cfg<BLOCK_N>;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tout;
   if (!make_tmap(&ta, g.aq, g.M, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;
   if (!make_tmap(&tb, g.bq, g.N, g.K, BLOCK_N, why)) return cudaErrorInvalidValue;
+  // Bulk tensor stores need a 16-byte aligned base and row pitch; the accumulator dump
+  // (a debugging aid) and odd N keep the per-thread store path.
+  const int use_tma_store = (g.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0) &&
+                            g.acc_dump == nullptr;
+  if (use_tma_store) {
+    if (!make_out_tmap(&tout, g.out, g.M, g.N, why)) return cudaErrorInvalidValue;
+  } else {
+    tout = ta;  // unused by the kernel
+  }
   const int64_t tiles = ((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + BLOCK_N - 1) / BLOCK_N);
   const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
   count_launch();
-  qgemm_tc_kernel<BLOCK_N><<<grid, kNumThreads, C::kSmemBytes, s>>>(ta, tb, g);
+  qgemm_tc_kernel<BLOCK_N><<<grid, kNumThreads, C::kSmemBytes, s>>>(ta, tb, tout, use_tma_store, g);
   return cudaGetLastError();
 }
 
