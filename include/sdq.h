@@ -139,6 +139,28 @@ SDQ_API int sdq_qgemm_prequantized(sdq_weight_t w, const int8_t* aq_dev, const f
                            int64_t M, float* out_dev, const float* bias_dev,
                            int32_t* acc_dump_dev, uint32_t flags, void* stream);
 
+/* The same computation as sdq_qgemm for callers that cannot allocate device memory
+ * while they run (a host that has given all HBM to its own pool, a plugin inside
+ * another allocator, a section where cudaMalloc's implicit device-wide
+ * synchronisation is not acceptable).  It has no counterpart in the reference,
+ * which runs on the CPU and allocates its scratch with aligned_alloc on every
+ * call.  This entry point calls no cudaMalloc / cudaFree and needs no sdq_init
+ * and no weight handle: the weight is given as device pointers (int8 [N,K] and
+ * fp32 [N]) and the int8 activations and row scales live in a fixed array that is
+ * part of the library image, held on every GPU that loads the library until the
+ * process exits (about 32.1 MiB).  Limits: M <= SDQ_STATIC_MAX_ROWS and
+ * M*K <= SDQ_STATIC_MAX_AQ_BYTES, else SDQ_ERR_INVALID.  All calls on a device
+ * share that array: calls that can overlap on the GPU race; order them (one
+ * stream, or events).  A, out and bias are device memory (SDQ_A_HOST /
+ * SDQ_OUT_HOST are rejected: staging would need an allocation).  The first call
+ * on each device does a one-time host-side set-up; make it before any stream
+ * capture begins. */
+#define SDQ_STATIC_MAX_ROWS 32768
+#define SDQ_STATIC_MAX_AQ_BYTES 33554432
+SDQ_API int sdq_qgemm_static_scratch(const int8_t* wq_dev, const float* w_scale_dev, int64_t N,
+                                     int64_t K, const float* A_dev, int64_t M, float* out_dev,
+                                     const float* bias_dev, uint32_t flags, void* stream);
+
 /* ---- weight quantizers ---- */
 
 /* Quantizes `rows` rows of `last` elements to int8 with one fp32 scale per row.

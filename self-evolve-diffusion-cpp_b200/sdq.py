@@ -19,6 +19,7 @@ SRC_HOST, DST_HOST = 0x1, 0x2
 PACK_UPLOAD = 0x1
 DT_F32, DT_I8 = 0, 2
 ERR_DEVICE_TIMEOUT = 6
+STATIC_MAX_ROWS, STATIC_MAX_AQ_BYTES = 32768, 33554432
 
 
 def lib_path():
@@ -72,6 +73,8 @@ _SIGS = {
     "sdq_quantize_activations": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sdq_qgemm_prequantized": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_qgemm_static_scratch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
+                                           C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_quantize_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_void_p,
                                     C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_dequant_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_uint32, C.c_void_p]),
@@ -287,6 +290,12 @@ class Sdq:
                                                  dacc.ptr, flags, None))
         return (dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,)),
                 dacc.to_numpy(np.int32, (M, N)), dout.to_numpy(np.float32, (M, N)))
+
+    def qgemm_static_scratch(self, wq_ptr, ws_ptr, N, K, A_ptr, M, out_ptr, bias_ptr=None, flags=0,
+                             stream=None):
+        """The no-allocation variant: raw device pointers, scratch inside the library image."""
+        self._ck(self.lib.sdq_qgemm_static_scratch(wq_ptr, ws_ptr, N, K, A_ptr, M, out_ptr, bias_ptr,
+                                                   flags, stream))
 
     # ---- quantizers ----
     def quantize_rows(self, src, src_dtype, mode):
