@@ -119,14 +119,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
-// Bulk tensor store of a 32x32 fp32 box from shared memory; rows/columns outside the
-// tensor are clipped by the hardware.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(src), "r"(x), "r"(y)
-               : "memory");
-}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -141,6 +133,36 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, float4 v) {
   asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
                "f"(v.w)
                : "memory");
+}
+// L2 eviction policies: weights are re-read by every band of row-blocks (keep them),
+// outputs are written once and not read again by this kernel (let them go first).
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                 int x, int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+// Bulk tensor store of a 32x32 fp32 box from shared memory; rows/columns outside the
+// tensor are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, uint32_t src, int x, int y,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::
+          "l"(reinterpret_cast<uint64_t>(map)),
+      "r"(src), "r"(x), "r"(y), "l"(policy)
+      : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -211,6 +233,23 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
   return d;
+}
+
+// Tile order.  Consecutive tile indices (= the tiles the 148 CTAs work on at the same
+// time) walk down a band of kGroupM row-blocks before moving to the next column-block,
+// so a wave touches ~16 A tiles and ~9 B tiles instead of 3 and all of them: each
+// operand tile is fetched from HBM once per band and then served to its other users
+// from L2, and the weight matrix is re-read once per band rather than once per row-block.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_coords(int tile, int num_m_blocks, int num_n_blocks,
+                                            int& m_blk, int& n_blk) {
+  const int per_group = kGroupM * num_n_blocks;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int gsize = min(kGroupM, num_m_blocks - first_m);
+  const int r = tile - group * per_group;
+  m_blk = first_m + r % gsize;
+  n_blk = r / gsize;
 }
 
 // 32 consecutive outputs of one row: rescale (+bias) (+GELU), compile-time specialised.
@@ -297,17 +336,20 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------ TMA producer
+      const uint64_t keep_policy = policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m_blk = tile / num_n_blocks, n_blk = tile % num_n_blocks;
+        int m_blk, n_blk;
+        tile_coords(tile, num_m_blocks, num_n_blocks, m_blk, n_blk);
         for (int kb = 0; kb < num_k_blocks; kb++) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x100 | 1);
           if (!ok) break;
           const uint32_t full = bar_full + 8 * stage;
           mbar_expect_tx(full, C::kStageBytes);
           tma_load_2d(smem_a + stage * C::kABytes, &tmap_a, full, kb * BLOCK_K, m_blk * BLOCK_M);
-          tma_load_2d(smem_b + stage * C::kBBytes, &tmap_b, full, kb * BLOCK_K, n_blk * BLOCK_N);
+          tma_load_2d_hint(smem_b + stage * C::kBBytes, &tmap_b, full, kb * BLOCK_K,
+                           n_blk * BLOCK_N, keep_policy);
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -351,10 +393,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int half = (warp - 2) >> 2;
     const int mode = (g.bias ? 1 : 0) | ((g.flags & SDQ_GELU_TANH) ? 2 : 0);
     const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
+    const uint64_t stream_policy = policy_evict_first();
     uint32_t abuf = 0, aphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const int m_blk = tile / num_n_blocks, n_blk = tile % num_n_blocks;
+      int m_blk, n_blk;
+      tile_coords(tile, num_m_blocks, num_n_blocks, m_blk, n_blk);
       ok = mbar_wait(bar_tfull + 8 * abuf, aphase, abort_flag, g.status, 0x300 | 1);
       // all 32 lanes poll the same barrier, so `ok` is warp-uniform in practice; make it so
       ok = __all_sync(0xffffffffu, ok);
@@ -392,7 +436,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_2d(&tmap_out, box, (int)nc, (int)row0);
+              tma_store_2d_hint(&tmap_out, box, (int)nc, (int)row0, stream_policy);
               bulk_commit();
             }
           } else if (row_ok) {
