@@ -1,0 +1,334 @@
+// The large-problem variant of the tcgen05 int8 GEMM: two CTAs on neighbouring SMs
+// (a cluster of 2) work on one 256 x 256 output tile with tcgen05.mma.cta_group::2.
+//
+// Per k-block each CTA stages only its own 128 rows of aq and its own 128 of the
+// tile's 256 weight rows (32 KiB instead of 48 KiB), and the tensor cores of both SMs
+// read the weight halves from both shared memories.  That cuts the L2->SM and the
+// shared-memory traffic per MMA by a third and leaves room for 6 pipeline stages,
+// which is what the 1-CTA kernel is short of at the int8 rate.
+//
+//   CTA rank r of the pair:  rows  m_pair*256 + r*128 .. +127   (its A half, its D rows)
+//                            weight rows n_blk*256 + r*128 .. +127 (its B half)
+//   leader (rank 0), one lane: issues every MMA; tcgen05.commit with a 2-CTA multicast
+//                            releases a stage / publishes the accumulator in both CTAs
+//   both CTAs' TMA lanes   : complete_tx on the LEADER's "full" barrier
+//   both CTAs' epilogue    : read their own TMEM (128 lanes x 256 columns), store their
+//                            own 128 rows, arrive on the LEADER's "tmem empty" barrier
+// No TMA multicast is used.  Every wait is bounded as in the 1-CTA kernel, and the two
+// CTAs leave through a cluster barrier so that neither frees shared or tensor memory
+// the other may still signal.
+#include <cstdio>
+#include <cstdlib>
+
+#include "tc_common.cuh"
+
+namespace sdq {
+namespace {
+using namespace tc;
+
+constexpr int kBlockN2 = 256;
+constexpr int kStages2 = 6;
+constexpr int kHalfBytes = BLOCK_M * BLOCK_K;         // 16 KiB: 128 rows x 128 B
+constexpr int kStageBytes2 = 2 * kHalfBytes;          // per CTA: A half + B half
+constexpr int kStagingBytes2 = 8 * 4096;
+constexpr int kTmemCols2 = 2 * kBlockN2;
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + kStagingBytes2 + 256 + 1024;
+// D=s32, A=B=s8, K-major both, N=256 (>>3 at bit 17), M=256 (>>4 at bit 24)
+constexpr uint32_t kIdesc2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN2 >> 3) << 17) |
+                             ((uint32_t)(256 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address, in the cluster-wide shared window, of CTA `rank`'s copy of a shared variable.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// 2-CTA form of the tiled load: the destination is this CTA's shared memory, the
+// mbarrier may live in the partner CTA (cluster-window address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster, int x, int y,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once
+// the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar),
+      "h"((uint16_t)3)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kNumThreads, 1)
+    qgemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                     const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_out, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // same offset in both CTAs of the pair
+  uint8_t* smem = smem_raw + (base - raw);
+
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = base + kStages2 * kHalfBytes;
+  const uint32_t smem_staging = base + kStages2 * kStageBytes2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes2 + kStagingBytes2);
+  const uint32_t bar_full = smem_u32(bars);            // used in the leader only
+  const uint32_t bar_empty = bar_full + 8 * kStages2;  // one per CTA, signalled by multicast commit
+  const uint32_t bar_tfull = bar_empty + 8 * kStages2; // one per CTA, multicast commit
+  const uint32_t bar_tempty = bar_tfull + 16;          // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages2 + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int num_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+  const int num_m_pairs = (int)((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M));
+  const int num_n_blocks = (int)((g.N + kBlockN2 - 1) / kBlockN2);
+  const int num_k_blocks = (int)((g.K + BLOCK_K - 1) / BLOCK_K);
+  const int num_tiles = num_m_pairs * num_n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; s++) {
+      mbar_init(bar_full + 8 * s, 1);   // the leader's producer arrives once (+ both CTAs' bytes)
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 16);  // 8 epilogue warps in each of the two CTAs
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_out);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols2);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------ TMA producer (both CTAs)
+      const uint64_t keep_policy = policy_evict_last();
+      const uint64_t normal_policy = policy_evict_normal();
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+        int m_pair, n_blk;
+        tile_coords_g(tile, num_m_pairs, num_n_blocks, kGroupM / 2, m_pair, n_blk);
+        const int row0 = (m_pair * 2 + (int)rank) * BLOCK_M;
+        const int wrow0 = n_blk * kBlockN2 + (int)rank * BLOCK_M;
+        for (int kb = 0; kb < num_k_blocks; kb++) {
+          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x1100 | 1);
+          if (!ok) break;
+          const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
+          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes2);
+          tma_load_2d_pair(smem_a + stage * kHalfBytes, &tmap_a, full_leader, kb * BLOCK_K, row0,
+                           normal_policy);
+          tma_load_2d_pair(smem_b + stage * kHalfBytes, &tmap_b, full_leader, kb * BLOCK_K, wrow0,
+                           keep_policy);
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ------------------------------------------------ MMA issuer (leader CTA only)
+      uint32_t stage = 0, phase = 0, abuf = 0, aphase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+        ok = mbar_wait(bar_tempty + 8 * abuf, aphase ^ 1u, abort_flag, g.status, 0x1200 | 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + abuf * kBlockN2;
+        for (int kb = 0; kb < num_k_blocks; kb++) {
+          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x1200 | 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_a + stage * kHalfBytes);
+          const uint64_t bdesc = make_smem_desc(smem_b + stage * kHalfBytes);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+            umma_i8_pair(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)),
+                         bdesc + (uint64_t)(k * (UMMA_K >> 4)), kIdesc2, (uint32_t)((kb | k) != 0));
+          umma_commit_pair(bar_empty + 8 * stage);
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_pair(bar_tfull + 8 * abuf);
+        abuf ^= 1u;
+        if (abuf == 0) aphase ^= 1u;
+      }
+    }
+  } else {
+    // -------------------------------------------------- epilogue (8 warps, both CTAs)
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int mode = (g.bias ? 1 : 0) | ((g.flags & SDQ_GELU_TANH) ? 2 : 0);
+    const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
+    const uint64_t stream_policy = policy_evict_first();
+    const uint32_t tempty_leader0 = map_to_cta(bar_tempty, 0);
+    uint32_t abuf = 0, aphase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+      int m_pair, n_blk;
+      tile_coords_g(tile, num_m_pairs, num_n_blocks, kGroupM / 2, m_pair, n_blk);
+      ok = mbar_wait_warp(bar_tfull + 8 * abuf, aphase, abort_flag, g.status, 0x1300 | 1);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row0 = (int64_t)(m_pair * 2 + (int)rank) * BLOCK_M + quarter * 32;
+      const int64_t row = row0 + lane;
+      const float a_s = row < g.M ? g.a_scale[row] : 0.0f;
+      const int64_t n0 = (int64_t)n_blk * kBlockN2;
+      if (row0 < g.M) {
+#pragma unroll 1
+        for (int c = half; c < kBlockN2 / 32; c += 2) {
+          const int64_t nc = n0 + c * 32;
+          if (nc >= g.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + abuf * kBlockN2 + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+          tmem_ld_wait();
+          float o[32];
+          switch (mode) {
+            case 0: chunk_values<false, false>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
+            case 1: chunk_values<true, false>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
+            case 2: chunk_values<false, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
+            default: chunk_values<true, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
+          }
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            st_shared_v4(box + (uint32_t)(lane * 128 + (((j >> 2) ^ (lane & 7)) << 4)),
+                         make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]));
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d_hint(&tmap_out, box, (int)nc, (int)row0, stream_policy);
+            bulk_commit();
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * abuf);
+      abuf ^= 1u;
+      if (abuf == 0) aphase ^= 1u;
+    }
+  }
+
+  // ---------------------------------------------------- common exit
+  if (warp >= 2 && lane == 0) bulk_wait_read<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);  // let bulk copies in flight land (~1 ms)
+    __syncthreads();
+  }
+  // Neither CTA may release its shared / tensor memory while the partner can still signal it.
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, kTmemCols2);
+  }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- host side
+int qgemm_tc2_setup(std::string* why) {
+  cudaError_t a = cudaFuncSetAttribute(qgemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemBytes2);
+  if (a != cudaSuccess) {
+    if (why) *why = std::string("cudaFuncSetAttribute(2-CTA GEMM, max dynamic smem): ") + cudaGetErrorString(a);
+    return SDQ_ERR_CUDA;
+  }
+  return SDQ_OK;
+}
+
+// The pair kernel stores only through bulk tensor stores (N % 4 == 0, 16-byte aligned
+// out, no accumulator dump) and pays off once every cluster has at least one tile.
+bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count) {
+  static const int forced = [] {
+    const char* v = getenv("SDQ_TC_VARIANT");  // "1": never, "2": whenever possible
+    return v ? atoi(v) : 0;
+  }();
+  if (forced == 1) return false;
+  if (g.N % 4 != 0 || (reinterpret_cast<uintptr_t>(g.out) & 15) != 0 || g.acc_dump) return false;
+  const int64_t tiles = ((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((g.N + kBlockN2 - 1) / kBlockN2);
+  if (forced == 2) return true;
+  return tiles >= sm_count / 2;
+}
+
+cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
+  CUtensorMap ta, tb, tout;
+  if (!make_tmap(&ta, g.aq, g.M, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;
+  if (!make_tmap(&tb, g.bq, g.N, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;  // 128-row halves
+  if (!make_out_tmap(&tout, g.out, g.M, g.N, why)) return cudaErrorInvalidValue;
+  const int64_t tiles = ((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((g.N + kBlockN2 - 1) / kBlockN2);
+  int64_t clusters = sm_count / 2;
+  if (tiles < clusters) clusters = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(clusters * 2));
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = kSmemBytes2;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  count_launch();
+  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel, ta, tb, tout, g);
+}
+
+}  // namespace sdq

@@ -54,4 +54,9 @@ cudaError_t launch_qgemm_tc(const GemmArgs& g, int sm_count, cudaStream_t s, std
 // One-time set-up (driver entry point lookup, max-shared-memory attributes).
 int qgemm_tc_setup(std::string* why);
 
+// 2-CTA (cta_group::2) variant for large problems: qgemm_tcgen05_2cta.cu.
+int qgemm_tc2_setup(std::string* why);
+bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count);  // call only if qgemm_tc_supported(g)
+cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why);
+
 }  // namespace sdq
