@@ -295,8 +295,9 @@ def run_b200(args):
         hY = torch.empty(M, D_MODEL, dtype=torch.float32, pin_memory=True)
 
         def e2e_step():
-            ck(lib.sdq_qgemm(w1, hA.data_ptr(), M, H.data_ptr(), b1.data_ptr(), S.A_HOST | S.GELU_TANH, sp))
-            ck(lib.sdq_qgemm(w2, H.data_ptr(), M, hY.data_ptr(), b2.data_ptr(), S.OUT_HOST, sp))
+            # the public call for the pair: host x in, host y out, copies inside the call
+            ck(lib.sdq_ffn_pair(w1, b1.data_ptr(), w2, b2.data_ptr(), hA.data_ptr(), M, None, hY.data_ptr(),
+                                S.A_HOST | S.OUT_HOST, sp))
         n_e2e = max(3, min(args.steps, 10))
         for _ in range(3):
             e2e_step()

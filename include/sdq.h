@@ -139,6 +139,19 @@ SDQ_API int sdq_qgemm_prequantized(sdq_weight_t w, const int8_t* aq_dev, const f
                            int64_t M, float* out_dev, const float* bias_dev,
                            int32_t* acc_dump_dev, uint32_t flags, void* stream);
 
+/* y = fc2(gelu_tanh(fc1(x))) for one FFN -- replaces the three lines of the reference's
+ * ffn_fwd that are on this path (src/model/ovi_dit.cpp:218-220: mlin fc1,
+ * gelu_tanh_inplace, mlin fc2; each mlin = sd::qgemm + bias pass).  x is fp32
+ * [M, K1], y fp32 [M, N2]; w2's K must equal w1's N.  Device pointers by default;
+ * `hidden_dev` (fp32 [M, N1], device, may be NULL) receives the activations between
+ * the two linears.  With SDQ_A_HOST | SDQ_OUT_HOST (both or neither) x and y are host
+ * memory -- pinned memory makes the copies asynchronous -- and the rows are processed
+ * in chunks so that the upload of the next chunk and the download of the previous one
+ * overlap the arithmetic; hidden_dev is ignored and the call returns when y is complete. */
+SDQ_API int sdq_ffn_pair(sdq_weight_t w1, const float* bias1_dev, sdq_weight_t w2,
+                         const float* bias2_dev, const float* x, int64_t M, float* hidden_dev,
+                         float* y, uint32_t flags, void* stream);
+
 /* The same computation as sdq_qgemm for callers that cannot allocate device memory
  * while they run (a host that has given all HBM to its own pool, a plugin inside
  * another allocator, a section where cudaMalloc's implicit device-wide

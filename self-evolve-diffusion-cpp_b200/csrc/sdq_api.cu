@@ -41,6 +41,12 @@ struct Context {
   std::vector<Weight> weights;                       // handle = index + 1
   std::unordered_map<const void*, sdq_weight_t> by_host;
   std::unordered_map<cudaStream_t, Workspace> ws;
+  // the FFN pair's host-pointer pipeline: two copy streams, events, chunk buffers
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev_in[2] = {}, ev_a_free[2] = {}, ev_comp[2] = {}, ev_out_done[2] = {};
+  float* pa[2] = {}; size_t pa_bytes[2] = {};
+  float* py[2] = {}; size_t py_bytes[2] = {};
+  float* ph = nullptr; size_t ph_bytes = 0;
 };
 Context* g_ctx = nullptr;
 std::mutex g_init_mu;
@@ -160,6 +166,14 @@ int sdq_shutdown(void) {
     cudaFree(kv.second.aq); cudaFree(kv.second.a_scale);
     cudaFree(kv.second.a_stage); cudaFree(kv.second.out_stage);
   }
+  for (int i = 0; i < 2; i++) {
+    cudaFree(g_ctx->pa[i]); cudaFree(g_ctx->py[i]);
+    if (g_ctx->ev_in[i]) { cudaEventDestroy(g_ctx->ev_in[i]); cudaEventDestroy(g_ctx->ev_a_free[i]);
+                           cudaEventDestroy(g_ctx->ev_comp[i]); cudaEventDestroy(g_ctx->ev_out_done[i]); }
+  }
+  cudaFree(g_ctx->ph);
+  if (g_ctx->copy_in) cudaStreamDestroy(g_ctx->copy_in);
+  if (g_ctx->copy_out) cudaStreamDestroy(g_ctx->copy_out);
   cudaFree(g_ctx->status);
   delete g_ctx;
   g_ctx = nullptr;
@@ -346,6 +360,96 @@ int sdq_qgemm(sdq_weight_t h, const float* A, int64_t M, float* out, const float
   }
   if (flags & SDQ_SYNC) return sdq_stream_sync(stream);
   return SDQ_OK;
+}
+
+// ---- FFN pair ----
+// fc1 -> GELU(tanh) -> fc2 on [r0, r1) rows that are already on the device.
+static int ffn_rows_device(const Weight& w1, const float* b1, const Weight& w2, const float* b2,
+                           const float* x, int64_t rows, float* h, float* y, Workspace* ws,
+                           cudaStream_t s) {
+  if (int rc = grow(&ws->aq, &ws->aq_bytes, (size_t)rows * std::max(w1.K, w2.K))) return rc;
+  if (int rc = grow(&ws->a_scale, &ws->a_scale_bytes, (size_t)rows * 4)) return rc;
+  SDQ_CUDA(launch_act_quant(x, rows, w1.K, ws->aq, ws->a_scale, g_ctx->sm_count, s));
+  if (int rc = run_gemm(w1, ws->aq, ws->a_scale, rows, h, b1, nullptr, SDQ_GELU_TANH, s)) return rc;
+  SDQ_CUDA(launch_act_quant(h, rows, w2.K, ws->aq, ws->a_scale, g_ctx->sm_count, s));
+  return run_gemm(w2, ws->aq, ws->a_scale, rows, y, b2, nullptr, 0, s);
+}
+
+int sdq_ffn_pair(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, const float* bias2_dev,
+                 const float* x, int64_t M, float* hidden_dev, float* y, uint32_t flags,
+                 void* stream) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w1 = get_weight(h1);
+  Weight* w2 = get_weight(h2);
+  if (!w1 || !w2) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: bad weight handle");
+  if (w2->K != w1->N) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: fc2 input width differs from fc1 output width");
+  if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: negative M");
+  if (M == 0) return SDQ_OK;
+  if (!x || !y) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: null pointer");
+  const bool x_host = flags & SDQ_A_HOST, y_host = flags & SDQ_OUT_HOST;
+  if (x_host != y_host) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: x and y must both be host or both be device memory");
+  cudaStream_t s = (cudaStream_t)stream;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  const int64_t D = w1->K, F = w1->N, Dout = w2->N;
+  if (!x_host) {
+    float* h = hidden_dev;
+    if (!h) {  // caller does not want the hidden activations: keep them in the staging buffer
+      if (int rc = grow(&ws->out_stage, &ws->out_stage_bytes, (size_t)M * F * 4)) return rc;
+      h = ws->out_stage;
+    }
+    if (int rc = ffn_rows_device(*w1, bias1_dev, *w2, bias2_dev, x, M, h, y, ws, s)) return rc;
+    return (flags & SDQ_SYNC) ? sdq_stream_sync(stream) : SDQ_OK;
+  }
+
+  // Host x and y: rows are independent, so the pair is run chunk by chunk with the
+  // copies of neighbouring chunks overlapping the arithmetic:
+  //   copy_in : H2D x[i+1]   |  stream : quant, fc1, quant, fc2 on chunk i  |  copy_out : D2H y[i-1]
+  Context* c = g_ctx;
+  if (!c->copy_in) {
+    SDQ_CUDA(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
+    SDQ_CUDA(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; i++) {
+      SDQ_CUDA(cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming));
+      SDQ_CUDA(cudaEventCreateWithFlags(&c->ev_a_free[i], cudaEventDisableTiming));
+      SDQ_CUDA(cudaEventCreateWithFlags(&c->ev_comp[i], cudaEventDisableTiming));
+      SDQ_CUDA(cudaEventCreateWithFlags(&c->ev_out_done[i], cudaEventDisableTiming));
+    }
+  }
+  const int64_t chunk = std::min<int64_t>(M, 4096);
+  for (int i = 0; i < 2; i++) {
+    if (int rc = grow(&c->pa[i], &c->pa_bytes[i], (size_t)chunk * D * 4)) return rc;
+    if (int rc = grow(&c->py[i], &c->py_bytes[i], (size_t)chunk * Dout * 4)) return rc;
+  }
+  if (int rc = grow(&c->ph, &c->ph_bytes, (size_t)chunk * F * 4)) return rc;
+  // the copy streams start after whatever the caller already queued on `stream`
+  SDQ_CUDA(cudaEventRecord(c->ev_comp[0], s));
+  SDQ_CUDA(cudaStreamWaitEvent(c->copy_in, c->ev_comp[0], 0));
+  SDQ_CUDA(cudaStreamWaitEvent(c->copy_out, c->ev_comp[0], 0));
+  int64_t n = 0;
+  for (int64_t r0 = 0; r0 < M; r0 += chunk, n++) {
+    const int64_t rows = std::min(chunk, M - r0);
+    const int b = (int)(n & 1);
+    if (n >= 2) SDQ_CUDA(cudaStreamWaitEvent(c->copy_in, c->ev_a_free[b], 0));  // x buffer consumed
+    SDQ_CUDA(cudaMemcpyAsync(c->pa[b], x + r0 * D, (size_t)rows * D * 4, cudaMemcpyHostToDevice, c->copy_in));
+    SDQ_CUDA(cudaEventRecord(c->ev_in[b], c->copy_in));
+    SDQ_CUDA(cudaStreamWaitEvent(s, c->ev_in[b], 0));
+    if (n >= 2) SDQ_CUDA(cudaStreamWaitEvent(s, c->ev_out_done[b], 0));         // y buffer copied out
+    if (int rc = ffn_rows_device(*w1, bias1_dev, *w2, bias2_dev, c->pa[b], rows, c->ph, c->py[b], ws, s)) return rc;
+    SDQ_CUDA(cudaEventRecord(c->ev_a_free[b], s));
+    SDQ_CUDA(cudaEventRecord(c->ev_comp[b], s));
+    SDQ_CUDA(cudaStreamWaitEvent(c->copy_out, c->ev_comp[b], 0));
+    SDQ_CUDA(cudaMemcpyAsync(y + r0 * Dout, c->py[b], (size_t)rows * Dout * 4, cudaMemcpyDeviceToHost, c->copy_out));
+    SDQ_CUDA(cudaEventRecord(c->ev_out_done[b], c->copy_out));
+  }
+  // the caller's stream (and the host) see the call as complete when the last copy-out is
+  SDQ_CUDA(cudaStreamWaitEvent(s, c->ev_out_done[0], 0));
+  SDQ_CUDA(cudaStreamWaitEvent(s, c->ev_out_done[1], 0));
+  SDQ_CUDA(cudaStreamSynchronize(c->copy_out));
+  return sdq_stream_sync(stream);
 }
 
 // ---- weight quantizers ----

@@ -73,6 +73,8 @@ _SIGS = {
     "sdq_quantize_activations": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sdq_qgemm_prequantized": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_ffn_pair": (C.c_int, [C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64,
+                               C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_static_scratch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
                                            C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_quantize_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_void_p,
@@ -290,6 +292,18 @@ class Sdq:
                                                  dacc.ptr, flags, None))
         return (dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,)),
                 dacc.to_numpy(np.int32, (M, N)), dout.to_numpy(np.float32, (M, N)))
+
+    def ffn_pair_host(self, w1, b1, w2, b2, x):
+        """numpy in, numpy out through the chunked host-pointer pipeline of sdq_ffn_pair."""
+        x = np.ascontiguousarray(x, np.float32)
+        M = x.shape[0]
+        N2 = self.weight_info(w2)[0]
+        y = np.empty((M, N2), np.float32)
+        d1 = self.to_device(np.ascontiguousarray(b1, np.float32)) if b1 is not None else None
+        d2 = self.to_device(np.ascontiguousarray(b2, np.float32)) if b2 is not None else None
+        self._ck(self.lib.sdq_ffn_pair(w1, d1.ptr if d1 else None, w2, d2.ptr if d2 else None, _np_ptr(x), M,
+                                       None, _np_ptr(y), A_HOST | OUT_HOST, None))
+        return y
 
     def qgemm_static_scratch(self, wq_ptr, ws_ptr, N, K, A_ptr, M, out_ptr, bias_ptr=None, flags=0,
                              stream=None):

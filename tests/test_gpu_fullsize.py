@@ -98,3 +98,38 @@ def test_fused_qkv_equals_three_calls(sdq, oracle):
         assert bits_equal(sdq.qgemm_host(w, A), fused[:, i * D:(i + 1) * D])
         sdq.weight_release(w)
     sdq.weight_release(wcat)
+
+
+def test_ffn_pair_entry_point(sdq, pkg, oracle):
+    """sdq_ffn_pair (fc1 -> GELU -> fc2): the chunked host-pointer pipeline and the device
+    path give the same bits as two sdq_qgemm calls, and stay within 1e-3 of the CPU chain."""
+    rng = np.random.default_rng(55)
+    M, D, F = 9000, 512, 1024                       # 3 chunks of 4096 rows, the last one partial
+    x = (rng.standard_normal((M, D)) * 0.5).astype(np.float32)
+    w1q, w1s = packed_weights(rng, F, D, oracle)
+    w2q, w2s = packed_weights(rng, D, F, oracle)
+    b1 = (rng.standard_normal(F) * 0.02).astype(np.float32)
+    b2 = (rng.standard_normal(D) * 0.02).astype(np.float32)
+    w1, w2 = sdq.weight_upload(w1q, w1s), sdq.weight_upload(w2q, w2s)
+    y_pipe = sdq.ffn_pair_host(w1, b1, w2, b2, x)
+    h = sdq.qgemm_host(w1, x, bias=b1, gelu=True)
+    y_two = sdq.qgemm_host(w2, h, bias=b2)
+    assert bits_equal(y_pipe, y_two)
+    # device pointers, hidden activations returned
+    dx, db1, db2 = sdq.to_device(x), sdq.to_device(b1), sdq.to_device(b2)
+    dh, dy = sdq.alloc(M * F * 4), sdq.alloc(M * D * 4)
+    sdq._ck(sdq.lib.sdq_ffn_pair(w1, db1.ptr, w2, db2.ptr, dx.ptr, M, dh.ptr, dy.ptr, pkg.sdq.SYNC, None))
+    assert bits_equal(dy.to_numpy(np.float32, (M, D)), y_two)
+    assert bits_equal(dh.to_numpy(np.float32, (M, F)), h)
+    # against the CPU chain (GELU is the only inexact step): 1e-3 of the output's max
+    rows = np.sort(rng.choice(M, 256, replace=False))
+    h_cpu = oracle.gelu_tanh(oracle.bias_add(oracle.qgemm(x[rows], w1q, w1s), b1))
+    y_cpu = oracle.bias_add(oracle.qgemm(h_cpu, w2q, w2s), b2)
+    assert max_rel_err(y_pipe[rows], y_cpu) < 1e-3
+    # mismatched widths and mixed host/device pointers are rejected
+    with pytest.raises(pkg.SdqError):
+        sdq._ck(sdq.lib.sdq_ffn_pair(w1, None, w1, None, dx.ptr, M, None, dy.ptr, 0, None))
+    with pytest.raises(pkg.SdqError):
+        sdq._ck(sdq.lib.sdq_ffn_pair(w1, None, w2, None, dx.ptr, M, None, dy.ptr, pkg.sdq.A_HOST, None))
+    sdq.weight_release(w1)
+    sdq.weight_release(w2)
