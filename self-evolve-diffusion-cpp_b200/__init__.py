@@ -7,3 +7,11 @@ valid Python identifier: load it with `__graft_entry__.load_package()`.
 """
 from .sdq import Sdq, SdqError, DeviceBuffer, lib_path, build  # noqa: F401
 from . import sharding  # noqa: F401
+
+
+def __getattr__(name):
+    # `parallel` needs torch; import it only when asked for
+    if name == "parallel":
+        import importlib
+        return importlib.import_module(__name__ + ".parallel")
+    raise AttributeError(name)

@@ -1,0 +1,182 @@
+// libsd_b200.so: the reference's sd:: functions of the int8 quantized-linear path,
+// defined on top of the sdq C ABI (include/sdq.h).  Host-side container code
+// (Tensor, bf16 conversion, parallel_for) is plain C++; everything that computes
+// goes to the GPU through libsdq.so and throws when that fails -- there is no CPU
+// implementation of qgemm or quantize_rowwise in this library.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <stdexcept>
+#include <thread>
+
+#include "core/tensor.h"
+#include "sdq.h"
+#include "serde/sdcpp.h"
+
+namespace sd {
+namespace {
+
+size_t elem_size(DType d) { return d == DType::F32 ? 4 : d == DType::BF16 ? 2 : 1; }
+
+void ensure_device() {
+  static std::once_flag once;
+  static int rc = SDQ_OK;
+  static std::string msg;
+  std::call_once(once, [] {
+    const char* dev = std::getenv("SD_DEVICE");
+    rc = sdq_init(dev ? std::atoi(dev) : 0);
+    if (rc != SDQ_OK) msg = sdq_last_error();
+  });
+  if (rc != SDQ_OK) throw std::runtime_error("sd (B200): " + msg);
+}
+
+[[noreturn]] void raise_last() { throw std::runtime_error(sdq_last_error()); }
+
+}  // namespace
+
+// ---- Tensor (reference src/core/tensor.cpp:19-37) ----
+Tensor::Tensor(std::vector<int64_t> s, DType d) : shape(std::move(s)), dtype(d) {
+  int64_t n = 1;
+  for (int64_t x : shape) n *= x;
+  nbytes = (size_t)n * elem_size(dtype);
+  data = aligned_alloc(64, (nbytes + 63) / 64 * 64 + 64);
+  if (!data) throw std::bad_alloc();
+  std::memset(data, 0, nbytes);
+}
+Tensor::~Tensor() {
+  if (owning && data) std::free(data);
+}
+Tensor::Tensor(Tensor&& o) noexcept { *this = std::move(o); }
+Tensor& Tensor::operator=(Tensor&& o) noexcept {
+  if (this == &o) return *this;
+  if (owning && data) std::free(data);
+  shape = std::move(o.shape);
+  dtype = o.dtype;
+  data = o.data;
+  nbytes = o.nbytes;
+  owning = o.owning;
+  o.data = nullptr;
+  o.nbytes = 0;
+  return *this;
+}
+int64_t Tensor::numel() const {
+  int64_t n = 1;
+  for (int64_t x : shape) n *= x;
+  return n;
+}
+void Tensor::reshape(std::vector<int64_t> s) {
+  int64_t n = 1;
+  for (int64_t x : s) n *= x;
+  if (n != numel()) std::abort();
+  shape = std::move(s);
+}
+
+// ---- bf16 (reference src/core/tensor.cpp:39-60) ----
+void to_f32(const Tensor& bf16, Tensor& out) {
+  out = Tensor(bf16.shape, DType::F32);
+  const uint16_t* s = bf16.ptr<uint16_t>();
+  uint32_t* d = out.ptr<uint32_t>();
+  for (int64_t i = 0, n = bf16.numel(); i < n; i++) d[i] = (uint32_t)s[i] << 16;
+}
+void to_bf16(const Tensor& f32, Tensor& out) {
+  out = Tensor(f32.shape, DType::BF16);
+  const uint32_t* s = f32.ptr<uint32_t>();
+  uint16_t* d = out.ptr<uint16_t>();
+  for (int64_t i = 0, n = f32.numel(); i < n; i++) {
+    uint32_t u = s[i];
+    u += 0x7fffu + ((u >> 16) & 1u);
+    d[i] = (uint16_t)(u >> 16);
+  }
+}
+
+// ---- the hot path (reference src/core/qgemm.cpp:73-142) ----
+void qgemm(const Tensor& A, const Tensor& Bq, const Tensor& bs, Tensor& out) {
+  const int64_t M = A.rows(), K = A.cols(), N = Bq.rows();
+  out = Tensor({M, N}, DType::F32);
+  if (M == 0 || N == 0 || K == 0) return;
+  ensure_device();
+  sdq_weight_t w = 0;
+  bool temporary = false;
+  if (sdq_weight_lookup(Bq.data, &w) != SDQ_OK) {
+    if (sdq_weight_upload(Bq.ptr<int8_t>(), bs.ptr<float>(), N, K, &w) != SDQ_OK) raise_last();
+    temporary = true;
+  }
+  const int rc = sdq_qgemm(w, A.ptr<float>(), M, out.ptr<float>(), nullptr,
+                           SDQ_A_HOST | SDQ_OUT_HOST, nullptr);
+  const std::string msg = rc != SDQ_OK ? sdq_last_error() : "";
+  if (temporary) sdq_weight_release(w);
+  if (rc != SDQ_OK) throw std::runtime_error(msg);
+}
+
+// reference src/core/tensor.cpp:63-78
+void quantize_rowwise(const Tensor& W, Tensor& Wq, Tensor& scale) {
+  const int64_t N = W.rows(), K = W.cols();
+  Wq = Tensor({N, K}, DType::I8);
+  scale = Tensor({N}, DType::F32);
+  if (N == 0 || K == 0) return;
+  ensure_device();
+  if (sdq_quantize_rows(W.data, SDQ_F32, N, K, SDQ_MODE_ROWWISE, Wq.ptr<int8_t>(),
+                        scale.ptr<float>(), SDQ_SRC_HOST | SDQ_DST_HOST, nullptr) != SDQ_OK)
+    raise_last();
+}
+
+// reference src/serde/sdcpp.cpp:47-133
+std::unordered_map<std::string, Tensor> load_sdcpp(const std::string& path,
+                                                   std::shared_ptr<void>& owner) {
+  // Format errors are reported before a device is required, as the reference would.
+  sdq_pack* probe = nullptr;
+  if (sdq_pack_open(path.c_str(), 0, &probe) != SDQ_OK) raise_last();
+  sdq_pack_close(probe);
+  ensure_device();
+  sdq_pack* p = nullptr;
+  if (sdq_pack_open(path.c_str(), SDQ_PACK_UPLOAD, &p) != SDQ_OK) raise_last();
+  owner = std::shared_ptr<void>(p, [](void* q) { sdq_pack_close(static_cast<sdq_pack*>(q)); });
+  std::unordered_map<std::string, Tensor> out;
+  for (int64_t i = 0, n = sdq_pack_count(p); i < n; i++) {
+    sdq_entry e;
+    if (sdq_pack_entry(p, i, &e) != SDQ_OK) raise_last();
+    Tensor t;
+    t.shape.assign(e.dims, e.dims + e.ndim);
+    t.dtype = e.dtype == SDQ_DT_I8 ? DType::I8 : DType::F32;
+    t.data = const_cast<void*>(e.data);
+    t.nbytes = (size_t)e.nbytes;
+    t.owning = false;
+    out.emplace(e.name, std::move(t));
+  }
+  return out;
+}
+
+// ---- host thread dispatch (reference src/core/tensor.cpp:81-103) ----
+namespace {
+std::atomic<int> g_threads{(int)std::thread::hardware_concurrency()};
+}
+int nthreads() { return g_threads.load(); }
+void set_nthreads(int n) { g_threads.store(n > 0 ? n : 1); }
+
+void parallel_for(int64_t begin, int64_t end, int64_t grain,
+                  const std::function<void(int64_t, int64_t)>& fn) {
+  if (end <= begin) return;
+  if (grain < 1) grain = 1;
+  const int64_t chunks = (end - begin + grain - 1) / grain;
+  int nt = nthreads();
+  if (chunks < nt) nt = (int)chunks;
+  if (nt <= 1) {
+    fn(begin, end);
+    return;
+  }
+  std::atomic<int64_t> next{0};
+  auto work = [&] {
+    for (int64_t c = next.fetch_add(1); c < chunks; c = next.fetch_add(1)) {
+      const int64_t b = begin + c * grain;
+      fn(b, b + grain < end ? b + grain : end);
+    }
+  };
+  std::vector<std::thread> team;
+  team.reserve(nt - 1);
+  for (int t = 1; t < nt; t++) team.emplace_back(work);
+  work();
+  for (auto& th : team) th.join();
+}
+
+}  // namespace sd
