@@ -44,6 +44,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=M_720P, help="token rows per GPU")
+    ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch"])
+    ap.add_argument("--blocks", type=int, default=30, help="branch workload: number of DiT blocks")
+    ap.add_argument("--verify-blocks", type=int, default=1, help="branch workload: blocks whose packed bytes are compared with the CPU packer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -362,6 +365,220 @@ def run_b200(args):
     return 0
 
 
+# ------------------------------------------------------------------ shape sweep
+SWEEP_KN = [(3072, 3072), (3072, 9216), (3072, 14336), (14336, 3072), (3072, 18432)]
+SWEEP_M = [192, 1024, 4096, 16384, 27280, 54560]
+
+
+def run_sweep(args):
+    """Every DiT linear (K,N) over the token counts of the shape sweep; rows split over the
+    ranks (total work fixed), whole sd::qgemm per point = quantize launch + GEMM launch.
+    L2 is flushed (256 MiB write) before every timed call.  One JSON line, key "sweep"."""
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as ge
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = ge.load_package()
+    s = pkg.Sdq(local)
+    S, lib = pkg.sdq, s.lib
+    dev = torch.device("cuda", local)
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    g = torch.Generator(device=dev)
+    g.manual_seed(7 + rank)
+    flush = torch.empty(256 << 20, device=dev, dtype=torch.uint8)
+    pk, pk_kind = peaks()
+    hbm = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    tens = float(pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    points = []
+    for (K, N) in SWEEP_KN:
+        wb = (torch.randn(N, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        q = torch.empty(N, K, device=dev, dtype=torch.int8)
+        sc = torch.empty(N, device=dev, dtype=torch.float32)
+        s._ck(lib.sdq_quantize_rows(wb.data_ptr(), S.BF16, N, K, S.MODE_PACKER, q.data_ptr(), sc.data_ptr(), 0, sp))
+        w = s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), N, K)
+        for Mtot in SWEEP_M:
+            r0, r1 = pkg.sharding.row_shard(Mtot, world, rank)
+            M = r1 - r0
+            A = torch.randn(max(M, 1), K, device=dev, generator=g)
+            out = torch.empty(max(M, 1), N, device=dev)
+            times = []
+            for it in range(2 + args.steps):
+                flush.zero_()
+                if world > 1:
+                    dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                s._ck(lib.sdq_qgemm(w, A.data_ptr(), M, out.data_ptr(), None, 0, sp))
+                e1.record(stream)
+                torch.cuda.synchronize()
+                if it >= 2:
+                    times.append(e0.elapsed_time(e1))
+            t = torch.tensor([float(np.median(times))], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            ops = 2.0 * Mtot * N * K
+            byts = gemm_bytes(Mtot, K, N, bias=False)
+            t_tensor = ops / (tens * 1e12 * world) * 1e3
+            t_hbm = byts / (hbm * 1e9 * world) * 1e3
+            points.append({"K": K, "N": N, "M": Mtot, "ms": ms, "tops": ops / (ms * 1e-3) / 1e12,
+                           "bound": "tensor" if t_tensor >= t_hbm else "hbm",
+                           "frac_of_bound": max(t_tensor, t_hbm) / ms})
+            del A, out
+        s.weight_release(w)
+        del wb, q, sc
+    s.sync(sp)
+    if rank == 0:
+        total_ops = sum(2.0 * p["M"] * p["N"] * p["K"] for p in points)
+        total_ms = sum(p["ms"] for p in points)
+        print(json.dumps({"metric": "int8_qgemm_throughput", "value": total_ops / (total_ms * 1e-3) / 1e12,
+                          "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": 2,
+                          "ms_per_step": total_ms, "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+                          "config": {"workload": "dit_linear_shape_sweep", "points": len(points),
+                                     "l2": "flushed with a 256 MiB write before every timed call",
+                                     "peaks": "bound = max(2MNK / bf16 sustained " + pk_kind +
+                                              ", bytes / HBM copy " + pk_kind + ")"},
+                          "sweep": points}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+# ------------------------------------------------------------------ whole branch
+# linears of one DiT block of the video branch (name, K, N, rows: None = all tokens)
+BLOCK_LINEARS = [("self_attn.qkv", 3072, 9216, None), ("self_attn.o", 3072, 3072, None),
+                 ("cross_attn.q", 3072, 3072, None), ("cross_attn.k", 3072, 3072, 512),
+                 ("cross_attn.v", 3072, 3072, 512), ("cross_attn.o", 3072, 3072, None),
+                 ("ffn.0", 3072, 14336, None), ("ffn.2", 14336, 3072, None)]
+
+
+def run_branch(args):
+    """A random-init 5B-parameter DiT branch: 30 blocks of int8 linears.  Phase 1 packs the bf16
+    weights to the .sdcpp int8 layout on the GPU (with --verify-blocks n, the packed bytes and
+    scales of the first n blocks are compared with the CPU packer arithmetic).  Phase 2 runs
+    every linear once at M = --rows tokens (K/V projections at 512 text tokens).  Branches are
+    independent and rows are split over the ranks; one JSON line."""
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as ge
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = ge.load_package()
+    s = pkg.Sdq(local)
+    S, lib = pkg.sdq, s.lib
+    dev = torch.device("cuda", local)
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)                                   # the same weights on every rank (replicated)
+    blocks = args.blocks
+    r0, r1 = pkg.sharding.row_shard(args.rows, world, rank)
+    M = r1 - r0
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    weights, pack_ms, pack_elems, verified = [], 0.0, 0, 0
+    orc = None
+    for b in range(blocks):
+        for (name, K, N, rows) in BLOCK_LINEARS:
+            wb = (torch.randn(N, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            q = torch.empty(N, K, device=dev, dtype=torch.int8)
+            sc = torch.empty(N, device=dev, dtype=torch.float32)
+            e0, e1 = ev(), ev()
+            e0.record(stream)
+            s._ck(lib.sdq_quantize_rows(wb.data_ptr(), S.BF16, N, K, S.MODE_PACKER, q.data_ptr(), sc.data_ptr(), 0, sp))
+            e1.record(stream)
+            torch.cuda.synchronize()
+            pack_ms += e0.elapsed_time(e1)
+            pack_elems += N * K
+            if rank == 0 and b < args.verify_blocks:
+                if orc is None:
+                    from oracle.binding import Oracle
+                    orc = Oracle()
+                bits = wb.view(torch.int16).cpu().numpy().view(np.uint16)
+                q_c, s_c = orc.quant_rows_packer(orc.bf16_to_f32(bits))
+                if q.cpu().numpy().tobytes() != q_c.tobytes() or sc.cpu().numpy().tobytes() != s_c.tobytes():
+                    raise SystemExit("packed bytes of block %d %s differ from the CPU packer" % (b, name))
+                verified += 1
+            weights.append((K, N, rows, q, sc, s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), N, K)))
+            del wb
+    x = torch.randn(max(M, 1), 3072, device=dev, generator=g)
+    xf = torch.randn(max(M, 1), 14336, device=dev, generator=g)
+    xt = torch.randn(512, 3072, device=dev, generator=g)
+    out = torch.empty(max(M, 1) * 14336, device=dev)
+
+    def forward():
+        ops = 0.0
+        for (K, N, rows, q, sc, w) in weights:
+            if rows is None:
+                a, m = (x if K == 3072 else xf), M
+            else:
+                a, m = xt, (rows if rank == 0 else 0)   # the text K/V rows are not worth splitting
+            if m:
+                s._ck(lib.sdq_qgemm(w, a.data_ptr(), m, out.data_ptr(), None, 0, sp))
+            ops += 2.0 * (args.rows if rows is None else rows) * N * K
+        return ops
+    forward()
+    s.sync(sp)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    n0 = s.launches()
+    e0, e1 = ev(), ev()
+    e0.record(stream)
+    for _ in range(args.steps):
+        ops = forward()
+    e1.record(stream)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s.sync(sp)
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        pk, pk_kind = peaks()
+        hbm = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+        pack_gbs = (3.0 * pack_elems) / (pack_ms * 1e-3) / 1e9
+        print(json.dumps({"metric": "int8_qgemm_throughput", "value": ops / (ms * 1e-3) / 1e12, "unit": "TOPS",
+                          "n_gpus": world, "steps": args.steps, "warmup": 1, "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8",
+                          "data": "synthetic",
+                          "config": {"workload": "dit_branch_all_linears", "blocks": blocks, "rows": args.rows,
+                                     "int8_params": pack_elems},
+                          "gpu_launches": s.launches() - n0,
+                          "pack": {"elements": pack_elems, "ms": pack_ms, "gb_per_s": pack_gbs,
+                                   "roofline": {"bound": "hbm", "achieved": pack_gbs, "peak": hbm, "unit": "GB/s",
+                                                "frac": pack_gbs / hbm, "of": pk_kind},
+                                   "tensors_verified_against_cpu_packer": verified}}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 if __name__ == "__main__":
     a = parse_args()
-    sys.exit(run_reference(a) if a.impl == "reference" else run_b200(a))
+    if a.impl == "reference":
+        sys.exit(run_reference(a))
+    sys.exit(run_sweep(a) if a.workload == "sweep" else run_branch(a) if a.workload == "branch" else run_b200(a))

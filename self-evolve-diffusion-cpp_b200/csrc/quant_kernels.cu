@@ -157,6 +157,76 @@ struct RowRecipe {
   }
 };
 
+// One block per row with the row held in registers between the max and the rounding:
+// 16-byte loads (8 bf16/f16 or 4 fp32 elements), packed stores.  Needs last % EPV == 0,
+// 16-byte aligned rows, last <= kThreads * EPV * VPT.
+template <int DT>
+struct Vec {
+  static constexpr int EPV = DT == SDQ_F32 ? 4 : 8;  // elements per 16-byte vector
+  __device__ static void load(const void* row, int idx, float (&v)[EPV]) {
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(row) + idx);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    if constexpr (DT == SDQ_F32) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) v[i] = __uint_as_float(w[i]);
+    } else if constexpr (DT == SDQ_BF16) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        v[2 * i] = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xffffu)));
+        v[2 * i + 1] = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16)));
+      }
+    }
+  }
+};
+
+template <int DT, int MODE, int VPT>
+__global__ void __launch_bounds__(kThreads) quant_rows_regs(const void* __restrict__ src,
+                                                            int64_t rows, int64_t last,
+                                                            int8_t* __restrict__ q,
+                                                            float* __restrict__ scale) {
+  constexpr int EPV = Vec<DT>::EPV;
+  constexpr int ESZ = DT == SDQ_F32 ? 4 : 2;
+  __shared__ float red[kThreads / 32];
+  const int nvec = (int)(last / EPV);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const char* rp = static_cast<const char*>(src) + row * last * ESZ;
+    float v[VPT][EPV];
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < nvec) {
+        Vec<DT>::load(rp, idx, v[i]);
+#pragma unroll
+        for (int e = 0; e < EPV; e++) mx = fmaxf(mx, fabsf(v[i][e]));
+      }
+    }
+    mx = block_max(mx, red);
+    const RowRecipe<MODE> rr(mx);
+    if (threadIdx.x == 0) scale[row] = rr.scale;
+    int8_t* qp = q + row * last;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < nvec) {
+        uint32_t w0 = pack4(rr.q(v[i][0]), rr.q(v[i][1]), rr.q(v[i][2]), rr.q(v[i][3]));
+        if constexpr (EPV == 4) {
+          reinterpret_cast<uint32_t*>(qp)[idx] = w0;
+        } else {
+          uint32_t w1 = pack4(rr.q(v[i][EPV - 4]), rr.q(v[i][EPV - 3]), rr.q(v[i][EPV - 2]), rr.q(v[i][EPV - 1]));
+          reinterpret_cast<uint2*>(qp)[idx] = make_uint2(w0, w1);
+        }
+      }
+    }
+  }
+}
+
 // One block per row (grid-stride), two sweeps.  `last` any size.
 template <int DT, int MODE>
 __global__ void __launch_bounds__(kThreads) quant_rows_block(const void* __restrict__ src,
@@ -219,7 +289,18 @@ cudaError_t launch_quant_t(const void* src, int64_t rows, int64_t last, int8_t* 
     quant_rows_warp<DT, MODE><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
   } else {
     int64_t blocks = rows < (int64_t)sm_count * 8 ? rows : (int64_t)sm_count * 8;
-    quant_rows_block<DT, MODE><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
+    constexpr int EPV = Vec<DT>::EPV;
+    const bool vec = (last % EPV == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+    const int64_t per_thread = (last / EPV + kThreads - 1) / kThreads;
+    if (vec && per_thread <= 2)
+      quant_rows_regs<DT, MODE, 2><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
+    else if (vec && per_thread <= 4)
+      quant_rows_regs<DT, MODE, 4><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
+    else if (vec && per_thread <= 8)
+      quant_rows_regs<DT, MODE, 8><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
+    else
+      quant_rows_block<DT, MODE><<<(unsigned)blocks, kThreads, 0, s>>>(src, rows, last, q, scale);
   }
   return cudaGetLastError();
 }
