@@ -86,6 +86,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const int num_n_blocks = (int)((g.N + BLOCK_N - 1) / BLOCK_N);
   const int num_k_blocks = (int)((g.K + BLOCK_K - 1) / BLOCK_K);
   const int num_tiles = num_m_blocks * num_n_blocks;
+  // Split-K: a work item is (tile, K slice).  Slices of one tile add their int32 partial
+  // sums into g.splitk_acc with atomics (integer addition: exact in any order); a second
+  // kernel turns the sums into fp32.  k_splits == 1 is the ordinary case.
+  const int k_splits = g.k_splits > 1 ? g.k_splits : 1;
+  const int kb_per_split = (num_k_blocks + k_splits - 1) / k_splits;
+  const int num_work = num_tiles * k_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; s++) {
@@ -101,7 +107,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
-    if (use_tma_store) prefetch_tmap(&tmap_out);
+    if (use_tma_store || g.k_splits > 1) prefetch_tmap(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
@@ -118,10 +124,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const uint64_t keep_policy = policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, num_m_blocks, num_n_blocks, m_blk, n_blk);
-        for (int kb = 0; kb < num_k_blocks; kb++) {
+        tile_coords(work % num_tiles, num_m_blocks, num_n_blocks, m_blk, n_blk);
+        const int kb0 = (work / num_tiles) * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, num_k_blocks);
+        for (int kb = kb0; kb < kb1; kb++) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x100 | 1);
           if (!ok) break;
           const uint32_t full = bar_full + 8 * stage;
@@ -138,12 +146,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       // ------------------------------------------------ MMA issuer
       uint32_t stage = 0, phase = 0, abuf = 0, aphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
         ok = mbar_wait(bar_tempty + 8 * abuf, aphase ^ 1u, abort_flag, g.status, 0x200 | 1);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + abuf * BLOCK_N;
-        for (int kb = 0; kb < num_k_blocks; kb++) {
+        const int kb0 = (work / num_tiles) * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, num_k_blocks);
+        for (int kb = kb0; kb < kb1; kb++) {
           ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x200 | 2);
           if (!ok) break;
           tc_fence_after();
@@ -153,7 +163,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
             // stepping K by 32 bytes inside the swizzle atom = +2 in the 16-byte address field
             umma_i8(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)),
-                    bdesc + (uint64_t)(k * (UMMA_K >> 4)), C::kIdesc, (uint32_t)((kb | k) != 0));
+                    bdesc + (uint64_t)(k * (UMMA_K >> 4)), C::kIdesc, (uint32_t)(((kb - kb0) | k) != 0));
           }
           umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -175,9 +185,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const uint64_t stream_policy = policy_evict_first();
     uint32_t abuf = 0, aphase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(tile, num_m_blocks, num_n_blocks, m_blk, n_blk);
+      tile_coords(work % num_tiles, num_m_blocks, num_n_blocks, m_blk, n_blk);
       ok = mbar_wait_warp(bar_tfull + 8 * abuf, aphase, abort_flag, g.status, 0x300 | 1);
       if (!ok) break;
       tc_fence_after();
@@ -194,7 +204,22 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + abuf * BLOCK_N + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
           tmem_ld_wait();
-          if (use_tma_store) {
+          if (k_splits > 1) {
+            // raw partial sums: staged like an output box, then added into the int32
+            // accumulator by a bulk tensor reduction (tmap_out describes g.splitk_acc here)
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              st_shared_v4_b32(box + (uint32_t)(lane * 128 + (((j >> 2) ^ (lane & 7)) << 4)), r[j],
+                               r[j + 1], r[j + 2], r[j + 3]);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_2d(&tmap_out, box, (int)nc, (int)row0);
+              bulk_commit();
+            }
+          } else if (use_tma_store) {
             float o[32];
             switch (mode) {
               case 0: chunk_values<false, false>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
@@ -258,6 +283,19 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   }
 }
 
+// Second step of split-K: fp32 outputs from the summed int32 accumulators.
+__global__ void __launch_bounds__(256) splitk_finalize_kernel(GemmArgs g) {
+  const bool gelu = (g.flags & SDQ_GELU_TANH) != 0;
+  const int64_t total = g.M * g.N;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int64_t row = i / g.N, col = i - row * g.N;
+    const int acc = g.splitk_acc[i];
+    if (g.acc_dump) g.acc_dump[i] = acc;
+    g.out[i] = epilogue_value(acc, g.a_scale[row], __ldg(g.b_scale + col),
+                              g.bias ? g.bias + col : nullptr, gelu);
+  }
+}
+
 // ---------------------------------------------------------------- host side
 
 template <int BLOCK_N>
@@ -269,17 +307,29 @@ cudaError_t launch_t(const GemmArgs& g, int sm_count, cudaStream_t s, std::strin
   // Bulk tensor stores need a 16-byte aligned base and row pitch; the accumulator dump
   // (a debugging aid) and odd N keep the per-thread store path.
   const int use_tma_store = (g.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0) &&
-                            g.acc_dump == nullptr;
-  if (use_tma_store) {
+                            g.acc_dump == nullptr && g.k_splits <= 1;
+  if (g.k_splits > 1) {
+    if (!make_out_tmap(&tout, g.splitk_acc, g.M, g.N, why, CU_TENSOR_MAP_DATA_TYPE_INT32))
+      return cudaErrorInvalidValue;
+  } else if (use_tma_store) {
     if (!make_out_tmap(&tout, g.out, g.M, g.N, why)) return cudaErrorInvalidValue;
   } else {
     tout = ta;  // unused by the kernel
   }
-  const int64_t tiles = ((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + BLOCK_N - 1) / BLOCK_N);
-  const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+  const int64_t work = ((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + BLOCK_N - 1) / BLOCK_N) *
+                       (g.k_splits > 1 ? g.k_splits : 1);
+  const unsigned grid = (unsigned)(work < sm_count ? work : sm_count);
   count_launch();
   qgemm_tc_kernel<BLOCK_N><<<grid, kNumThreads, C::kSmemBytes, s>>>(ta, tb, tout, use_tma_store, g);
-  return cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && g.k_splits > 1) {
+    int64_t blocks = (g.M * g.N + 255) / 256;
+    if (blocks > (int64_t)sm_count * 8) blocks = (int64_t)sm_count * 8;
+    count_launch();
+    splitk_finalize_kernel<<<(unsigned)blocks, 256, 0, s>>>(g);
+    e = cudaGetLastError();
+  }
+  return e;
 }
 
 template <int BLOCK_N>
@@ -319,16 +369,64 @@ bool qgemm_tc_supported(const GemmArgs& g) {
          ((g.M + BLOCK_M - 1) / BLOCK_M) * ((g.N + 31) / 32) < (int64_t(1) << 31);
 }
 
-cudaError_t launch_qgemm_tc(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
-  // Largest N tile that still gives every SM a tile; small problems take narrower
-  // tiles so that more SMs pull weight bytes from HBM at once.
-  if (qgemm_tc2_wanted(g, sm_count)) return launch_qgemm_tc2(g, sm_count, s, why);
+namespace {
+// Small problems (too few tiles to give every SM pair a 256x256 tile) are bound by how
+// fast the SMs can pull operand bytes, wave by wave.  Estimated time of a plan:
+//   waves x (k-blocks per slice x max(stage bytes / per-SM fetch rate, MMA time) + fixed)
+// plus the memset + finalize launches when K is split.  A narrow N tile spreads the
+// weight bytes over more SMs but re-reads the activation tile once per column block; a
+// K split multiplies the CTAs without re-reading anything.
+struct Plan { int bn; int splits; };
+Plan plan_small(const GemmArgs& g, int sm_count, bool allow_split) {
   const int64_t mb = (g.M + BLOCK_M - 1) / BLOCK_M;
-  auto tiles = [&](int bn) { return mb * ((g.N + bn - 1) / bn); };
-  if (tiles(256) >= sm_count) return launch_t<256>(g, sm_count, s, why);
-  if (tiles(128) >= sm_count) return launch_t<128>(g, sm_count, s, why);
-  if (tiles(64) >= sm_count) return launch_t<64>(g, sm_count, s, why);
-  return launch_t<32>(g, sm_count, s, why);
+  const int kb = (int)((g.K + BLOCK_K - 1) / BLOCK_K);
+  const double rows_frac = (double)g.M / (double)(mb * BLOCK_M);  // rows past M are not fetched
+  Plan best = {256, 1};
+  double best_t = 1e30;
+  for (int bn : {256, 128, 64, 32}) {
+    for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
+      if (splits > 1 && (!allow_split || kb / splits < 4 || g.N % 4 != 0)) continue;
+      const int kbs = (kb + splits - 1) / splits;
+      const int64_t work = mb * ((g.N + bn - 1) / bn) * splits;
+      const double waves = (double)((work + sm_count - 1) / sm_count);
+      const double stage_bytes = BLOCK_M * BLOCK_K * rows_frac + (double)bn * BLOCK_K;
+      const double t_fetch = stage_bytes / 120e3;               // us at ~120 GB/s per SM
+      const double t_mma = 4.0 * (bn / 256.0) * 128.0 / 1.9e3;  // us: 128 cycles per N=256 MMA
+      double t = waves * (kbs * (t_fetch > t_mma ? t_fetch : t_mma) + 1.5 + 0.25 * bn / 32.0);
+      if (splits > 1) t += 5.0 + (double)g.M * g.N * 4.0 * 3.0 / 3e6;  // memset + atomics + finalize
+      if (t < best_t) { best_t = t; best = {bn, splits}; }
+    }
+  }
+  return best;
+}
+}  // namespace
+
+int qgemm_tc_plan_splits(const GemmArgs& g, int sm_count) {
+  if (!qgemm_tc_supported(g) || qgemm_tc2_wanted(g, sm_count)) return 1;
+  return plan_small(g, sm_count, true).splits;
+}
+
+cudaError_t launch_qgemm_tc(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
+  if (qgemm_tc2_wanted(g, sm_count)) return launch_qgemm_tc2(g, sm_count, s, why);
+  GemmArgs a = g;
+  Plan p;
+  if (g.splitk_acc && g.k_splits > 1) {
+    // the caller sized and cleared the accumulator for this many slices: honour it
+    p = plan_small(g, sm_count, true);
+    if (p.splits != g.k_splits) {
+      p = plan_small(g, sm_count, false);
+      p.splits = g.k_splits;
+    }
+  } else {
+    p = plan_small(g, sm_count, false);
+  }
+  a.k_splits = p.splits;
+  switch (p.bn) {
+    case 256: return launch_t<256>(a, sm_count, s, why);
+    case 128: return launch_t<128>(a, sm_count, s, why);
+    case 64: return launch_t<64>(a, sm_count, s, why);
+    default: return launch_t<32>(a, sm_count, s, why);
+  }
 }
 
 }  // namespace sdq

@@ -31,6 +31,7 @@ struct Workspace {
   float* a_scale = nullptr; size_t a_scale_bytes = 0;
   float* a_stage = nullptr; size_t a_stage_bytes = 0;
   float* out_stage = nullptr; size_t out_stage_bytes = 0;
+  int32_t* acc = nullptr; size_t acc_bytes = 0;   // split-K partial sums
 };
 
 struct Context {
@@ -95,6 +96,18 @@ int run_gemm(const Weight& w, const int8_t* aq, const float* a_scale, int64_t M,
   g.status = g_ctx->status;
   if (!(flags & SDQ_FORCE_SIMT) && qgemm_tc_supported(g)) {
     std::string why;
+    const int splits = qgemm_tc_plan_splits(g, g_ctx->sm_count);
+    if (splits > 1) {
+      Workspace* ws;
+      {
+        std::lock_guard<std::mutex> lk(g_ctx->mu);
+        ws = &g_ctx->ws[s];
+      }
+      if (int rc = grow(&ws->acc, &ws->acc_bytes, (size_t)M * w.N * 4)) return rc;
+      SDQ_CUDA(cudaMemsetAsync(ws->acc, 0, (size_t)M * w.N * 4, s));
+      g.splitk_acc = ws->acc;
+      g.k_splits = splits;
+    }
     cudaError_t e = launch_qgemm_tc(g, g_ctx->sm_count, s, &why);
     if (e != cudaSuccess) return fail(SDQ_ERR_CUDA, why.empty() ? std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e) : why);
     return SDQ_OK;
@@ -164,7 +177,7 @@ int sdq_shutdown(void) {
     if (w.live && w.owned) { cudaFree(const_cast<int8_t*>(w.q)); cudaFree(const_cast<float*>(w.scale)); }
   for (auto& kv : g_ctx->ws) {
     cudaFree(kv.second.aq); cudaFree(kv.second.a_scale);
-    cudaFree(kv.second.a_stage); cudaFree(kv.second.out_stage);
+    cudaFree(kv.second.a_stage); cudaFree(kv.second.out_stage); cudaFree(kv.second.acc);
   }
   for (int i = 0; i < 2; i++) {
     cudaFree(g_ctx->pa[i]); cudaFree(g_ctx->py[i]);

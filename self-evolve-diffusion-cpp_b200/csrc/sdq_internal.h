@@ -42,6 +42,8 @@ struct GemmArgs {
   int64_t M, N, K;
   uint32_t flags;         // SDQ_GELU_TANH
   int* status;            // device word: 0 ok, else a code written by a kernel that gave up
+  int32_t* splitk_acc = nullptr;  // [M,N] zeroed int32 sums when K is split, else null
+  int k_splits = 1;               // >1 only together with splitk_acc
 };
 
 // Portable CUDA-core kernel (any M, N, K): qgemm_simt.cu
@@ -51,6 +53,9 @@ cudaError_t launch_qgemm_simt(const GemmArgs& g, cudaStream_t s);
 bool qgemm_tc_supported(const GemmArgs& g);
 // Returns cudaSuccess or the launch error; `why` receives text on tensor-map failures.
 cudaError_t launch_qgemm_tc(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why);
+// K slices the planner wants for this problem (1 = none); the caller then provides a
+// zeroed [M,N] int32 accumulator in g.splitk_acc and sets g.k_splits to this value.
+int qgemm_tc_plan_splits(const GemmArgs& g, int sm_count);
 // One-time set-up (driver entry point lookup, max-shared-memory attributes).
 int qgemm_tc_setup(std::string* why);
 

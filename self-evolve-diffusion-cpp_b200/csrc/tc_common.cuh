@@ -88,6 +88,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// Bulk tensor reduction: adds a 32x32 int32 box from shared memory into global memory
+// (element-wise integer add performed by the memory system; clipped like a store).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::
+                   "l"(reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void st_shared_v4_b32(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                                 uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -280,12 +293,13 @@ inline bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K
 }
 
 // out [M,N] fp32 row-major, box = 32 rows x 32 columns (128 bytes), 128-byte swizzle.
-inline bool make_out_tmap(CUtensorMap* map, float* out, int64_t M, int64_t N, std::string* why) {
+inline bool make_out_tmap(CUtensorMap* map, void* out, int64_t M, int64_t N, std::string* why,
+                          CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32) {
   cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
   cuuint64_t strides[1] = {(cuuint64_t)N * 4};
   cuuint32_t box[2] = {32, 32};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr,
+  CUresult r = g_encode(map, dt, 2, out, dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {

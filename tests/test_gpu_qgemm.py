@@ -53,6 +53,7 @@ def test_golden_digests(sdq, oracle, gold):
     (1, 16, 1), (1, 256, 3072), (5, 48, 36), (128, 128, 256), (129, 144, 257), (192, 3072, 3072),
     (200, 512, 384), (256, 1024, 192), (300, 272, 1000), (1000, 64, 4100), (2048, 512, 256),
     (2500, 3072, 192), (4096, 256, 3072), (19072, 128, 512), (512, 4096, 3072),
+    (192, 14336, 3072), (100, 8192, 200), (64, 14336, 1024),          # large K, few rows: K is split
 ])
 def test_intermediates_match_oracle(sdq, oracle, M, K, N):
     """aq, a_scale, int32 accumulators and fp32 outputs, all exact, over every tile width."""
@@ -67,6 +68,22 @@ def test_intermediates_match_oracle(sdq, oracle, M, K, N):
     assert bits_equal(acc, acc_c)
     assert bits_equal(out, oracle.rescale(acc_c, as_c, ws))
     sdq.weight_release(w)
+
+
+def test_split_k_host_path_matches_oracle(sdq, oracle):
+    """The few-rows / long-K shapes take the split-K plan (int32 partial sums added with
+    atomics, then a finalize pass); bias and the host-pointer path included."""
+    rng = np.random.default_rng(77)
+    for (M, K, N) in [(192, 14336, 3072), (64, 14336, 512)]:
+        A = rng.standard_normal((M, K)).astype(np.float32)
+        wq, ws = packed_weights(rng, N, K, oracle)
+        b = (rng.standard_normal(N) * 0.02).astype(np.float32)
+        w = sdq.weight_upload(wq, ws)
+        want = oracle.qgemm(A, wq, ws)
+        assert bits_equal(sdq.qgemm_host(w, A), want)
+        assert bits_equal(sdq.qgemm_host(w, A), want)          # the accumulator is cleared per call
+        assert bits_equal(sdq.qgemm_host(w, A, bias=b), oracle.bias_add(want, b))
+        sdq.weight_release(w)
 
 
 def test_extreme_accumulators(sdq, oracle):
