@@ -32,9 +32,9 @@ D_MODEL, D_FFN, M_720P = 3072, 14336, 27280
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 INT8_NOMINAL_TOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (the
-# 3072->14336 GEMM at M=27280), from the ncu capture summarised under profiles/; None
-# until that capture exists.
-NCU_TRAFFIC_BYTES = None
+# 3072->14336 GEMM at M=27280: 688.1 MB read + 1513.6 MB written), from the one-pass ncu
+# launch list summarised in profiles/ffn_pair_720p_launch_list.md.
+NCU_TRAFFIC_BYTES = 2201607680
 
 
 def parse_args():
@@ -330,8 +330,8 @@ def run_b200(args):
     dom_ops = 2.0 * M * D_MODEL * D_FFN
     achieved = dom_ops / (kern_ms[dom] * 1e-3) / 1e12
     peak = float(pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
-    roofline = {"bound": "tensor", "kernel": "qgemm_tc_kernel<256> " + dom, "achieved": achieved, "peak": peak,
-                "unit": "TFLOP/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+    roofline = {"bound": "tensor", "kernel": "qgemm_tc2_kernel " + dom, "achieved": achieved, "peak": peak,
+                "unit": "TFLOP/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES if M == M_720P else None,
                 "peak_kind": "dense bf16 sustained, of " + pk_kind + " (no int8 figure is measured on this pool)",
                 "frac_of_nominal_int8_4500": achieved / INT8_NOMINAL_TOPS,
                 "algorithmic_bytes": gemm_bytes(M, D_MODEL, D_FFN),
