@@ -437,6 +437,44 @@ def run_sweep(args):
             del A, out
         s.weight_release(w)
         del wb, q, sc
+    # column split + all-gather at the largest token count: every rank holds N/world weight
+    # rows and all of A, computes out[:, n0:n1]; the blocks are all-gathered (NCCL) into [M, N]
+    nsplit = []
+    if world > 1:
+        par = pkg.parallel
+        Mtot = SWEEP_M[-1]
+        for (K, N) in SWEEP_KN:
+            n0, n1 = pkg.sharding.col_shard(N, world, rank)
+            wb = (torch.randn(n1 - n0, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            q = torch.empty(n1 - n0, K, device=dev, dtype=torch.int8)
+            sc = torch.empty(n1 - n0, device=dev, dtype=torch.float32)
+            s._ck(lib.sdq_quantize_rows(wb.data_ptr(), S.BF16, n1 - n0, K, S.MODE_PACKER, q.data_ptr(),
+                                        sc.data_ptr(), 0, sp))
+            w = s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), n1 - n0, K)
+            A = torch.randn(Mtot, K, device=dev, generator=g)
+            block = torch.empty(Mtot, n1 - n0, device=dev)
+            tg, ta = [], []
+            for it in range(1 + args.steps):
+                flush.zero_()
+                dist.barrier()
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                e0.record(stream)
+                s._ck(lib.sdq_qgemm(w, A.data_ptr(), Mtot, block.data_ptr(), None, 0, sp))
+                e1.record(stream)
+                full = par.allgather_columns(block, N)
+                e2.record(stream)
+                torch.cuda.synchronize()
+                if it >= 1:
+                    tg.append(e0.elapsed_time(e1))
+                    ta.append(e1.elapsed_time(e2))
+                del full
+            t = torch.tensor([float(np.median(tg)), float(np.median(ta))], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            nsplit.append({"K": K, "N": N, "M": Mtot, "gemm_ms": float(t[0]), "allgather_ms": float(t[1]),
+                           "gathered_bytes_per_rank": 4 * Mtot * N * (world - 1) // world,
+                           "tops_total": 2.0 * Mtot * N * K / (float(t[0] + t[1]) * 1e-3) / 1e12})
+            s.weight_release(w)
+            del wb, q, sc, A, block
     s.sync(sp)
     if rank == 0:
         total_ops = sum(2.0 * p["M"] * p["N"] * p["K"] for p in points)
@@ -449,7 +487,7 @@ def run_sweep(args):
                                      "l2": "flushed with a 256 MiB write before every timed call",
                                      "peaks": "bound = max(2MNK / bf16 sustained " + pk_kind +
                                               ", bytes / HBM copy " + pk_kind + ")"},
-                          "sweep": points}))
+                          "sweep": points, "column_split_allgather": nsplit}))
     if world > 1:
         dist.destroy_process_group()
     return 0
