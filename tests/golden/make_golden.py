@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Regenerates the committed golden fixtures in this directory.
 
-Run in a checkout that has the reference tree mounted (REF, default
-/root/reference) and oracle/_ref built:  python tests/golden/make_golden.py
+Run in a checkout that has the reference tree mounted (its location is taken from
+the REF environment variable) and oracle/_ref built:  python tests/golden/make_golden.py
 
 It drives the REFERENCE's own code -- tools/quantize/pack_sdcpp.py (imported and
 run as a script) and sd::qgemm / sd::quantize_rowwise compiled from source --

@@ -1,4 +1,4 @@
-"""GPU: BASELINE-sized shapes.  The oracle checks sampled rows bit-for-bit (rows of a
+"""GPU: Full-size shapes of the benchmark configurations.  The oracle checks sampled rows bit-for-bit (rows of a
 quantized linear are independent), and whole outputs are checked through
 properties that need no oracle: splitting rows or columns, or permuting rows,
 must not change a single bit.

@@ -1,7 +1,7 @@
 """GPU: sd::qgemm through the C ABI is bit-identical to the reference.
 
 Small cases are compared whole against the golden fixtures (outputs of the
-reference's own compiled sd::qgemm) and the oracle; BASELINE-sized cases are
+reference's own compiled sd::qgemm) and the oracle; full-size cases are
 compared on sampled rows (rows are independent) and through size-independent
 properties: row-split and column-split invariance, row permutation.
 Tolerance: 0 (bit-exact) for int8 bytes, int32 accumulators and fp32 outputs;
