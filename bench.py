@@ -468,11 +468,31 @@ def run_sweep(args):
                     tg.append(e0.elapsed_time(e1))
                     ta.append(e1.elapsed_time(e2))
                 del full
-            t = torch.tensor([float(np.median(tg)), float(np.median(ta))], device=dev, dtype=torch.float64)
+            # fused form: the GEMM epilogue stores the block into every rank's [M, N] buffer;
+            # timed to the end of a 1-element all-reduce that orders the ranks on the stream
+            shared = par.SharedOutput(s, Mtot * N * 4)
+            tok = torch.zeros(1, device=dev)
+            tf = []
+            for it in range(1 + args.steps):
+                flush.zero_()
+                dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                par.qgemm_colsplit_fused(s, w, A.data_ptr(), Mtot, N, shared, stream=sp)
+                dist.all_reduce(tok)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                if it >= 1:
+                    tf.append(e0.elapsed_time(e1))
+            shared.close()
+            t = torch.tensor([float(np.median(tg)), float(np.median(ta)), float(np.median(tf))], device=dev,
+                             dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             nsplit.append({"K": K, "N": N, "M": Mtot, "gemm_ms": float(t[0]), "allgather_ms": float(t[1]),
+                           "fused_peer_store_ms": float(t[2]),
                            "gathered_bytes_per_rank": 4 * Mtot * N * (world - 1) // world,
-                           "tops_total": 2.0 * Mtot * N * K / (float(t[0] + t[1]) * 1e-3) / 1e12})
+                           "tops_gemm_then_allgather": 2.0 * Mtot * N * K / (float(t[0] + t[1]) * 1e-3) / 1e12,
+                           "tops_fused": 2.0 * Mtot * N * K / (float(t[2]) * 1e-3) / 1e12})
             s.weight_release(w)
             del wb, q, sc, A, block
     s.sync(sp)

@@ -139,6 +139,26 @@ SDQ_API int sdq_qgemm_prequantized(sdq_weight_t w, const int8_t* aq_dev, const f
                            int64_t M, float* out_dev, const float* bias_dev,
                            int32_t* acc_dump_dev, uint32_t flags, void* stream);
 
+/* ---- one linear split by output columns over the GPUs of a box ----
+ * No counterpart in the reference (it is single-process CPU code); columns of sd::qgemm's
+ * output are independent (each weight row has its own scale, src/core/qgemm.cpp:123-135), so
+ * a rank that holds weight rows [col0, col0+Nw) computes out[:, col0:col0+Nw] exactly.
+ * sdq_qgemm_colsplit fuses the exchange into the GEMM: the epilogue writes the finished
+ * block straight into `n_outs` destination buffers, each a full [M, N_total] fp32 matrix --
+ * this GPU's own and its peers' (addresses from sdq_ipc_open; the stores cross NVLink).
+ * When every rank has made the call and the ranks have synchronised (any barrier after the
+ * stream work), every buffer holds the complete row-major result: an all-gather without a
+ * separate collective or re-layout pass.  col0 must be a multiple of 32 and Nw a multiple
+ * of 32 unless the block is the last one; N_total % 4 == 0; destinations 16-byte aligned.
+ * sdq_ipc_export/open/close exchange buffers made by sdq_malloc between the processes
+ * (64-byte CUDA IPC handles, carried by whatever channel the host program has). */
+SDQ_API int sdq_qgemm_colsplit(sdq_weight_t w_block, const float* A_dev, int64_t M, int64_t col0,
+                               int64_t N_total, float* const* outs_dev, int n_outs,
+                               const float* bias_block_dev, uint32_t flags, void* stream);
+SDQ_API int sdq_ipc_export(const void* dptr, unsigned char handle[64]);
+SDQ_API int sdq_ipc_open(const unsigned char handle[64], void** dptr);
+SDQ_API int sdq_ipc_close(void* dptr);
+
 /* y = fc2(gelu_tanh(fc1(x))) for one FFN -- replaces the three lines of the reference's
  * ffn_fwd that are on this path (src/model/ovi_dit.cpp:218-220: mlin fc1,
  * gelu_tanh_inplace, mlin fc2; each mlin = sd::qgemm + bias pass).  x is fp32

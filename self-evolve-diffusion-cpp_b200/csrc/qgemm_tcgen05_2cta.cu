@@ -98,10 +98,16 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       : "memory");
 }
 
+// Output tensor maps: one in the ordinary case; in the column-split multi-GPU form one per
+// destination buffer (this GPU's and each peer's), all describing [M, out_ld] fp32.
+struct OutMaps {
+  CUtensorMap m[8];
+};
+
 __global__ void __launch_bounds__(kNumThreads, 1)
     qgemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
-                     const __grid_constant__ CUtensorMap tmap_out, GemmArgs g) {
+                     const __grid_constant__ OutMaps outs, int num_outs, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // same offset in both CTAs of the pair
@@ -141,7 +147,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
-    prefetch_tmap(&tmap_out);
+    for (int i = 0; i < num_outs; i++) prefetch_tmap(&outs.m[i]);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols2);
@@ -250,7 +256,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d_hint(&tmap_out, box, (int)nc, (int)row0, stream_policy);
+            // one staged box, one bulk store per destination (peer stores cross NVLink)
+            for (int i = 0; i < num_outs; i++)
+              tma_store_2d_hint(&outs.m[i], box, (int)(g.out_col0 + nc), (int)row0, stream_policy);
             bulk_commit();
           }
         }
@@ -300,18 +308,35 @@ bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count) {
     const char* v = getenv("SDQ_TC_VARIANT");  // "1": never, "2": whenever possible
     return v ? atoi(v) : 0;
   }();
+  if (g.acc_dump) return false;
+  if (g.out_copies > 0) {
+    // every destination 16-byte aligned with a 16-byte row pitch and column offset
+    if (g.out_ld % 4 != 0 || g.out_col0 % 4 != 0) return false;
+    for (int i = 0; i < g.out_copies; i++)
+      if ((reinterpret_cast<uintptr_t>(g.out_all[i]) & 15) != 0) return false;
+    return true;  // the caller asked for the fused form; it has no other kernel
+  }
   if (forced == 1) return false;
-  if (g.N % 4 != 0 || (reinterpret_cast<uintptr_t>(g.out) & 15) != 0 || g.acc_dump) return false;
+  if (g.N % 4 != 0 || (reinterpret_cast<uintptr_t>(g.out) & 15) != 0) return false;
   const int64_t tiles = ((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((g.N + kBlockN2 - 1) / kBlockN2);
   if (forced == 2) return true;
   return tiles >= sm_count / 2;
 }
 
 cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
-  CUtensorMap ta, tb, tout;
+  CUtensorMap ta, tb;
+  OutMaps outs;
   if (!make_tmap(&ta, g.aq, g.M, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;
   if (!make_tmap(&tb, g.bq, g.N, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;  // 128-row halves
-  if (!make_out_tmap(&tout, g.out, g.M, g.N, why)) return cudaErrorInvalidValue;
+  int num_outs = 1;
+  if (g.out_copies > 0) {
+    num_outs = g.out_copies;
+    for (int i = 0; i < num_outs; i++)
+      if (!make_out_tmap(&outs.m[i], g.out_all[i], g.M, g.out_ld, why)) return cudaErrorInvalidValue;
+  } else {
+    if (!make_out_tmap(&outs.m[0], g.out, g.M, g.N, why)) return cudaErrorInvalidValue;
+  }
+  for (int i = num_outs; i < 8; i++) outs.m[i] = outs.m[0];
   const int64_t tiles = ((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((g.N + kBlockN2 - 1) / kBlockN2);
   int64_t clusters = sm_count / 2;
   if (tiles < clusters) clusters = tiles;
@@ -328,7 +353,7 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, st
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   count_launch();
-  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel, ta, tb, tout, g);
+  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel, ta, tb, outs, num_outs, g);
 }
 
 }  // namespace sdq

@@ -375,6 +375,72 @@ int sdq_qgemm(sdq_weight_t h, const float* A, int64_t M, float* out, const float
   return SDQ_OK;
 }
 
+// ---- column split across GPUs ----
+int sdq_ipc_export(const void* dptr, unsigned char handle[64]) {
+  if (int rc = need_ctx()) return rc;
+  if (!dptr || !handle) return fail(SDQ_ERR_INVALID, "sdq_ipc_export: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  SDQ_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(dptr)));
+  std::memcpy(handle, &h, 64);
+  return SDQ_OK;
+}
+
+int sdq_ipc_open(const unsigned char handle[64], void** dptr) {
+  if (int rc = need_ctx()) return rc;
+  if (!dptr || !handle) return fail(SDQ_ERR_INVALID, "sdq_ipc_open: null pointer");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  SDQ_CUDA(cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return SDQ_OK;
+}
+
+int sdq_ipc_close(void* dptr) {
+  if (int rc = need_ctx()) return rc;
+  if (dptr) SDQ_CUDA(cudaIpcCloseMemHandle(dptr));
+  return SDQ_OK;
+}
+
+int sdq_qgemm_colsplit(sdq_weight_t h, const float* A_dev, int64_t M, int64_t col0, int64_t N_total,
+                       float* const* outs_dev, int n_outs, const float* bias_dev, uint32_t flags,
+                       void* stream) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: bad weight handle");
+  if (M < 0 || col0 < 0 || N_total < col0 + w->N || n_outs < 1 || n_outs > 8 || !outs_dev)
+    return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: bad shape or destination count (1..8)");
+  if (col0 % 32 != 0 || (w->N % 32 != 0 && col0 + w->N != N_total))
+    return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: a column block must start on a multiple of 32 and, unless it is the last one, be a multiple of 32 wide");
+  if (N_total % 4 != 0 || w->K % 16 != 0)
+    return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: needs N_total % 4 == 0 and K % 16 == 0");
+  if (M == 0) return SDQ_OK;
+  if (!A_dev) return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  if (int rc = grow(&ws->aq, &ws->aq_bytes, (size_t)M * w->K)) return rc;
+  if (int rc = grow(&ws->a_scale, &ws->a_scale_bytes, (size_t)M * 4)) return rc;
+  SDQ_CUDA(launch_act_quant(A_dev, M, w->K, ws->aq, ws->a_scale, g_ctx->sm_count, s));
+  GemmArgs g;
+  g.aq = ws->aq; g.a_scale = ws->a_scale; g.bq = w->q; g.b_scale = w->scale; g.bias = bias_dev;
+  g.out = outs_dev[0]; g.acc_dump = nullptr; g.M = M; g.N = w->N; g.K = w->K;
+  g.flags = flags & SDQ_GELU_TANH; g.status = g_ctx->status;
+  g.out_col0 = col0; g.out_ld = N_total; g.out_copies = n_outs;
+  for (int i = 0; i < n_outs; i++) {
+    if (!outs_dev[i]) return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: null destination");
+    g.out_all[i] = outs_dev[i];
+  }
+  if (!qgemm_tc_supported(g) || !qgemm_tc2_wanted(g, g_ctx->sm_count))
+    return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: destinations must be 16-byte aligned");
+  std::string why;
+  cudaError_t e = launch_qgemm_tc2(g, g_ctx->sm_count, s, &why);
+  if (e != cudaSuccess) return fail(SDQ_ERR_CUDA, why.empty() ? std::string("column-split GEMM launch: ") + cudaGetErrorString(e) : why);
+  return (flags & SDQ_SYNC) ? sdq_stream_sync(stream) : SDQ_OK;
+}
+
 // ---- FFN pair ----
 // fc1 -> GELU(tanh) -> fc2 on [r0, r1) rows that are already on the device.
 static int ffn_rows_device(const Weight& w1, const float* b1, const Weight& w2, const float* b2,

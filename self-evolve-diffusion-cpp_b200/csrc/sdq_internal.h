@@ -42,6 +42,12 @@ struct GemmArgs {
   int64_t M, N, K;
   uint32_t flags;         // SDQ_GELU_TANH
   int* status;            // device word: 0 ok, else a code written by a kernel that gave up
+  // Column-split multi-GPU form: this launch computes columns [out_col0, out_col0 + N) of a
+  // wider [M, out_ld] result and writes the block into out_copies buffers (this GPU's and
+  // its peers').  out_copies == 0 is the ordinary single-output case (out, row pitch N).
+  int64_t out_col0 = 0, out_ld = 0;
+  int out_copies = 0;
+  float* out_all[8] = {};
   int32_t* splitk_acc = nullptr;  // [M,N] zeroed int32 sums when K is split, else null
   int k_splits = 1;               // >1 only together with splitk_acc
 };

@@ -80,3 +80,47 @@ def gather_rows(local_rows_block, M, group=None):
         b, e = row_shard(M, world, r)
         parts.append(gathered[r][: e - b])
     return torch.cat(parts, dim=0)
+
+
+class SharedOutput:
+    """One [M, N] fp32 result buffer per rank, each mapped into every other rank (CUDA IPC),
+    for the fused column split: a rank's GEMM epilogue stores its column block into all of
+    them, so no separate all-gather runs.  Collective: every rank of `group` constructs it."""
+
+    def __init__(self, sdq, nbytes, group=None):
+        self.sdq, self.group = sdq, group
+        self.local = sdq.alloc(nbytes)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.opened = []
+        if self.world == 1:
+            self.ptrs = [self.local.ptr]
+            return
+        handles = [None] * self.world
+        dist.all_gather_object(handles, sdq.ipc_export(self.local.ptr), group=group)
+        by_rank = {}
+        for r in range(self.world):
+            if r == self.rank:
+                by_rank[r] = self.local.ptr
+            else:
+                by_rank[r] = sdq.ipc_open(handles[r])
+                self.opened.append(by_rank[r])
+        # start with the own buffer, then the peers in ring order, so that at any moment the
+        # ranks are not all storing into the same GPU
+        self.ptrs = [by_rank[(self.rank + i) % self.world] for i in range(self.world)]
+
+    def close(self):
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)      # nobody still stores into a buffer about to go
+        for p in self.opened:
+            self.sdq.ipc_close(p)
+        self.opened = []
+        self.local.free()
+
+
+def qgemm_colsplit_fused(sdq, w_block, A_ptr, M, N_total, shared, bias_ptr=None, flags=0, stream=None):
+    """This rank's column block of the linear, stored by the GEMM epilogue into every rank's
+    buffer of `shared`.  The result is complete on a rank once all ranks' calls have finished:
+    follow with a barrier (or any collective) before reading shared.local."""
+    n0, _ = col_shard(N_total, shared.world, shared.rank)
+    sdq.qgemm_colsplit(w_block, A_ptr, M, n0, N_total, shared.ptrs, bias_ptr, flags, stream)

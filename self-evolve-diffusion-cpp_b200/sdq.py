@@ -73,6 +73,11 @@ _SIGS = {
     "sdq_quantize_activations": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sdq_qgemm_prequantized": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_qgemm_colsplit": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_void_p),
+                                     C.c_int, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sdq_ipc_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "sdq_ipc_close": (C.c_int, [C.c_void_p]),
     "sdq_ffn_pair": (C.c_int, [C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64,
                                C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_static_scratch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
@@ -292,6 +297,24 @@ class Sdq:
                                                  dacc.ptr, flags, None))
         return (dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,)),
                 dacc.to_numpy(np.int32, (M, N)), dout.to_numpy(np.float32, (M, N)))
+
+    def qgemm_colsplit(self, w, A_ptr, M, col0, N_total, out_ptrs, bias_ptr=None, flags=0, stream=None):
+        """One column block of a linear, written into every buffer of `out_ptrs` ([M, N_total] each)."""
+        arr = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+        self._ck(self.lib.sdq_qgemm_colsplit(w, A_ptr, M, col0, N_total, arr, len(out_ptrs), bias_ptr, flags, stream))
+
+    def ipc_export(self, dptr):
+        buf = C.create_string_buffer(64)
+        self._ck(self.lib.sdq_ipc_export(dptr, buf))
+        return buf.raw
+
+    def ipc_open(self, handle):
+        p = C.c_void_p()
+        self._ck(self.lib.sdq_ipc_open(C.create_string_buffer(handle, 64), C.byref(p)))
+        return p.value
+
+    def ipc_close(self, dptr):
+        self._ck(self.lib.sdq_ipc_close(dptr))
 
     def ffn_pair_host(self, w1, b1, w2, b2, x):
         """numpy in, numpy out through the chunked host-pointer pipeline of sdq_ffn_pair."""

@@ -65,6 +65,16 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         ok_cols = full[torch.from_numpy(rows).cuda()].cpu().numpy().tobytes() == want_rows.tobytes()
 
+        # the same column split with the exchange fused into the GEMM epilogue: every rank's
+        # block is stored straight into every rank's [M, N] buffer over NVLink
+        shared = par.SharedOutput(s, M * N * 4)
+        par.qgemm_colsplit_fused(s, w, dA.data_ptr(), M, N, shared, stream=sp)
+        s.sync(sp)
+        dist.barrier()
+        fused = shared.local.to_numpy(np.float32, (M, N))
+        ok_cols = ok_cols and fused.tobytes() == full.cpu().numpy().tobytes()
+        shared.close()
+
         # row split: full weights, this rank's rows; gathered only for the comparison
         wf = s.weight_upload(wq, ws)
         r0, r1 = par.local_rows(M)
