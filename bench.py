@@ -159,7 +159,7 @@ def run_reference(args):
     A, w1, w2, b1, b2 = host_problem(4096)
     t_probe, kind, cores = reference_throughput(A, w1, w2, b1, b2, probe_rows)
     # size a step so that warmup+steps take about two minutes of CPU time
-    budget = 120.0 / max(1, args.steps + args.warmup)
+    budget = float(os.environ.get("SDQ_BENCH_REF_BUDGET_S", "120")) / max(1, args.steps + args.warmup)
     rows = int(max(32, min(4096, probe_rows * budget / t_probe)))
     rows -= rows % 8
     for _ in range(args.warmup):

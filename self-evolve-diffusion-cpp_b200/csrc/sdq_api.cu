@@ -2,6 +2,7 @@
 // weight registry, and the dispatch of sd::qgemm's two halves onto the kernels.
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -498,7 +499,14 @@ int sdq_ffn_pair(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, const
       SDQ_CUDA(cudaEventCreateWithFlags(&c->ev_out_done[i], cudaEventDisableTiming));
     }
   }
-  const int64_t chunk = std::min<int64_t>(M, 4096);
+  // rows per chunk: small enough that the first upload and the last download (which nothing
+  // overlaps) are short, large enough that each chunk's GEMMs still fill the GPU
+  static const int64_t chunk_rows = [] {
+    const char* v = std::getenv("SDQ_FFN_CHUNK_ROWS");
+    const int64_t n = v ? std::atoll(v) : 0;
+    return n >= 128 ? n : 4096;
+  }();
+  const int64_t chunk = std::min<int64_t>(M, chunk_rows);
   for (int i = 0; i < 2; i++) {
     if (int rc = grow(&c->pa[i], &c->pa_bytes[i], (size_t)chunk * D * 4)) return rc;
     if (int rc = grow(&c->py[i], &c->py_bytes[i], (size_t)chunk * Dout * 4)) return rc;
