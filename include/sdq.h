@@ -130,6 +130,20 @@ SDQ_API int sdq_qgemm(sdq_weight_t w, const float* A, int64_t M, float* out, con
 SDQ_API int sdq_quantize_activations(const float* A_dev, int64_t M, int64_t K, int8_t* aq_dev,
                              float* a_scale_dev, void* stream);
 
+/* The step the reference runs in front of most DiT linears, fused with the first half of
+ * sd::qgemm: LayerNorm without affine parameters (blk::layernorm, src/model/blocks.cpp:18-43),
+ * the per-channel modulation h = ln * (1 + scale[c]) + shift[c] (mod_rows,
+ * src/model/ovi_dit.cpp:162-173; call sites :205-217) and the activation quantization
+ * (src/core/qgemm.cpp:82-96), in one pass over x: fp32 `h` is never written unless
+ * `h_out_dev` (fp32 [M,K], may be NULL) asks for it.  Feed aq / a_scale to
+ * sdq_qgemm_prequantized.  The row mean and variance are tree sums, so h matches the CPU to
+ * rounding error rather than bit for bit (an int8 value may differ by one step); the linear's
+ * output stays within the 1e-3 bound.  K % 4 == 0, K <= 16384, pointers 16-byte aligned. */
+SDQ_API int sdq_layernorm_mod_quantize(const float* X_dev, int64_t M, int64_t K,
+                                       const float* shift_dev, const float* scale_dev, float eps,
+                                       int8_t* aq_dev, float* a_scale_dev, float* h_out_dev,
+                                       void* stream);
+
 /* Second half of sd::qgemm (src/core/qgemm.cpp:98-138) on activations that are
  * already quantized: lets a caller quantize x once and run the q, k and v
  * projections on it (the reference re-quantizes x three times,

@@ -45,7 +45,7 @@ class Oracle:
         for name in ("orc_act_quant_rows", "orc_dot_s32", "orc_rescale", "orc_qgemm",
                      "orc_bias_add", "orc_gelu_tanh", "orc_quantize_rowwise",
                      "orc_quant_rows_packer", "orc_dequant_rows", "orc_f32_to_bf16",
-                     "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads"):
+                     "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads", "orc_layernorm_mod"):
             getattr(L, name).restype = None
 
     def threads(self):
@@ -119,6 +119,13 @@ class Oracle:
         self.lib.orc_dequant_rows(_ptr(q), _ptr(scale), i64(rows), i64(last), _ptr(w))
         return w
 
+    def layernorm_mod(self, x, shift, scale, eps=1e-6):
+        x, shift, scale = _c(x, np.float32), _c(shift, np.float32), _c(scale, np.float32)
+        M, K = x.shape
+        y = np.empty((M, K), np.float32)
+        self.lib.orc_layernorm_mod(_ptr(x), i64(M), i64(K), _ptr(shift), _ptr(scale), C.c_float(eps), _ptr(y))
+        return y
+
     def f32_to_bf16(self, x):
         x = _c(x, np.float32)
         o = np.empty(x.shape, np.uint16)
@@ -191,6 +198,14 @@ class Reference:
         o = np.empty(x.shape, np.uint16)
         self.lib.sdref_to_bf16(_ptr(x), _ptr(o), i64(x.size))
         return o
+
+    def layernorm(self, x, eps=1e-6):
+        x = _c(x, np.float32)
+        M, K = x.shape
+        y = np.empty((M, K), np.float32)
+        self.lib.sdref_layernorm.restype = None
+        self.lib.sdref_layernorm(_ptr(x), i64(M), i64(K), C.c_float(eps), _ptr(y))
+        return y
 
     def load_sdcpp_listing(self, path):
         """(count, listing) or raises RuntimeError with the loader's message."""

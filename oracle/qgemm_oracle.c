@@ -301,3 +301,34 @@ void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t
   for (int64_t i = 0; i < rows; i++)
     for (int64_t k = 0; k < last; k++) w[i * last + k] = (float)q[i * last + k] * scale[i];
 }
+
+/* src/model/blocks.cpp:18-43 (w = b = null) then src/model/ovi_dit.cpp:162-173. */
+typedef struct { const float* x; const float* shift; const float* scale; float* y; int64_t K; float eps; } ln_t;
+
+static void ln_range(int64_t b, int64_t e, void* p) {
+  ln_t* j = (ln_t*)p;
+  const int64_t N = j->K;
+  for (int64_t i = b; i < e; i++) {
+    const float* r = j->x + i * N;
+    float mu = 0.0f;
+    for (int64_t k = 0; k < N; k++) mu += r[k];
+    mu /= (float)N;
+    float var = 0.0f;
+    for (int64_t k = 0; k < N; k++) {
+      float d = r[k] - mu;
+      var += d * d;
+    }
+    const float inv = 1.0f / sqrtf(var / (float)N + j->eps);
+    float* o = j->y + i * N;
+    for (int64_t k = 0; k < N; k++) {
+      const float ln = (r[k] - mu) * inv * 1.0f + 0.0f;
+      o[k] = ln * (1.0f + j->scale[k]) + j->shift[k];
+    }
+  }
+}
+
+void orc_layernorm_mod(const float* x, int64_t M, int64_t K, const float* shift,
+                       const float* scale, float eps, float* y) {
+  ln_t j = {x, shift, scale, y, K, eps};
+  par_rows(M, ln_range, &j);
+}

@@ -56,6 +56,12 @@ void orc_quant_rows_packer(const float* x, int64_t rows, int64_t last, int8_t* q
 /* w = q * scale[row]  (src/model/ovi_dit.cpp:53-63). */
 void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last, float* w);
 
+/* LayerNorm without affine parameters followed by the per-channel modulation
+ * y = ln(x) * (1 + scale[c]) + shift[c]   (src/model/blocks.cpp:18-43 with w = b = null,
+ * src/model/ovi_dit.cpp:162-173).  Sums run left to right in fp32 as the reference's do. */
+void orc_layernorm_mod(const float* x, int64_t M, int64_t K, const float* shift,
+                       const float* scale, float eps, float* y);
+
 /* Threads used by the loops above (OpenMP); <=0 restores the default. */
 void orc_set_threads(int n);
 int orc_threads(void);

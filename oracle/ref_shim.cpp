@@ -7,6 +7,7 @@
 // (src/core/tensor.h:48-61, src/serde/sdcpp.h:18-19).
 #include "core/tensor.h"
 #include "serde/sdcpp.h"
+#include "model/blocks.h"
 
 #include <algorithm>
 #include <cstdio>
@@ -55,6 +56,15 @@ void sdref_quantize_rowwise(const float* W, int64_t N, int64_t K, int8_t* q, flo
   sd::quantize_rowwise(w, wq, sc);
   std::memcpy(q, wq.data, wq.nbytes);
   std::memcpy(scale, sc.data, sc.nbytes);
+}
+
+// blk::layernorm without affine parameters (src/model/blocks.cpp:18-43), as ffn_fwd and
+// block_self_fwd call it (src/model/ovi_dit.cpp:205-217).
+void sdref_layernorm(const float* x, int64_t M, int64_t K, float eps, float* y) {
+  sd::Tensor t = view(x, {M, K}, sd::DType::F32, (size_t)M * K * 4);
+  sd::Tensor o;
+  sd::blk::layernorm(t, o, nullptr, nullptr, eps);
+  std::memcpy(y, o.data, o.nbytes);
 }
 
 void sdref_to_bf16(const float* src, uint16_t* dst, int64_t n) {

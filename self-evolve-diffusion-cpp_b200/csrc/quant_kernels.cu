@@ -110,6 +110,93 @@ __global__ void __launch_bounds__(kThreads) act_quant_generic(const float* __res
   }
 }
 
+// ---- LayerNorm + modulation + activation quantization in one pass ----
+// The step in front of most DiT linears (reference src/model/blocks.cpp:18-43 without affine
+// parameters, then mod_rows, src/model/ovi_dit.cpp:162-173, then the first half of sd::qgemm):
+//   ln = (x - mean) * rsqrt(var + eps);  h = ln * (1 + scale[c]) + shift[c];  aq = quantize(h)
+// Fusing them deletes the fp32 round trip of `h` (4 bytes/element written and read again).
+// The means and variances are block-wide tree sums, not the CPU's left-to-right sums, so
+// `h` agrees with the CPU to rounding error (not bit for bit) and an int8 value can differ
+// by one step where h lands on a rounding boundary.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < kThreads / 32) ? red[lane] : 0.0f;
+  return warp_sum(r);
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __restrict__ X, int64_t M,
+                                                              int64_t K, const float* __restrict__ shift,
+                                                              const float* __restrict__ scale, float eps,
+                                                              int8_t* __restrict__ aq,
+                                                              float* __restrict__ a_scale,
+                                                              float* __restrict__ h_out) {
+  __shared__ float red[kThreads / 32];
+  const int k4 = (int)(K >> 2);
+  const float inv_n = 1.0f / (float)K;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float4* src = reinterpret_cast<const float4*>(X + row * K);
+    float4 v[VPT];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < k4) {
+        v[i] = ld_stream(src + idx);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      }
+    }
+    const float mu = block_sum(s, red) * inv_n;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < k4) {
+        const float a = v[i].x - mu, b = v[i].y - mu, c = v[i].z - mu, d = v[i].w - mu;
+        q += (a * a + b * b) + (c * c + d * d);
+      }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(q, red) * inv_n + eps);
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < k4) {
+        const float4 sc = __ldg(reinterpret_cast<const float4*>(scale) + idx);
+        const float4 sh = __ldg(reinterpret_cast<const float4*>(shift) + idx);
+        v[i].x = __fadd_rn(__fmul_rn(__fmul_rn(v[i].x - mu, inv), 1.0f + sc.x), sh.x);
+        v[i].y = __fadd_rn(__fmul_rn(__fmul_rn(v[i].y - mu, inv), 1.0f + sc.y), sh.y);
+        v[i].z = __fadd_rn(__fmul_rn(__fmul_rn(v[i].z - mu, inv), 1.0f + sc.z), sh.z);
+        v[i].w = __fadd_rn(__fmul_rn(__fmul_rn(v[i].w - mu, inv), 1.0f + sc.w), sh.w);
+        mx = fold_abs(fold_abs(fold_abs(fold_abs(mx, v[i].x), v[i].y), v[i].z), v[i].w);
+        if (h_out) reinterpret_cast<float4*>(h_out + row * K)[idx] = v[i];
+      }
+    }
+    mx = block_max(mx, red);
+    float sc = __fdiv_rn(mx, 127.0f);
+    if (sc == 0.0f) sc = 1.0f;
+    if (threadIdx.x == 0) a_scale[row] = sc;
+    const float qinv = __fdiv_rn(1.0f, sc);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(aq + row * K);
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < k4)
+        dst[idx] = pack4(act_round(__fmul_rn(v[i].x, qinv)), act_round(__fmul_rn(v[i].y, qinv)),
+                         act_round(__fmul_rn(v[i].z, qinv)), act_round(__fmul_rn(v[i].w, qinv)));
+    }
+  }
+}
+
 // ---- weights ----
 template <int DT>
 __device__ __forceinline__ float load_src(const void* p, int64_t i);
@@ -327,6 +414,28 @@ cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, f
   } else {
     act_quant_generic<<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const float* shift,
+                                const float* scale, float eps, int8_t* aq, float* a_scale,
+                                float* h_out, int sm_count, cudaStream_t s) {
+  if (M <= 0 || K <= 0) return cudaSuccess;
+  const int64_t per_thread = (K / 4 + kThreads - 1) / kThreads;
+  const bool ok = (K % 4 == 0) && per_thread <= 16 && ((reinterpret_cast<uintptr_t>(X) & 15) == 0) &&
+                  ((reinterpret_cast<uintptr_t>(shift) & 15) == 0) &&
+                  ((reinterpret_cast<uintptr_t>(scale) & 15) == 0) &&
+                  ((reinterpret_cast<uintptr_t>(aq) & 3) == 0) &&
+                  (!h_out || (reinterpret_cast<uintptr_t>(h_out) & 15) == 0);
+  if (!ok) return cudaErrorInvalidValue;
+  int64_t blocks = M < (int64_t)sm_count * 8 ? M : (int64_t)sm_count * 8;
+  count_launch();
+  if (per_thread <= 3)
+    ln_mod_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out);
+  else if (per_thread <= 8)
+    ln_mod_quant_regs<8><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out);
+  else
+    ln_mod_quant_regs<16><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out);
   return cudaGetLastError();
 }
 

@@ -323,6 +323,22 @@ int sdq_quantize_activations(const float* A_dev, int64_t M, int64_t K, int8_t* a
   return SDQ_OK;
 }
 
+int sdq_layernorm_mod_quantize(const float* X_dev, int64_t M, int64_t K, const float* shift_dev,
+                               const float* scale_dev, float eps, int8_t* aq_dev,
+                               float* a_scale_dev, float* h_out_dev, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (M < 0 || K < 0) return fail(SDQ_ERR_INVALID, "sdq_layernorm_mod_quantize: negative shape");
+  if (M == 0 || K == 0) return SDQ_OK;
+  if (!X_dev || !shift_dev || !scale_dev || !aq_dev || !a_scale_dev)
+    return fail(SDQ_ERR_INVALID, "sdq_layernorm_mod_quantize: null pointer");
+  cudaError_t e = launch_ln_mod_quant(X_dev, M, K, shift_dev, scale_dev, eps, aq_dev, a_scale_dev,
+                                      h_out_dev, g_ctx->sm_count, (cudaStream_t)stream);
+  if (e == cudaErrorInvalidValue)
+    return fail(SDQ_ERR_INVALID, "sdq_layernorm_mod_quantize: needs K % 4 == 0, K <= 16384 and 16-byte aligned pointers");
+  SDQ_CUDA(e);
+  return SDQ_OK;
+}
+
 int sdq_qgemm_prequantized(sdq_weight_t h, const int8_t* aq_dev, const float* a_scale_dev,
                            int64_t M, float* out_dev, const float* bias_dev,
                            int32_t* acc_dump_dev, uint32_t flags, void* stream) {

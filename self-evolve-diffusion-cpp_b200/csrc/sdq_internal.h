@@ -24,6 +24,11 @@ void count_launch(int n = 1);
 // aq int8 [M,K], a_scale f32 [M]; all device pointers.
 cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, float* a_scale,
                              int sm_count, cudaStream_t s);
+// LayerNorm (no affine) + modulation + activation quantization; h_out (fp32 [M,K]) optional.
+// cudaErrorInvalidValue when K % 4 != 0, K > 16384 or a pointer is not 16-byte aligned.
+cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const float* shift,
+                                const float* scale, float eps, int8_t* aq, float* a_scale,
+                                float* h_out, int sm_count, cudaStream_t s);
 // src_dtype SDQ_F32/BF16/F16, mode SDQ_MODE_*; all device pointers.
 cudaError_t launch_quantize_rows(const void* src, int src_dtype, int64_t rows, int64_t last,
                                  int mode, int8_t* q, float* scale, int sm_count, cudaStream_t s);

@@ -71,6 +71,8 @@ _SIGS = {
     "sdq_weight_release": (C.c_int, [C.c_uint64]),
     "sdq_qgemm": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_quantize_activations": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sdq_layernorm_mod_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_float,
+                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sdq_qgemm_prequantized": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_colsplit": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_void_p),
@@ -281,6 +283,20 @@ class Sdq:
         self._ck(self.lib.sdq_quantize_activations(dA.ptr, M, K, dq.ptr, ds.ptr, None))
         self.sync()
         return dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,))
+
+    def layernorm_mod_quantize(self, X, shift, scale, eps=1e-6, want_h=False):
+        """numpy [M,K] -> (aq, a_scale[, h]) through the fused LayerNorm+modulation+quantize kernel."""
+        X = np.ascontiguousarray(X, np.float32)
+        M, K = X.shape
+        dX, dsh, dsc = self.to_device(X), self.to_device(np.ascontiguousarray(shift, np.float32)), \
+            self.to_device(np.ascontiguousarray(scale, np.float32))
+        dq, ds = self.alloc(M * K), self.alloc(M * 4)
+        dh = self.alloc(M * K * 4) if want_h else None
+        self._ck(self.lib.sdq_layernorm_mod_quantize(dX.ptr, M, K, dsh.ptr, dsc.ptr, eps, dq.ptr, ds.ptr,
+                                                     dh.ptr if dh else None, None))
+        self.sync()
+        out = (dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,)))
+        return out + (dh.to_numpy(np.float32, (M, K)),) if want_h else out
 
     def qgemm_debug(self, w, A, bias=None, gelu=False, force_simt=False):
         """Both halves with every intermediate returned: (aq, a_scale, acc, out)."""

@@ -8,7 +8,7 @@ import os
 import numpy as np
 import pytest
 
-from util import bits_equal, weights_bf16
+from util import bits_equal, max_rel_err, packed_weights, weights_bf16
 
 pytestmark = pytest.mark.gpu
 
@@ -117,3 +117,34 @@ def test_dequant_rows(sdq, oracle):
     W = rng.uniform(-1, 1, (37, 513)).astype(np.float32)
     qq, ss = sdq.quantize_rows(W, 0, 1)
     assert np.all(np.abs(sdq.dequant_rows(qq, ss) - W) < ss[:, None])
+
+
+@pytest.mark.parametrize("M,K", [(300, 3072), (64, 14336), (1000, 512)])
+def test_fused_layernorm_modulation_quantize(sdq, pkg, oracle, M, K):
+    """LayerNorm + modulation + activation quantization in one kernel.  The row sums are tree
+    sums while the CPU adds K fp32 values left to right (whose own rounding error grows with K),
+    so h is compared under a tolerance -- 5e-5 of the row's max -- and an int8 value may differ
+    by one step on a rounding boundary; the linear fed with it stays inside the 1e-3 bound."""
+    rng = np.random.default_rng(M + K)
+    x = (rng.standard_normal((M, K)) * 2 + 0.3).astype(np.float32)
+    shift = (rng.standard_normal(K) * 0.5).astype(np.float32)
+    scale = (rng.standard_normal(K) * 0.1).astype(np.float32)
+    aq, a_s, h = sdq.layernorm_mod_quantize(x, shift, scale, 1e-6, want_h=True)
+    h_c = oracle.layernorm_mod(x, shift, scale, 1e-6)
+    aq_c, as_c = oracle.act_quant_rows(h_c)
+    assert np.max(np.abs(h - h_c) / np.max(np.abs(h_c), axis=1, keepdims=True)) < 5e-5
+    assert np.max(np.abs(a_s - as_c) / as_c) < 5e-5
+    diff = np.abs(aq.astype(np.int32) - aq_c.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 2e-2
+    # the quantization itself is exact given the kernel's own h
+    aq_h, as_h = oracle.act_quant_rows(h)
+    assert bits_equal(aq, aq_h) and bits_equal(a_s, as_h)
+    # end to end through the linear: within 1e-3 of the CPU chain
+    N = 256
+    wq, ws = packed_weights(rng, N, K, oracle)
+    w = sdq.weight_upload(wq, ws)
+    dq, ds, dout = sdq.to_device(aq), sdq.to_device(a_s), sdq.alloc(M * N * 4)
+    sdq._ck(sdq.lib.sdq_qgemm_prequantized(w, dq.ptr, ds.ptr, M, dout.ptr, None, None, pkg.sdq.SYNC, None))
+    got = dout.to_numpy(np.float32, (M, N))
+    assert max_rel_err(got, oracle.qgemm(h_c, wq, ws)) < 1e-3
+    sdq.weight_release(w)

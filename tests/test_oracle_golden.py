@@ -106,6 +106,19 @@ def test_live_reference_agrees(oracle, reference):
     assert bits_equal(oracle.f32_to_bf16(x), reference.to_bf16(x))
 
 
+def test_layernorm_restates_reference(oracle, reference):
+    """The step in front of the linears: blk::layernorm without affine parameters."""
+    rng = np.random.default_rng(6)
+    x = (rng.standard_normal((64, 3072)) * 3 + 0.5).astype(np.float32)
+    zero = np.zeros(3072, np.float32)
+    assert bits_equal(oracle.layernorm_mod(x, zero, zero, 1e-6), reference.layernorm(x, 1e-6))
+    # modulation: y = ln * (1 + scale) + shift, per channel (src/model/ovi_dit.cpp:162-173)
+    shift = rng.standard_normal(3072).astype(np.float32)
+    scale = (rng.standard_normal(3072) * 0.1).astype(np.float32)
+    ln = reference.layernorm(x, 1e-6)
+    assert bits_equal(oracle.layernorm_mod(x, shift, scale, 1e-6), ln * (np.float32(1) + scale) + shift)
+
+
 def test_pack_file_matches_reference_packer(oracle, gold, golden_dir, tmp_path):
     src = os.path.join(golden_dir, "tiny_model.safetensors")
     dst = str(tmp_path / "o.sdcpp")
