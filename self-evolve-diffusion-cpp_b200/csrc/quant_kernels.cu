@@ -89,6 +89,45 @@ __global__ void __launch_bounds__(kThreads) act_quant_regs(const float* __restri
   }
 }
 
+// Rows of up to 32*4*VPT elements (K = 3072, the DiT width, with VPT = 24): one WARP per
+// row, the row in the warp's registers, no block-wide barrier at all -- shuffles only -- so a
+// short row does not pay two __syncthreads per 12 KiB of traffic.
+template <int VPT>
+__global__ void __launch_bounds__(kThreads) act_quant_warp_rows(const float* __restrict__ A,
+                                                                int64_t M, int64_t K,
+                                                                int8_t* __restrict__ aq,
+                                                                float* __restrict__ a_scale) {
+  const int lane = threadIdx.x & 31;
+  const int k4 = (int)(K >> 2);
+  const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t row = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); row < M; row += warps) {
+    const float4* src = reinterpret_cast<const float4*>(A + row * K);
+    float4 v[VPT];
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = lane + i * 32;
+      if (idx < k4) {
+        v[i] = ld_stream(src + idx);
+        mx = fold_abs(fold_abs(fold_abs(fold_abs(mx, v[i].x), v[i].y), v[i].z), v[i].w);
+      }
+    }
+    mx = warp_max(mx);
+    float sc = __fdiv_rn(mx, 127.0f);
+    if (sc == 0.0f) sc = 1.0f;
+    if (lane == 0) a_scale[row] = sc;
+    const float inv = __fdiv_rn(1.0f, sc);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(aq + row * K);
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = lane + i * 32;
+      if (idx < k4)
+        dst[idx] = pack4(act_round(__fmul_rn(v[i].x, inv)), act_round(__fmul_rn(v[i].y, inv)),
+                         act_round(__fmul_rn(v[i].z, inv)), act_round(__fmul_rn(v[i].w, inv)));
+    }
+  }
+}
+
 // Any K and alignment: two sweeps over the row (the second is served by L1/L2).
 __global__ void __launch_bounds__(kThreads) act_quant_generic(const float* __restrict__ A,
                                                               int64_t M, int64_t K,
@@ -403,7 +442,14 @@ cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, f
                    ((reinterpret_cast<uintptr_t>(aq) & 3) == 0);
   const int64_t per_thread = (K / 4 + kThreads - 1) / kThreads;  // float4 per thread
   count_launch();
-  if (vec && per_thread <= 3) {
+  if (vec && K <= 32 * 4 * 24 && M >= 64) {
+    int64_t wblocks = (M + kThreads / 32 - 1) / (kThreads / 32);
+    if (wblocks > (int64_t)sm_count * 4) wblocks = (int64_t)sm_count * 4;
+    if (K <= 32 * 4 * 8)
+      act_quant_warp_rows<8><<<(unsigned)wblocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
+    else
+      act_quant_warp_rows<24><<<(unsigned)wblocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
+  } else if (vec && per_thread <= 3) {
     act_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
   } else if (vec && per_thread <= 6) {
     act_quant_regs<6><<<(unsigned)blocks, kThreads, 0, s>>>(A, M, K, aq, a_scale);
