@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--rows", type=int, default=M_720P, help="token rows per GPU")
     ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch"])
     ap.add_argument("--blocks", type=int, default=30, help="branch workload: number of DiT blocks")
+    ap.add_argument("--pack-file-blocks", type=int, default=0,
+                    help="branch workload: also write this many blocks as a .sdcpp file and time the load")
     ap.add_argument("--verify-blocks", type=int, default=1, help="branch workload: blocks whose packed bytes are compared with the CPU packer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -580,6 +582,38 @@ def run_branch(args):
                 verified += 1
             weights.append((K, N, rows, q, sc, s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), N, K)))
             del wb
+    # optional: write the first blocks as a .sdcpp file and time open + validate + upload
+    load = None
+    if rank == 0 and args.pack_file_blocks > 0:
+        import struct
+        import tempfile
+        nb = min(args.pack_file_blocks, blocks) * len(BLOCK_LINEARS)
+        path = os.path.join(tempfile.gettempdir(), "sdq_bench_branch.sdcpp")
+        entries, off = [], 0
+        for i in range(nb):
+            K, N = weights[i][0], weights[i][1]
+            entries.append(("blocks.%d.%s.weight" % (i // len(BLOCK_LINEARS), BLOCK_LINEARS[i % len(BLOCK_LINEARS)][0]), N, K, off))
+            off += N * K + 4 * N
+        with open(path, "wb") as f:
+            f.write(b"SDCP" + struct.pack("<II", 1, nb))
+            for name, N, K, o in entries:
+                f.write(struct.pack("<I", len(name)) + name.encode() + struct.pack("<BI", 0, 2) + struct.pack("<qqQ", N, K, o))
+            for i in range(nb):
+                f.write(weights[i][3].cpu().numpy().tobytes())
+                f.write(weights[i][4].cpu().numpy().tobytes())
+        nbytes = os.path.getsize(path)
+        times = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            pack = s.open_pack(path, upload=True)
+            s.sync(None)
+            times.append(time.perf_counter() - t0)
+            pinned = pack.pinned()
+            n_ent = len(pack.entries())
+            pack.close()
+        os.remove(path)
+        load = {"file_bytes": nbytes, "entries": n_ent, "seconds_best": min(times), "seconds_first": times[0],
+                "gb_per_s": nbytes / min(times) / 1e9, "mapping_page_locked": pinned}
     x = torch.randn(max(M, 1), 3072, device=dev, generator=g)
     xf = torch.randn(max(M, 1), 14336, device=dev, generator=g)
     xt = torch.randn(512, 3072, device=dev, generator=g)
@@ -629,7 +663,8 @@ def run_branch(args):
                           "pack": {"elements": pack_elems, "ms": pack_ms, "gb_per_s": pack_gbs,
                                    "roofline": {"bound": "hbm", "achieved": pack_gbs, "peak": hbm, "unit": "GB/s",
                                                 "frac": pack_gbs / hbm, "of": pk_kind},
-                                   "tensors_verified_against_cpu_packer": verified}}))
+                                   "tensors_verified_against_cpu_packer": verified},
+                          "pack_load": load}))
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -260,6 +260,8 @@ typedef struct sdq_entry {
  * reference's messages ("sdcpp: bad magic", "sdcpp: truncated file", ...). */
 SDQ_API int sdq_pack_open(const char* path, uint32_t flags, sdq_pack** out);
 SDQ_API int64_t sdq_pack_count(const sdq_pack* p);
+/* 1 when the file mapping could be page-locked at open (uploads were direct DMA), else 0. */
+SDQ_API int sdq_pack_pinned(const sdq_pack* p);
 SDQ_API int sdq_pack_entry(const sdq_pack* p, int64_t index, sdq_entry* out);
 SDQ_API int sdq_pack_find(const sdq_pack* p, const char* name, sdq_entry* out);
 /* Unmaps the file and releases the device copies made at open. */

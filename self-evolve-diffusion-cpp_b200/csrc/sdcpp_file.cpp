@@ -26,11 +26,14 @@
 
 namespace sdq {
 int context_sm_count();
+bool pin_readonly_mapping(void* base, size_t size);
+void unpin_mapping(void* base);
 }
 
 struct sdq_pack {
   void* base = nullptr;
   size_t size = 0;
+  bool registered = false;  // the mapping is page-locked for direct DMA (SDQ_PACK_UPLOAD)
   struct Item {
     std::string name;
     int32_t dtype;
@@ -172,6 +175,10 @@ int sdq_pack_open(const char* path, uint32_t flags, sdq_pack** out) {
   }
 
   if (flags & SDQ_PACK_UPLOAD) {
+    // Page-lock the read-only file mapping so that the uploads below are direct DMA from the
+    // page cache (no staging copy).  Not every kernel / file system allows it for a
+    // file-backed mapping; when it is refused the copies go through the driver's own staging.
+    p->registered = sdq::pin_readonly_mapping(p->base, p->size);
     for (auto& it : p->items) {
       if (it.dtype != SDQ_DT_I8 || it.nbytes == 0) continue;
       const int64_t last = it.dims.back(), rows = (int64_t)it.nbytes / last;
@@ -189,6 +196,7 @@ int sdq_pack_open(const char* path, uint32_t flags, sdq_pack** out) {
 }
 
 int64_t sdq_pack_count(const sdq_pack* p) { return p ? (int64_t)p->items.size() : -1; }
+int sdq_pack_pinned(const sdq_pack* p) { return p && p->registered ? 1 : 0; }
 
 int sdq_pack_entry(const sdq_pack* p, int64_t index, sdq_entry* out) {
   if (!p || !out || index < 0 || index >= (int64_t)p->items.size())
@@ -209,6 +217,7 @@ int sdq_pack_close(sdq_pack* p) {
   if (!p) return SDQ_OK;
   for (auto& it : p->items)
     if (it.weight) sdq_weight_release(it.weight);
+  if (p->registered) sdq::unpin_mapping(p->base);
   if (p->base) munmap(p->base, p->size);
   delete p;
   return SDQ_OK;

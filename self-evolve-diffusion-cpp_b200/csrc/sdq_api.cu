@@ -126,6 +126,20 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// used by the pack loader (sdcpp_file.cpp): page-lock / release a read-only file mapping
+bool pin_readonly_mapping(void* base, size_t size) {
+  if (!g_ctx || !base || !size) return false;
+  cudaError_t e = cudaHostRegister(base, size, cudaHostRegisterReadOnly | cudaHostRegisterPortable);
+  if (e != cudaSuccess) {
+    cudaGetLastError();  // a refusal is not an error of the load
+    return false;
+  }
+  return true;
+}
+void unpin_mapping(void* base) {
+  if (cudaHostUnregister(base) != cudaSuccess) cudaGetLastError();
+}
+
 // used by the pack loader (sdcpp_file.cpp)
 int context_sm_count() { return g_ctx ? g_ctx->sm_count : 0; }
 

@@ -90,6 +90,7 @@ _SIGS = {
     "sdq_pack_sdcpp": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p]),
     "sdq_pack_open": (C.c_int, [C.c_char_p, C.c_uint32, C.POINTER(C.c_void_p)]),
     "sdq_pack_count": (C.c_int64, [C.c_void_p]),
+    "sdq_pack_pinned": (C.c_int, [C.c_void_p]),
     "sdq_pack_entry": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(Entry)]),
     "sdq_pack_find": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Entry)]),
     "sdq_pack_close": (C.c_int, [C.c_void_p]),
@@ -160,6 +161,9 @@ class Pack:
         h = C.c_void_p()
         sdq._ck(sdq.lib.sdq_pack_open(os.fsencode(path), PACK_UPLOAD if upload else 0, C.byref(h)))
         self.h = h
+
+    def pinned(self):
+        return bool(self.sdq.lib.sdq_pack_pinned(self.h))
 
     def entries(self):
         out = []
