@@ -27,12 +27,11 @@ namespace {
 using namespace tc;
 
 constexpr int kBlockN2 = 256;
-constexpr int kStages2 = 6;
 constexpr int kHalfBytes = BLOCK_M * BLOCK_K;         // 16 KiB: 128 rows x 128 B
 constexpr int kStageBytes2 = 2 * kHalfBytes;          // per CTA: A half + B half
-constexpr int kStagingBytes2 = 8 * 4096;
 constexpr int kTmemCols2 = 2 * kBlockN2;
-constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + kStagingBytes2 + 256 + 1024;
+// dynamic shared memory: pipeline stages + epilogue staging boxes + barriers + realignment slack
+constexpr int smem_bytes2(int stages, int boxes) { return stages * kStageBytes2 + 8 * 4096 * boxes + 256 + 1024; }
 // D=s32, A=B=s8, K-major both, N=256 (>>3 at bit 17), M=256 (>>4 at bit 24)
 constexpr uint32_t kIdesc2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN2 >> 3) << 17) |
                              ((uint32_t)(256 >> 4) << 24);
@@ -104,10 +103,14 @@ struct OutMaps {
   CUtensorMap m[8];
 };
 
+// kStages2: depth of the operand ring; kBoxes: staging boxes per epilogue warp (with two, a
+// warp fills one box while the bulk store of the other is still reading shared memory).
+template <int kStages2, int kBoxes>
 __global__ void __launch_bounds__(kNumThreads, 1)
     qgemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ OutMaps outs, int num_outs, GemmArgs g) {
+  constexpr int kStagingBytes2 = 8 * 4096 * kBoxes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // same offset in both CTAs of the pair
@@ -217,7 +220,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int mode = (g.bias ? 1 : 0) | ((g.flags & SDQ_GELU_TANH) ? 2 : 0);
-    const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
+    const uint32_t box0 = smem_staging + (uint32_t)((warp - 2) * 4096 * kBoxes);
+    uint32_t box_sel = 0;
     const uint64_t stream_policy = policy_evict_first();
     const uint32_t tempty_leader0 = map_to_cta(bar_tempty, 0);
     uint32_t abuf = 0, aphase = 0;
@@ -247,7 +251,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             case 2: chunk_values<false, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
             default: chunk_values<true, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
           }
-          if (lane == 0) bulk_wait_read<0>();
+          const uint32_t box = box0 + box_sel * 4096;
+          if (kBoxes > 1) box_sel ^= 1u;
+          // the store that last read this box must have finished reading it
+          if (lane == 0) bulk_wait_read<kBoxes - 1>();
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < 32; j += 4)
@@ -291,9 +298,21 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 }  // namespace
 
 // ---------------------------------------------------------------- host side
+// 6 stages + 1 box and 5 stages + 2 boxes both fill the 227 KiB of an SM.
+int tc2_config() {
+  static const int cfg = [] {
+    const char* v = getenv("SDQ_TC2_CONFIG");  // "61": 6 stages, 1 box; "52": 5 stages, 2 boxes
+    return v ? atoi(v) : 61;
+  }();
+  return cfg == 52 ? 52 : 61;
+}
+
 int qgemm_tc2_setup(std::string* why) {
-  cudaError_t a = cudaFuncSetAttribute(qgemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kSmemBytes2);
+  cudaError_t a = cudaFuncSetAttribute(qgemm_tc2_kernel<6, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       smem_bytes2(6, 1));
+  if (a == cudaSuccess)
+    a = cudaFuncSetAttribute(qgemm_tc2_kernel<5, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem_bytes2(5, 2));
   if (a != cudaSuccess) {
     if (why) *why = std::string("cudaFuncSetAttribute(2-CTA GEMM, max dynamic smem): ") + cudaGetErrorString(a);
     return SDQ_ERR_CUDA;
@@ -343,7 +362,8 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, st
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(clusters * 2));
   cfg.blockDim = dim3(kNumThreads);
-  cfg.dynamicSmemBytes = kSmemBytes2;
+  const bool deep = tc2_config() == 61;
+  cfg.dynamicSmemBytes = deep ? smem_bytes2(6, 1) : smem_bytes2(5, 2);
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -353,7 +373,8 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, st
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   count_launch();
-  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel, ta, tb, outs, num_outs, g);
+  if (deep) return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1>, ta, tb, outs, num_outs, g);
+  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2>, ta, tb, outs, num_outs, g);
 }
 
 }  // namespace sdq
