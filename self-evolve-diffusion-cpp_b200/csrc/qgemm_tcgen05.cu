@@ -19,8 +19,11 @@
 //                      rescale, stage in shared memory, bulk tensor store.
 //                      The second TMEM buffer lets tile t's epilogue overlap
 //                      tile t+1's main loop.
-// Integer accumulation is exact and order-free, so any tiling gives the
-// reference's sums bit for bit.
+// Integer accumulation is exact and order-free, so any tiling -- and any split of K
+// whose int32 partial sums are added afterwards -- gives the reference's sums bit for
+// bit.  This file holds the 1-CTA kernel (small problems, odd N, accumulator dump,
+// split-K) and the dispatch; the 2-CTA kernel for large problems is in
+// qgemm_tcgen05_2cta.cu.
 //
 // Every wait on an mbarrier is bounded: after ~2 s it records a code in the
 // status word, raises a CTA-wide abort flag, and all roles fall through to the
@@ -36,7 +39,6 @@ EncodeTiledFn g_encode = nullptr;
 namespace {
 using namespace tc;
 
-
 template <int BLOCK_N>
 struct Cfg {
   static constexpr int kStages = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
@@ -44,9 +46,9 @@ struct Cfg {
   static constexpr int kBBytes = BLOCK_N * BLOCK_K;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BLOCK_N;  // two accumulator buffers; a power of two >= 32
-  // stages + barriers/bookkeeping + slack to realign the dynamic base to 1024 B
-  // epilogue staging: per epilogue warp one 32x32 fp32 box (4 KiB) for TMA stores
+  // epilogue staging: per epilogue warp one 32x32 fp32 box (4 KiB) for the bulk tensor stores
   static constexpr int kStagingBytes = 8 * 4096;
+  // stages + staging + barriers/bookkeeping + slack to realign the dynamic base to 1024 B
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 256 + 1024;
   // instruction descriptor: D=s32 (2<<4), A=s8 (1<<7), B=s8 (1<<10), both K-major,
   // N>>3 at bit 17, M>>4 at bit 24
