@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------ TMA producer
+      grid_dependency_wait();  // aq is written by the quantize kernel launched just before
       const uint64_t keep_policy = policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
@@ -185,6 +186,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int mode = (g.bias ? 1 : 0) | ((g.flags & SDQ_GELU_TANH) ? 2 : 0);
     const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
     const uint64_t stream_policy = policy_evict_first();
+    grid_dependency_wait();  // a_scale (and a split-K accumulator's memset) come from earlier work
     uint32_t abuf = 0, aphase = 0;
     bool ok = true;
     for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
@@ -322,8 +324,17 @@ cudaError_t launch_t(const GemmArgs& g, int sm_count, cudaStream_t s, std::strin
                        (g.k_splits > 1 ? g.k_splits : 1);
   const unsigned grid = (unsigned)(work < sm_count ? work : sm_count);
   count_launch();
-  qgemm_tc_kernel<BLOCK_N><<<grid, kNumThreads, C::kSmemBytes, s>>>(ta, tb, tout, use_tma_store, g);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see grid_dependency_wait()
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, qgemm_tc_kernel<BLOCK_N>, ta, tb, tout, use_tma_store, g);
   if (e == cudaSuccess && g.k_splits > 1) {
     int64_t blocks = (g.M * g.N + 255) / 256;
     if (blocks > (int64_t)sm_count * 8) blocks = (int64_t)sm_count * 8;

@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------ TMA producer (both CTAs)
+      grid_dependency_wait();  // aq is written by the quantize kernel launched just before
       const uint64_t keep_policy = policy_evict_last();
       const uint64_t normal_policy = policy_evict_normal();
       uint32_t stage = 0, phase = 0;
@@ -224,6 +225,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     uint32_t box_sel = 0;
     const uint64_t stream_policy = policy_evict_first();
     const uint32_t tempty_leader0 = map_to_cta(bar_tempty, 0);
+    grid_dependency_wait();  // a_scale comes from the quantize kernel
     uint32_t abuf = 0, aphase = 0;
     bool ok = true;
     for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
@@ -365,13 +367,15 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, st
   const bool deep = tc2_config() == 61;
   cfg.dynamicSmemBytes = deep ? smem_bytes2(6, 1) : smem_bytes2(5, 2);
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see grid_dependency_wait()
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   count_launch();
   if (deep) return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1>, ta, tb, outs, num_outs, g);
   return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2>, ta, tb, outs, num_outs, g);

@@ -53,12 +53,21 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
 
+// Programmatic dependent launch: lets the GEMM that follows in the stream (launched with
+// the programmatic-serialization attribute) start its prologue -- barrier set-up, tensor
+// memory allocation, descriptor prefetch -- while this kernel is still running.  The GEMM
+// waits (griddepcontrol.wait) for this whole grid and its writes before it reads anything.
+__device__ __forceinline__ void allow_dependent_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- activations: a row lives in registers between the max and the rounding ----
 // Requires K % 4 == 0, 16-byte aligned A, K <= kThreads * 4 * VPT.
 template <int VPT>
 __global__ void __launch_bounds__(kThreads) act_quant_regs(const float* __restrict__ A, int64_t M,
                                                            int64_t K, int8_t* __restrict__ aq,
                                                            float* __restrict__ a_scale) {
+  allow_dependent_launch();
   __shared__ float red[kThreads / 32];
   const int k4 = (int)(K >> 2);
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
@@ -97,6 +106,7 @@ __global__ void __launch_bounds__(kThreads) act_quant_warp_rows(const float* __r
                                                                 int64_t M, int64_t K,
                                                                 int8_t* __restrict__ aq,
                                                                 float* __restrict__ a_scale) {
+  allow_dependent_launch();
   const int lane = threadIdx.x & 31;
   const int k4 = (int)(K >> 2);
   const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
@@ -133,6 +143,7 @@ __global__ void __launch_bounds__(kThreads) act_quant_generic(const float* __res
                                                               int64_t M, int64_t K,
                                                               int8_t* __restrict__ aq,
                                                               float* __restrict__ a_scale) {
+  allow_dependent_launch();
   __shared__ float red[kThreads / 32];
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
     const float* src = A + row * K;
@@ -179,6 +190,7 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
                                                               int8_t* __restrict__ aq,
                                                               float* __restrict__ a_scale,
                                                               float* __restrict__ h_out) {
+  allow_dependent_launch();
   __shared__ float red[kThreads / 32];
   const int k4 = (int)(K >> 2);
   const float inv_n = 1.0f / (float)K;
@@ -442,7 +454,7 @@ cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, f
                    ((reinterpret_cast<uintptr_t>(aq) & 3) == 0);
   const int64_t per_thread = (K / 4 + kThreads - 1) / kThreads;  // float4 per thread
   count_launch();
-  if (vec && K <= 32 * 4 * 24 && M >= 64) {
+  if (vec && K <= 32 * 4 * 24 && M >= (int64_t)sm_count * 16) {
     int64_t wblocks = (M + kThreads / 32 - 1) / (kThreads / 32);
     if (wblocks > (int64_t)sm_count * 4) wblocks = (int64_t)sm_count * 4;
     if (K <= 32 * 4 * 8)

@@ -71,6 +71,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Programmatic dependent launch, consumer side: returns once every kernel this grid depends
+// on in its stream has completed and its writes are visible.  Everything before it (barrier
+// set-up, tensor-memory allocation, descriptor prefetch) may overlap the producer kernel.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // Warp-wide bounded wait: lane 0 polls, the other lanes park at the shuffle (no issue
 // slots, no power burnt spinning); every lane returns the same verdict.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
