@@ -133,3 +133,57 @@ def test_ffn_pair_entry_point(sdq, pkg, oracle):
         sdq._ck(sdq.lib.sdq_ffn_pair(w1, None, w2, None, dx.ptr, M, None, dy.ptr, pkg.sdq.A_HOST, None))
     sdq.weight_release(w1)
     sdq.weight_release(w2)
+
+
+def test_column_split_fused_stores_on_one_gpu(sdq, pkg, oracle):
+    """sdq_qgemm_colsplit, the multi-GPU column split with the exchange fused into the GEMM
+    epilogue, exercised on one GPU: two "ranks" each own half of the weight rows and store
+    their column block into both of two [M, N] buffers (here both local; on several GPUs the
+    second is a peer's, mapped through CUDA IPC).  Every buffer must end up with the bits of
+    the unsplit linear."""
+    rng = np.random.default_rng(91)
+    M, K, N = 5000, 1024, 1088                      # 1088 = 544 + 544: blocks of 17 x 32 columns
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    wq, ws = packed_weights(rng, N, K, oracle)
+    b = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    full = sdq.weight_upload(wq, ws)
+    want = sdq.qgemm_host(full, A, bias=b)
+    rows = np.sort(rng.choice(M, 40, replace=False))
+    assert bits_equal(want[rows], oracle.bias_add(oracle.qgemm(A[rows], wq, ws), b))
+    dA, db = sdq.to_device(A), sdq.to_device(b)
+    outs = [sdq.alloc(M * N * 4), sdq.alloc(M * N * 4)]
+    for o in outs:
+        sdq._ck(sdq.lib.sdq_memset(o.ptr, 0xFF, M * N * 4, None))
+    for r in range(2):
+        n0, n1 = pkg.sharding.col_shard(N, 2, r)
+        w = sdq.weight_upload(wq[n0:n1], ws[n0:n1])
+        sdq.qgemm_colsplit(w, dA.ptr, M, n0, N, [o.ptr for o in outs], db.ptr + 4 * n0, pkg.sdq.SYNC)
+        sdq.weight_release(w)
+    for o in outs:
+        assert bits_equal(o.to_numpy(np.float32, (M, N)), want)
+    # a block that neither starts on a multiple of 32 nor ends the matrix is refused
+    w = sdq.weight_upload(wq[:40], ws[:40])
+    with pytest.raises(pkg.SdqError) as e:
+        sdq.qgemm_colsplit(w, dA.ptr, M, 0, N, [outs[0].ptr])
+    assert e.value.code == 1
+    sdq.weight_release(w)
+    sdq.weight_release(full)
+
+
+def test_random_shapes_match_oracle(sdq, oracle):
+    """Seeded random (M, K, N), odd sizes and alignments included: whole outputs exact."""
+    rng = np.random.default_rng(2024)
+    for _ in range(24):
+        M = int(rng.integers(1, 700))
+        K = int(rng.choice([int(rng.integers(1, 300)), 16 * int(rng.integers(1, 80)), 128 * int(rng.integers(1, 30))]))
+        N = int(rng.choice([int(rng.integers(1, 300)), 4 * int(rng.integers(1, 200)), 32 * int(rng.integers(1, 40))]))
+        A = (rng.standard_normal((M, K)) * float(rng.choice([1e-3, 1.0, 50.0]))).astype(np.float32)
+        wq, ws = packed_weights(rng, N, K, oracle)
+        bias = (rng.standard_normal(N) * 0.02).astype(np.float32) if rng.integers(2) else None
+        w = sdq.weight_upload(wq, ws)
+        want = oracle.qgemm(A, wq, ws)
+        if bias is not None:
+            want = oracle.bias_add(want, bias)
+        got = sdq.qgemm_host(w, A, bias=bias)
+        assert bits_equal(got, want), (M, K, N)
+        sdq.weight_release(w)
