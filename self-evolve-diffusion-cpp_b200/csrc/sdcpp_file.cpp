@@ -27,6 +27,9 @@
 namespace sdq {
 int context_sm_count();
 bool pin_readonly_mapping(void* base, size_t size);
+int pack_upload_weight(const int8_t* q_host, const float* scale_host, int64_t N, int64_t K,
+                       sdq_weight_t* out);
+int pack_upload_finish();
 void unpin_mapping(void* base);
 }
 
@@ -182,13 +185,20 @@ int sdq_pack_open(const char* path, uint32_t flags, sdq_pack** out) {
     for (auto& it : p->items) {
       if (it.dtype != SDQ_DT_I8 || it.nbytes == 0) continue;
       const int64_t last = it.dims.back(), rows = (int64_t)it.nbytes / last;
-      int rc = sdq_weight_upload((const int8_t*)it.data, (const float*)(it.data + it.nbytes), rows,
-                                 last, &it.weight);
+      int rc = sdq::pack_upload_weight((const int8_t*)it.data, (const float*)(it.data + it.nbytes),
+                                       rows, last, &it.weight);
       if (rc != SDQ_OK) {
         const std::string msg = sdq_last_error();
         sdq_pack_close(p);
         return fail(rc, msg);
       }
+    }
+  }
+  if (flags & SDQ_PACK_UPLOAD) {
+    if (int rc = sdq::pack_upload_finish()) {
+      const std::string msg = sdq_last_error();
+      sdq_pack_close(p);
+      return fail(rc, msg);
     }
   }
   *out = p;

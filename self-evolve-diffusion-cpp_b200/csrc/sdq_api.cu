@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -49,6 +50,12 @@ struct Context {
   float* pa[2] = {}; size_t pa_bytes[2] = {};
   float* py[2] = {}; size_t py_bytes[2] = {};
   float* ph = nullptr; size_t ph_bytes = 0;
+  // staged uploads of large weights
+  std::mutex upload_mu;
+  cudaStream_t up_stream = nullptr;
+  void* up_buf[2] = {};
+  int up_next = 0;
+  cudaEvent_t up_done[2] = {};
 };
 Context* g_ctx = nullptr;
 std::mutex g_init_mu;
@@ -200,6 +207,11 @@ int sdq_shutdown(void) {
                            cudaEventDestroy(g_ctx->ev_comp[i]); cudaEventDestroy(g_ctx->ev_out_done[i]); }
   }
   cudaFree(g_ctx->ph);
+  for (int i = 0; i < 2; i++) {
+    if (g_ctx->up_buf[i]) cudaFreeHost(g_ctx->up_buf[i]);
+    if (g_ctx->up_done[i]) cudaEventDestroy(g_ctx->up_done[i]);
+  }
+  if (g_ctx->up_stream) cudaStreamDestroy(g_ctx->up_stream);
   if (g_ctx->copy_in) cudaStreamDestroy(g_ctx->copy_in);
   if (g_ctx->copy_out) cudaStreamDestroy(g_ctx->copy_out);
   cudaFree(g_ctx->status);
@@ -258,6 +270,60 @@ int sdq_stream_sync(void* stream) {
 }
 
 // ---- weights ----
+// Host -> device copy of a large pageable (typically file-mapped) range through two pinned
+// staging buffers: a few host threads fill one buffer (which is also what pages the file in)
+// while the DMA engine drains the other.  Ranges below a threshold take a plain cudaMemcpy.
+static int staged_upload(void* dst_dev, const void* src_host, size_t bytes, bool wait_at_end) {
+  constexpr size_t kChunk = size_t(32) << 20;
+  if (bytes < (size_t(1) << 20)) {
+    SDQ_CUDA(cudaMemcpy(dst_dev, src_host, bytes, cudaMemcpyHostToDevice));
+    return SDQ_OK;
+  }
+  Context* c = g_ctx;
+  std::lock_guard<std::mutex> lk(c->upload_mu);
+  if (!c->up_stream) {
+    SDQ_CUDA(cudaStreamCreateWithFlags(&c->up_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; i++) {
+      cudaError_t e = cudaHostAlloc(&c->up_buf[i], kChunk, cudaHostAllocDefault);
+      if (e != cudaSuccess) return fail(SDQ_ERR_NOMEM, std::string("cudaHostAlloc(staging): ") + cudaGetErrorString(e));
+      SDQ_CUDA(cudaEventCreateWithFlags(&c->up_done[i], cudaEventDisableTiming));
+    }
+  }
+  {  // already page-locked (pinned allocation or a registered mapping): direct DMA, no staging
+    cudaPointerAttributes pa;
+    if (cudaPointerGetAttributes(&pa, src_host) == cudaSuccess && pa.type == cudaMemoryTypeHost) {
+      SDQ_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, c->up_stream));
+      if (wait_at_end) SDQ_CUDA(cudaStreamSynchronize(c->up_stream));
+      return SDQ_OK;
+    }
+    cudaGetLastError();
+  }
+  const unsigned hw = std::thread::hardware_concurrency();
+  const int nthreads = (int)std::max(1u, std::min(8u, hw ? hw / 2 : 1u));
+  size_t off = 0;
+  for (; off < bytes; c->up_next ^= 1) {
+    const int i = c->up_next;  // buffers alternate across calls too, so uploads of consecutive
+                               // tensors of a pack overlap each other's DMA
+    const size_t n = std::min(kChunk, bytes - off);
+    SDQ_CUDA(cudaEventSynchronize(c->up_done[i]));  // the DMA that last read this buffer is done
+    const char* src = static_cast<const char*>(src_host) + off;
+    char* dstb = static_cast<char*>(c->up_buf[i]);
+    std::vector<std::thread> team;
+    const size_t per = (n + nthreads - 1) / nthreads;
+    for (int t = 1; t < nthreads; t++) {
+      const size_t b = std::min(n, per * t), e = std::min(n, per * (t + 1));
+      if (e > b) team.emplace_back([=] { std::memcpy(dstb + b, src + b, e - b); });
+    }
+    std::memcpy(dstb, src, std::min(n, per));
+    for (auto& th : team) th.join();
+    SDQ_CUDA(cudaMemcpyAsync(static_cast<char*>(dst_dev) + off, dstb, n, cudaMemcpyHostToDevice, c->up_stream));
+    SDQ_CUDA(cudaEventRecord(c->up_done[i], c->up_stream));
+    off += n;
+  }
+  if (wait_at_end) SDQ_CUDA(cudaStreamSynchronize(c->up_stream));
+  return SDQ_OK;
+}
+
 static int register_weight(const Weight& w, sdq_weight_t* out) {
   std::lock_guard<std::mutex> lk(g_ctx->mu);
   g_ctx->weights.push_back(w);
@@ -266,19 +332,24 @@ static int register_weight(const Weight& w, sdq_weight_t* out) {
   return SDQ_OK;
 }
 
-int sdq_weight_upload(const int8_t* q_host, const float* scale_host, int64_t N, int64_t K,
-                      sdq_weight_t* out) {
+static int weight_upload_impl(const int8_t* q_host, const float* scale_host, int64_t N, int64_t K,
+                              sdq_weight_t* out, bool wait_at_end) {
   if (int rc = need_ctx()) return rc;
   if (!q_host || !scale_host || !out || N <= 0 || K <= 0)
     return fail(SDQ_ERR_INVALID, "sdq_weight_upload: null pointer or non-positive shape");
   int8_t* dq = nullptr; float* ds = nullptr;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&dq), (size_t)N * K);  // cudaMalloc is >= 256-B aligned
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ds), (size_t)N * 4);
-  if (e == cudaSuccess) e = cudaMemcpy(dq, q_host, (size_t)N * K, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(ds, scale_host, (size_t)N * 4, cudaMemcpyHostToDevice);
   if (e != cudaSuccess) { cudaFree(dq); cudaFree(ds); return cuda_fail(e, "sdq_weight_upload"); }
+  if (int rc = staged_upload(dq, q_host, (size_t)N * K, wait_at_end)) { cudaFree(dq); cudaFree(ds); return rc; }
   Weight w; w.q = dq; w.scale = ds; w.N = N; w.K = K; w.owned = true; w.host_key = q_host; w.live = true;
   return register_weight(w, out);
+}
+
+int sdq_weight_upload(const int8_t* q_host, const float* scale_host, int64_t N, int64_t K,
+                      sdq_weight_t* out) {
+  return weight_upload_impl(q_host, scale_host, N, K, out, true);
 }
 
 int sdq_weight_wrap_device(const int8_t* q_dev, const float* scale_dev, int64_t N, int64_t K,
@@ -643,3 +714,15 @@ int sdq_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t 
 }
 
 }  // extern "C"
+
+namespace sdq {
+// Pack loader: upload without waiting for the DMA of each tensor; pack_upload_finish() waits once.
+int pack_upload_weight(const int8_t* q_host, const float* scale_host, int64_t N, int64_t K,
+                       sdq_weight_t* out) {
+  return weight_upload_impl(q_host, scale_host, N, K, out, false);
+}
+int pack_upload_finish() {
+  if (g_ctx && g_ctx->up_stream) SDQ_CUDA(cudaStreamSynchronize(g_ctx->up_stream));
+  return SDQ_OK;
+}
+}  // namespace sdq
