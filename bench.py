@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--verify-blocks", type=int, default=1, help="branch workload: blocks whose packed bytes are compared with the CPU packer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-peak-probe", action="store_true")
     return ap.parse_args()
 
 
@@ -340,6 +341,20 @@ def run_b200(args):
                 "kernel_ms": kern_ms,
                 "hbm_frac_act_quant_k14336": (5.0 * M * D_FFN + 4 * M) / (kern_ms["act_quant_k14336"] * 1e-3) / 1e9
                 / float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))}
+
+    # the device's own MMA-issue-bound int8 rate, measured now (burst: one 2 ms launch on an
+    # idle GPU; sustained: back-to-back launches for ~3 s, median of the last half)
+    if not args.no_peak_probe:
+        time.sleep(1.0)
+        burst = max(s.int8_mma_probe(2000)[1] for _ in range(3))
+        t_end, rates = time.time() + 3.0, []
+        while time.time() < t_end:
+            rates.append(s.int8_mma_probe(20000)[1])
+        sustained = float(np.median(rates[len(rates) // 2:]))
+        roofline["int8_mma_peak_measured"] = {"burst_tops": burst, "sustained_tops": sustained,
+                                              "how": "tcgen05.mma kind::i8 128x256x32 issued back to back "
+                                                     "from shared memory on all SMs (sdq_int8_mma_probe)"}
+        roofline["frac_of_int8_measured_sustained"] = achieved / sustained
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:

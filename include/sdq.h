@@ -81,6 +81,13 @@ SDQ_API const char* sdq_last_error(void);
 /* Number of kernels this library has launched since sdq_init (monotonic). */
 SDQ_API int64_t sdq_launch_count(void);
 
+/* A measuring stick (no counterpart in the reference): every SM issues `iters` batches of 16
+ * tcgen05.mma kind::i8 (M=128, N=256, K=32) back to back on operands already in shared memory
+ * -- no TMA, no epilogue, no global traffic.  Returns the device time of the launch and the
+ * rate in TOPS: the MMA-issue-bound int8 ceiling of this GPU at the clocks it holds, which
+ * is what the GEMM kernels' tensor rooflines are compared with.  Synchronous. */
+SDQ_API int sdq_int8_mma_probe(int iters, double* seconds, double* tera_ops_per_s);
+
 /* Device / pinned-host memory and copies for callers that do not link the CUDA
  * runtime themselves.  `stream` is a cudaStream_t (NULL = default stream). */
 SDQ_API int sdq_malloc(void** dptr, size_t bytes);

@@ -220,6 +220,17 @@ int sdq_shutdown(void) {
   return SDQ_OK;
 }
 
+int sdq_int8_mma_probe(int iters, double* seconds, double* tera_ops_per_s) {
+  if (int rc = need_ctx()) return rc;
+  if (iters < 1 || iters > (1 << 24)) return fail(SDQ_ERR_INVALID, "sdq_int8_mma_probe: iters out of range");
+  double sec = 0, ops = 0;
+  if (int rc = int8_mma_probe(g_ctx->sm_count, iters, g_ctx->status, &sec, &ops)) return rc;
+  if (int rc = check_status_word()) return rc;
+  if (seconds) *seconds = sec;
+  if (tera_ops_per_s) *tera_ops_per_s = sec > 0 ? ops / sec / 1e12 : 0;
+  return SDQ_OK;
+}
+
 int sdq_malloc(void** dptr, size_t bytes) {
   if (int rc = need_ctx()) return rc;
   if (!dptr) return fail(SDQ_ERR_INVALID, "sdq_malloc: null out pointer");

@@ -75,4 +75,7 @@ int qgemm_tc2_setup(std::string* why);
 bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count);  // call only if qgemm_tc_supported(g)
 cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why);
 
+// MMA-issue-bound int8 rate of the device (mma_probe.cu).
+int int8_mma_probe(int sm_count, int iters, int* status_dev, double* seconds, double* ops);
+
 }  // namespace sdq

@@ -55,6 +55,7 @@ _SIGS = {
     "sdq_version": (C.c_int, []),
     "sdq_last_error": (C.c_char_p, []),
     "sdq_launch_count": (C.c_int64, []),
+    "sdq_int8_mma_probe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "sdq_malloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "sdq_free": (C.c_int, [C.c_void_p]),
     "sdq_malloc_host": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
@@ -213,6 +214,12 @@ class Sdq:
 
     def launches(self):
         return int(self.lib.sdq_launch_count())
+
+    def int8_mma_probe(self, iters):
+        """(seconds, TOPS) of the MMA-issue-bound int8 probe."""
+        sec, tops = C.c_double(), C.c_double()
+        self._ck(self.lib.sdq_int8_mma_probe(iters, C.byref(sec), C.byref(tops)))
+        return sec.value, tops.value
 
     # ---- memory ----
     def alloc(self, nbytes):
