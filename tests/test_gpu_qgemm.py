@@ -165,3 +165,38 @@ def test_reference_gate_cosine(sdq, oracle):
         assert cosine(out, ref) > 0.999
         assert np.isfinite(out).all() and out.shape == (M, N)
         sdq.weight_release(w)
+
+
+def test_concurrent_host_threads_and_streams(sdq, pkg, oracle):
+    """Four host threads, each with its own stream, weight and shape, calling sdq_qgemm at the
+    same time: the scratch is per stream and the registry is locked, so every result is exact."""
+    import threading
+    rng = np.random.default_rng(12)
+    jobs = []
+    for (M, K, N) in [(700, 1024, 512), (300, 3072, 1024), (2500, 512, 768), (129, 2048, 384)]:
+        A = rng.standard_normal((M, K)).astype(np.float32)
+        wq, ws = packed_weights(rng, N, K, oracle)
+        jobs.append((A, wq, ws, oracle.qgemm(A, wq, ws)))
+    errors = []
+
+    def run(job):
+        try:
+            A, wq, ws, want = job
+            M, K = A.shape
+            N = wq.shape[0]
+            w = sdq.weight_upload(wq, ws)
+            dA, dout = sdq.to_device(A), sdq.alloc(M * N * 4)
+            for _ in range(20):
+                sdq.qgemm(w, dA.ptr, M, dout.ptr, None, pkg.sdq.SYNC)
+            got = dout.to_numpy(np.float32, (M, N))
+            if not bits_equal(got, want):
+                errors.append((M, K, N))
+            sdq.weight_release(w)
+        except Exception as e:  # pragma: no cover
+            errors.append(repr(e))
+    threads = [threading.Thread(target=run, args=(j,)) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
