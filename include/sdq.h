@@ -98,6 +98,11 @@ SDQ_API int sdq_memcpy_h2d(void* dst, const void* src, size_t bytes, void* strea
 SDQ_API int sdq_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
 SDQ_API int sdq_memset(void* dst, int value, size_t bytes, void* stream);
 SDQ_API int sdq_stream_sync(void* stream);
+/* A new non-blocking stream / its destruction, for callers without the CUDA runtime.  The
+ * scratch of the compute entry points is kept per stream: calls on different streams may run
+ * concurrently (also from different host threads); concurrent calls on ONE stream may not. */
+SDQ_API int sdq_stream_create(void** stream);
+SDQ_API int sdq_stream_destroy(void* stream);
 
 /* ---- weights ---- */
 

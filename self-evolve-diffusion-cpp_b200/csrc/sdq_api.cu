@@ -280,6 +280,33 @@ int sdq_stream_sync(void* stream) {
   return check_status_word();
 }
 
+int sdq_stream_create(void** stream) {
+  if (int rc = need_ctx()) return rc;
+  if (!stream) return fail(SDQ_ERR_INVALID, "sdq_stream_create: null out pointer");
+  cudaStream_t s = nullptr;
+  SDQ_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  *stream = s;
+  return SDQ_OK;
+}
+
+int sdq_stream_destroy(void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (!stream) return SDQ_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  SDQ_CUDA(cudaStreamSynchronize(s));
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    auto it = g_ctx->ws.find(s);
+    if (it != g_ctx->ws.end()) {
+      cudaFree(it->second.aq); cudaFree(it->second.a_scale); cudaFree(it->second.a_stage);
+      cudaFree(it->second.out_stage); cudaFree(it->second.acc);
+      g_ctx->ws.erase(it);
+    }
+  }
+  SDQ_CUDA(cudaStreamDestroy(s));
+  return SDQ_OK;
+}
+
 // ---- weights ----
 // Host -> device copy of a large pageable (typically file-mapped) range through two pinned
 // staging buffers: a few host threads fill one buffer (which is also what pages the file in)

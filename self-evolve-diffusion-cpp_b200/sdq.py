@@ -64,6 +64,8 @@ _SIGS = {
     "sdq_memcpy_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "sdq_memset": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
     "sdq_stream_sync": (C.c_int, [C.c_void_p]),
+    "sdq_stream_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "sdq_stream_destroy": (C.c_int, [C.c_void_p]),
     "sdq_weight_upload": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_uint64)]),
     "sdq_weight_wrap_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_uint64)]),
     "sdq_weight_lookup": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
@@ -211,6 +213,14 @@ class Sdq:
 
     def sync(self, stream=None):
         self._ck(self.lib.sdq_stream_sync(stream))
+
+    def stream_create(self):
+        p = C.c_void_p()
+        self._ck(self.lib.sdq_stream_create(C.byref(p)))
+        return p.value
+
+    def stream_destroy(self, stream):
+        self._ck(self.lib.sdq_stream_destroy(stream))
 
     def launches(self):
         return int(self.lib.sdq_launch_count())

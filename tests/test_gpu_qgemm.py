@@ -186,11 +186,14 @@ def test_concurrent_host_threads_and_streams(sdq, pkg, oracle):
             N = wq.shape[0]
             w = sdq.weight_upload(wq, ws)
             dA, dout = sdq.to_device(A), sdq.alloc(M * N * 4)
+            st = sdq.stream_create()
             for _ in range(20):
-                sdq.qgemm(w, dA.ptr, M, dout.ptr, None, pkg.sdq.SYNC)
+                sdq.qgemm(w, dA.ptr, M, dout.ptr, None, 0, st)
+            sdq.sync(st)
             got = dout.to_numpy(np.float32, (M, N))
             if not bits_equal(got, want):
                 errors.append((M, K, N))
+            sdq.stream_destroy(st)
             sdq.weight_release(w)
         except Exception as e:  # pragma: no cover
             errors.append(repr(e))
