@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=M_720P, help="token rows per GPU")
-    ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch"])
+    ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch", "libcompare"])
     ap.add_argument("--blocks", type=int, default=30, help="branch workload: number of DiT blocks")
     ap.add_argument("--pack-file-blocks", type=int, default=0,
                     help="branch workload: also write this many blocks as a .sdcpp file and time the load")
@@ -530,6 +530,67 @@ def run_sweep(args):
     return 0
 
 
+# ------------------------------------------------------------------ library comparison
+def run_libcompare(args):
+    """The GEMM launches alone (activations already int8) next to the vendor library's int8
+    GEMM (torch._int_mm -> cuBLASLt: int32 output, no rescale / bias / GELU), same shapes, same
+    loop of `--steps` back-to-back launches, alternating so that both see the same thermal and
+    power state.  Context only: the library GEMM is not on any path of this repository."""
+    import ctypes as C
+
+    import torch
+
+    import __graft_entry__ as ge
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = ge.load_package()
+    s = pkg.Sdq(0)
+    S, lib = pkg.sdq, s.lib
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    M = args.rows
+    rows = []
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+    for (K, N, flags) in [(D_MODEL, D_FFN, S.GELU_TANH), (D_FFN, D_MODEL, 0)]:
+        aq = torch.randint(-127, 128, (M, K), device=dev, dtype=torch.int8)
+        a_s = torch.rand(M, device=dev) * 0.01 + 0.001
+        q = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8)
+        sc = torch.rand(N, device=dev) * 0.01 + 0.001
+        b = torch.randn(N, device=dev) * 0.02
+        out = torch.empty(M, N, device=dev)
+        w = s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), N, K)
+        Ml = M - M % 8                                   # the library call wants M % 8 == 0
+        ours, libt = [], []
+        for _ in range(3):
+            ours.append(timed(lambda: s._ck(lib.sdq_qgemm_prequantized(
+                w, aq.data_ptr(), a_s.data_ptr(), M, out.data_ptr(), b.data_ptr(), None, flags, sp))))
+            libt.append(timed(lambda: torch._int_mm(aq[:Ml], q.t())))
+        ops = 2.0 * M * N * K
+        rows.append({"K": K, "N": N, "M": M, "ours_ms": float(np.median(ours)),
+                     "ours_tops": ops / (float(np.median(ours)) * 1e-3) / 1e12,
+                     "ours_epilogue": "rescale + bias" + (" + GELU" if flags else ""),
+                     "library_ms": float(np.median(libt)),
+                     "library_tops": 2.0 * Ml * N * K / (float(np.median(libt)) * 1e-3) / 1e12,
+                     "library_epilogue": "none (int32 out)"})
+        s.weight_release(w)
+    print(json.dumps({"metric": "int8_gemm_launch_ms", "config": {"workload": "library_comparison", "rows": M,
+                                                                  "launches_per_loop": args.steps},
+                      "rows": rows}))
+    return 0
+
+
 # ------------------------------------------------------------------ whole branch
 # linears of one DiT block of the video branch (name, K, N, rows: None = all tokens)
 BLOCK_LINEARS = [("self_attn.qkv", 3072, 9216, None), ("self_attn.o", 3072, 3072, None),
@@ -689,4 +750,4 @@ if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         sys.exit(run_reference(a))
-    sys.exit(run_sweep(a) if a.workload == "sweep" else run_branch(a) if a.workload == "branch" else run_b200(a))
+    sys.exit({"sweep": run_sweep, "branch": run_branch, "libcompare": run_libcompare}.get(a.workload, run_b200)(a))
