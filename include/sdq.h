@@ -261,6 +261,7 @@ typedef struct sdq_entry {
   uint64_t file_offset; /* of `data` from the start of the file */
   sdq_weight_t weight; /* device copy of an I8 entry when the pack was opened with
                           SDQ_PACK_UPLOAD, viewed as [numel/last, last]; else 0 */
+  uint64_t name_len;   /* bytes of `name` (a name may contain NUL bytes; the file stores a length) */
 } sdq_entry;
 
 #define SDQ_PACK_UPLOAD 0x1u /* upload every I8 entry (+ scales) to the device at open */

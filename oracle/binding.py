@@ -211,7 +211,7 @@ class Reference:
         """(count, listing) or raises RuntimeError with the loader's message."""
         buf = C.create_string_buffer(1 << 20)
         n = self.lib.sdref_load_sdcpp_listing(path.encode(), buf, i64(len(buf)))
-        text = buf.value.decode()
+        text = buf.value.decode(errors="replace")
         if n < 0:
             raise RuntimeError(text)
         return int(n), text

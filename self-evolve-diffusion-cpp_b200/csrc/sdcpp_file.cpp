@@ -83,6 +83,7 @@ void fill_entry(const sdq_pack::Item& it, const sdq_pack* p, sdq_entry* out) {
   out->nbytes = it.nbytes;
   out->file_offset = (uint64_t)(it.data - (const uint8_t*)p->base);
   out->weight = it.weight;
+  out->name_len = it.name.size();
 }
 
 }  // namespace

@@ -43,9 +43,9 @@ class SdqError(RuntimeError):
 
 
 class Entry(C.Structure):
-    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int32), ("ndim", C.c_int32),
+    _fields_ = [("name", C.c_void_p), ("dtype", C.c_int32), ("ndim", C.c_int32),
                 ("dims", C.c_int64 * 8), ("data", C.c_void_p), ("nbytes", C.c_uint64),
-                ("file_offset", C.c_uint64), ("weight", C.c_uint64)]
+                ("file_offset", C.c_uint64), ("weight", C.c_uint64), ("name_len", C.c_uint64)]
 
 
 _SIGS = {
@@ -184,7 +184,7 @@ class Pack:
     @staticmethod
     def _conv(e):
         dims = [int(e.dims[i]) for i in range(e.ndim)]
-        return {"name": e.name.decode(), "dtype": int(e.dtype), "dims": dims, "data": e.data,
+        return {"name": C.string_at(e.name, e.name_len).decode(errors="replace"), "dtype": int(e.dtype), "dims": dims, "data": e.data,
                 "nbytes": int(e.nbytes), "file_offset": int(e.file_offset), "weight": int(e.weight)}
 
     def array(self, entry):

@@ -70,7 +70,7 @@ def test_pack_reader_runs_on_cpu(pkg, golden_dir):
         e = pkg.sdq.Entry()
         assert lib.sdq_pack_entry(h, i, C.byref(e)) == 0
         dims = [str(e.dims[k]) for k in range(e.ndim)]
-        lines.append("%s %d %d %s %d %d" % (e.name.decode(), e.dtype, e.ndim, ",".join(dims) or "-",
+        lines.append("%s %d %d %s %d %d" % (C.string_at(e.name, e.name_len).decode(), e.dtype, e.ndim, ",".join(dims) or "-",
                                             e.file_offset, e.nbytes))
     assert "\n".join(sorted(lines)) + "\n" == gold["sdcpp_listing"]["listing"]
     assert lib.sdq_pack_close(h) == 0
