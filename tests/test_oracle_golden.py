@@ -157,3 +157,26 @@ def test_parse_errors_match_reference_loader(gold, golden_dir):
             pack_oracle.parse(data)
         want = gold["loader_errors"][tag].replace(" <path>", "")
         assert str(e.value) == want, tag
+
+
+def test_pack_restatement_matches_reference_packer_on_random_checkpoints(oracle, tmp_path):
+    """Where the reference tree is mounted: random small checkpoints through the reference's
+    python packer and through the restatement give identical files."""
+    import subprocess
+    import sys
+    from util import random_safetensors
+    ref_packer = os.path.join(os.environ.get("REF", "/root/reference"), "tools", "quantize", "pack_sdcpp.py")
+    if not os.path.exists(ref_packer):
+        pytest.skip("reference tree not mounted")
+    rng = np.random.default_rng(404)
+    for i in range(8):
+        src = str(tmp_path / ("r%d.safetensors" % i))
+        names = random_safetensors(rng, src, oracle)
+        extra = [[], ["--only", names[0][:2]], ["--dtype-preserve", "F16:BF16"]][i % 3]
+        a, b = str(tmp_path / "ref.sdcpp"), str(tmp_path / "mine.sdcpp")
+        subprocess.run([sys.executable, ref_packer, src, a] + extra, check=True, stdout=subprocess.DEVNULL)
+        kw = {}
+        if extra:
+            kw = {"only": extra[1]} if extra[0] == "--only" else {"dtype_preserve": extra[1]}
+        pack_oracle.pack(src, b, oracle, **kw)
+        assert open(a, "rb").read() == open(b, "rb").read(), (i, extra)
