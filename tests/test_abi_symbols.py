@@ -4,7 +4,6 @@ import os
 import re
 import subprocess
 
-import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

@@ -8,7 +8,6 @@ import ctypes as C
 import os
 
 import numpy as np
-import pytest
 
 from oracle import pack_oracle
 
