@@ -133,7 +133,8 @@ SDQ_API int sdq_weight_release(sdq_weight_t w);
  * runs afterwards (src/model/ovi_dit.cpp:71-79); SDQ_GELU_TANH fuses the
  * activation between the two FFN linears (src/model/ovi_dit.cpp:132-142,
  * 214-222).  A and out are device memory unless SDQ_A_HOST / SDQ_OUT_HOST.
- * M == 0 is a no-op (src/core/qgemm.cpp:76); a weight always has N >= 1 and K >= 1. */
+ * M == 0 is a no-op (src/core/qgemm.cpp:76); a weight always has N >= 1 and K >= 1.
+ * Like the reference (src/core/qgemm.cpp:21), the int32 sums cannot overflow for K <= 133152. */
 SDQ_API int sdq_qgemm(sdq_weight_t w, const float* A, int64_t M, float* out, const float* bias,
               uint32_t flags, void* stream);
 
