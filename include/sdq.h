@@ -199,6 +199,31 @@ SDQ_API int sdq_ffn_pair(sdq_weight_t w1, const float* bias1_dev, sdq_weight_t w
                          const float* bias2_dev, const float* x, int64_t M, float* hidden_dev,
                          float* y, uint32_t flags, void* stream);
 
+/* A linear followed by the residual update its caller in the reference runs as separate
+ * passes over [M,N]:  out = residual + (qgemm(A, W) + bias) * gate[j].
+ * With `gate_dev` (fp32 [N]) this is mlin + gated_add_inplace (src/model/ovi_dit.cpp:66-84,
+ * 152-159; call sites :205-212 and :214-222); with gate_dev NULL it is mlin + add_inplace
+ * (:144-149; call sites :254-255 and :266-267).  `residual_dev` is fp32 [M,N] and may be
+ * `out_dev` itself (the reference updates x in place).  The multiply-add is ONE fused
+ * operation, as in the reference built by its own Makefile (-O3 on an FMA target; checked
+ * against the compiled function), so the result is bit-identical to that build.  Device
+ * pointers only. */
+SDQ_API int sdq_qgemm_residual(sdq_weight_t w, const float* A_dev, int64_t M,
+                               const float* residual_dev, const float* gate_dev, float* out_dev,
+                               const float* bias_dev, uint32_t flags, void* stream);
+
+/* The whole ffn_fwd of a DiT block (src/model/ovi_dit.cpp:214-222), in place on x fp32 [M,D]:
+ *   h = layernorm(x) * (1 + scale) + shift;  y = fc2(gelu_tanh(fc1(h)));  x += y * gate
+ * as four launches: layernorm + modulation + quantization fused (sdq_layernorm_mod_quantize),
+ * fc1 + bias + GELU, quantization, fc2 + bias + gated residual.  shift / scale / gate are
+ * fp32 [D] (rows 3, 4, 5 of the block's modulation table).  The layernorm sums are tree sums
+ * and the GELU uses the device's ex2/rcp, so x matches the CPU within the 1e-3 bound rather
+ * than bit for bit.  D % 4 == 0, D <= 16384; device pointers only. */
+SDQ_API int sdq_ffn_block(sdq_weight_t w1, const float* bias1_dev, sdq_weight_t w2,
+                          const float* bias2_dev, float* x_dev, int64_t M, const float* shift_dev,
+                          const float* scale_dev, const float* gate_dev, float eps, uint32_t flags,
+                          void* stream);
+
 /* The same computation as sdq_qgemm for callers that cannot allocate device memory
  * while they run (a host that has given all HBM to its own pool, a plugin inside
  * another allocator, a section where cudaMalloc's implicit device-wide

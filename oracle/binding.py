@@ -45,7 +45,8 @@ class Oracle:
         for name in ("orc_act_quant_rows", "orc_dot_s32", "orc_rescale", "orc_qgemm",
                      "orc_bias_add", "orc_gelu_tanh", "orc_quantize_rowwise",
                      "orc_quant_rows_packer", "orc_dequant_rows", "orc_f32_to_bf16",
-                     "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads", "orc_layernorm_mod"):
+                     "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads", "orc_layernorm_mod",
+                     "orc_residual_add"):
             getattr(L, name).restype = None
 
     def threads(self):
@@ -90,6 +91,15 @@ class Oracle:
         b = _c(b, np.float32)
         self.lib.orc_bias_add(_ptr(y), _ptr(b), i64(y.shape[0]), i64(y.shape[1]))
         return y
+
+    def residual_add(self, x, y, gate=None):
+        """x + y * gate (one fused multiply-add per element) or x + y; returns a new array."""
+        x = np.array(x, dtype=np.float32, order="C", copy=True)
+        y = _c(y, np.float32)
+        gate = None if gate is None else _c(gate, np.float32)
+        self.lib.orc_residual_add(_ptr(x), _ptr(y), None if gate is None else _ptr(gate),
+                                  i64(x.shape[0]), i64(x.shape[1]))
+        return x
 
     def gelu_tanh(self, x, inplace=False):
         x = x if inplace else np.array(x, dtype=np.float32, order="C", copy=True)
@@ -206,6 +216,59 @@ class Reference:
         self.lib.sdref_layernorm.restype = None
         self.lib.sdref_layernorm(_ptr(x), i64(M), i64(K), C.c_float(eps), _ptr(y))
         return y
+
+    # ---- caller-side helpers of src/model/ovi_dit.cpp (ref_shim_dit.cpp) ----
+    def gated_add(self, x, y, gate):
+        x = np.array(x, dtype=np.float32, order="C", copy=True)
+        y, gate = _c(y, np.float32), _c(gate, np.float32)
+        self.lib.sdref_gated_add.restype = None
+        self.lib.sdref_gated_add(_ptr(x), _ptr(y), _ptr(gate), i64(x.shape[0]), i64(x.shape[1]))
+        return x
+
+    def add(self, x, y):
+        x = np.array(x, dtype=np.float32, order="C", copy=True)
+        y = _c(y, np.float32)
+        self.lib.sdref_add.restype = None
+        self.lib.sdref_add(_ptr(x), _ptr(y), i64(x.size))
+        return x
+
+    def mod_rows(self, x, shift, scale):
+        x, shift, scale = _c(x, np.float32), _c(shift, np.float32), _c(scale, np.float32)
+        y = np.empty(x.shape, np.float32)
+        self.lib.sdref_mod_rows.restype = None
+        self.lib.sdref_mod_rows(_ptr(x), _ptr(shift), _ptr(scale), i64(x.shape[0]), i64(x.shape[1]), _ptr(y))
+        return y
+
+    def gelu_tanh(self, x):
+        x = np.array(x, dtype=np.float32, order="C", copy=True)
+        self.lib.sdref_gelu_tanh.restype = None
+        self.lib.sdref_gelu_tanh(_ptr(x), i64(x.size))
+        return x
+
+    def mlin_i8(self, x, Bq, bs, bias=None):
+        x, Bq, bs = _c(x, np.float32), _c(Bq, np.int8), _c(bs, np.float32)
+        bias = None if bias is None else _c(bias, np.float32)
+        M, K = x.shape
+        N = Bq.shape[0]
+        y = np.zeros((M, N), np.float32)
+        self.lib.sdref_mlin_i8.restype = None
+        self.lib.sdref_mlin_i8(_ptr(x), i64(M), i64(K), _ptr(Bq), _ptr(bs),
+                               None if bias is None else _ptr(bias), i64(N), _ptr(y))
+        return y
+
+    def ffn_fwd(self, x, e, q1, s1, b1, q2, s2, b2):
+        """The reference's ffn_fwd on x[M,D] with the [6,D] modulation table e; returns new x."""
+        x = np.array(x, dtype=np.float32, order="C", copy=True)
+        e, q1, s1, q2, s2 = _c(e, np.float32), _c(q1, np.int8), _c(s1, np.float32), _c(q2, np.int8), _c(s2, np.float32)
+        b1 = None if b1 is None else _c(b1, np.float32)
+        b2 = None if b2 is None else _c(b2, np.float32)
+        M, D = x.shape
+        F = q1.shape[0]
+        self.lib.sdref_ffn_fwd.restype = None
+        self.lib.sdref_ffn_fwd(_ptr(x), i64(M), i64(D), i64(F), _ptr(e), _ptr(q1), _ptr(s1),
+                               None if b1 is None else _ptr(b1), _ptr(q2), _ptr(s2),
+                               None if b2 is None else _ptr(b2))
+        return x
 
     def load_sdcpp_listing(self, path):
         """(count, listing) or raises RuntimeError with the loader's message."""

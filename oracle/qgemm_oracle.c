@@ -221,6 +221,27 @@ void orc_bias_add(float* y, const float* b, int64_t M, int64_t N) {
   par_rows(M, bias_range, &j);
 }
 
+/* x += y * gate (src/model/ovi_dit.cpp:152-159) or x += y (src/model/ovi_dit.cpp:144-149).
+ * The reference is built -O3 for an FMA target, where GCC contracts x + y*g into one fused
+ * multiply-add; fmaf states that explicitly (this file is built with contraction off) and is
+ * bit-identical to the compiled reference function. */
+static void residual_range(int64_t b, int64_t e, void* p) {
+  job_t* j = (job_t*)p;
+  const int64_t N = j->N;
+  const float* y = j->A;
+  const float* gate = j->bias;
+  for (int64_t i = b; i < e; i++)
+    for (int64_t c = 0; c < N; c++)
+      j->out[i * N + c] = gate ? fmaf(y[i * N + c], gate[c], j->out[i * N + c])
+                               : j->out[i * N + c] + y[i * N + c];
+}
+
+void orc_residual_add(float* x, const float* y, const float* gate_or_null, int64_t M, int64_t N) {
+  job_t j = {0};
+  j.out = x; j.A = y; j.bias = gate_or_null; j.M = M; j.N = N;
+  par_rows(M, residual_range, &j);
+}
+
 /* src/model/ovi_dit.cpp:132-142.  tanhf differs between libms by an ulp or
  * two, so this one is compared under a tolerance, never bit-for-bit. */
 static void gelu_range(int64_t b, int64_t e, void* p) {
@@ -322,7 +343,9 @@ static void ln_range(int64_t b, int64_t e, void* p) {
     float* o = j->y + i * N;
     for (int64_t k = 0; k < N; k++) {
       const float ln = (r[k] - mu) * inv * 1.0f + 0.0f;
-      o[k] = ln * (1.0f + j->scale[k]) + j->shift[k];
+      /* mod_rows (src/model/ovi_dit.cpp:162-173): one fused multiply-add in the reference's
+       * -O3 build for an FMA target, as checked against the compiled function */
+      o[k] = fmaf(ln, 1.0f + j->scale[k], j->shift[k]);
     }
   }
 }

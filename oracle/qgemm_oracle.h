@@ -44,6 +44,11 @@ void orc_qgemm(const float* A, const int8_t* Bq, const float* bs, int64_t M, int
 /* y[i,j] += b[j]  (src/model/ovi_dit.cpp:71-79). */
 void orc_bias_add(float* y, const float* b, int64_t M, int64_t N);
 
+/* x[i,j] += y[i,j] * gate[j]  (gated_add_inplace, src/model/ovi_dit.cpp:152-159; one fused
+ * multiply-add as in the reference's -O3 build) or, with gate NULL, x += y (add_inplace,
+ * src/model/ovi_dit.cpp:144-149). */
+void orc_residual_add(float* x, const float* y, const float* gate_or_null, int64_t M, int64_t N);
+
 /* GELU, tanh form, in place (src/model/ovi_dit.cpp:132-142). */
 void orc_gelu_tanh(float* x, int64_t n);
 
@@ -62,7 +67,7 @@ void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t
 void orc_layernorm_mod(const float* x, int64_t M, int64_t K, const float* shift,
                        const float* scale, float eps, float* y);
 
-/* Threads used by the loops above (OpenMP); <=0 restores the default. */
+/* Threads used by the loops above; <=0 restores the default. */
 void orc_set_threads(int n);
 int orc_threads(void);
 

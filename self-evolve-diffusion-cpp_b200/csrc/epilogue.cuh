@@ -33,4 +33,13 @@ __device__ __forceinline__ float epilogue_value(int acc, float a_scale, float b_
   return o;
 }
 
+// The residual update the reference's callers run on a linear's output y:
+//   x[i,j] += y[i,j] * gate[j]   (gated_add_inplace, reference src/model/ovi_dit.cpp:152-159)
+//   x[i,j] += y[i,j]             (add_inplace, reference src/model/ovi_dit.cpp:144-149)
+// The reference is built -O3 for an FMA target and GCC contracts the first form into one fused
+// multiply-add (checked against the compiled function), so fmaf is the bit-exact form here.
+__device__ __forceinline__ float residual_value(float y, float x, const float* gate) {
+  return gate ? fmaf(y, *gate, x) : __fadd_rn(x, y);
+}
+
 }  // namespace sdq

@@ -47,8 +47,9 @@ __global__ void __launch_bounds__(256) qgemm_simt_kernel(GemmArgs g) {
       const int64_t gn = n0 + tx * 2 + j;
       if (gn >= g.N) continue;
       if (g.acc_dump) g.acc_dump[gm * g.N + gn] = acc[i][j];
-      g.out[gm * g.N + gn] =
-          epilogue_value(acc[i][j], as, g.b_scale[gn], g.bias ? g.bias + gn : nullptr, gelu);
+      float o = epilogue_value(acc[i][j], as, g.b_scale[gn], g.bias ? g.bias + gn : nullptr, gelu);
+      if (g.residual) o = residual_value(o, g.residual[gm * g.N + gn], g.gate ? g.gate + gn : nullptr);
+      g.out[gm * g.N + gn] = o;
     }
   }
 }

@@ -231,6 +231,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
               case 2: chunk_values<false, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
               default: chunk_values<true, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
             }
+            if (g.residual) {
+              float4 x[8];
+              chunk_load_residual(g.residual + row * g.N, row_ok, nc, g.N, x);
+              chunk_add_residual(o, x, g.gate, nc, g.N);
+            }
             // The values go through a swizzled 32x32 fp32 box in shared memory; one bulk
             // tensor store then writes full 128-byte lines and clips rows >= M, columns >= N.
             if (lane == 0) bulk_wait_read<0>();  // the previous store has finished reading the box
@@ -253,8 +258,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 #pragma unroll
             for (int j = 0; j < 32; j++) {
               if (nc + j < g.N) {
-                out_row[nc + j] = epilogue_value((int)r[j], a_s, __ldg(g.b_scale + nc + j),
-                                                 g.bias ? g.bias + nc + j : nullptr, gelu);
+                float o = epilogue_value((int)r[j], a_s, __ldg(g.b_scale + nc + j),
+                                         g.bias ? g.bias + nc + j : nullptr, gelu);
+                if (g.residual)
+                  o = residual_value(o, g.residual[row * g.N + nc + j], g.gate ? g.gate + nc + j : nullptr);
+                out_row[nc + j] = o;
                 if (dump_row) dump_row[nc + j] = (int)r[j];
               }
             }
@@ -295,8 +303,10 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(GemmArgs g) {
     const int64_t row = i / g.N, col = i - row * g.N;
     const int acc = g.splitk_acc[i];
     if (g.acc_dump) g.acc_dump[i] = acc;
-    g.out[i] = epilogue_value(acc, g.a_scale[row], __ldg(g.b_scale + col),
-                              g.bias ? g.bias + col : nullptr, gelu);
+    float o = epilogue_value(acc, g.a_scale[row], __ldg(g.b_scale + col),
+                             g.bias ? g.bias + col : nullptr, gelu);
+    if (g.residual) o = residual_value(o, g.residual[i], g.gate ? g.gate + col : nullptr);
+    g.out[i] = o;
   }
 }
 
@@ -311,7 +321,8 @@ cudaError_t launch_t(const GemmArgs& g, int sm_count, cudaStream_t s, std::strin
   // Bulk tensor stores need a 16-byte aligned base and row pitch; the accumulator dump
   // (a debugging aid) and odd N keep the per-thread store path.
   const int use_tma_store = (g.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0) &&
-                            g.acc_dump == nullptr && g.k_splits <= 1;
+                            g.acc_dump == nullptr && g.k_splits <= 1 &&
+                            (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0;
   if (g.k_splits > 1) {
     if (!make_out_tmap(&tout, g.splitk_acc, g.M, g.N, why, CU_TENSOR_MAP_DATA_TYPE_INT32))
       return cudaErrorInvalidValue;

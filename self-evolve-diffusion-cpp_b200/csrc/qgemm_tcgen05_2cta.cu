@@ -105,7 +105,7 @@ struct OutMaps {
 
 // kStages2: depth of the operand ring; kBoxes: staging boxes per epilogue warp (with two, a
 // warp fills one box while the bulk store of the other is still reading shared memory).
-template <int kStages2, int kBoxes>
+template <int kStages2, int kBoxes, bool kResidual>
 __global__ void __launch_bounds__(kNumThreads, 1)
     qgemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
@@ -245,6 +245,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (nc >= g.N) break;
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + abuf * kBlockN2 + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+          float4 x[8];
+          if (kResidual)  // in flight while the accumulators arrive from tensor memory
+            chunk_load_residual(g.residual + row * g.N, row < g.M, nc, g.N, x);
           tmem_ld_wait();
           float o[32];
           switch (mode) {
@@ -253,6 +256,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             case 2: chunk_values<false, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
             default: chunk_values<true, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
           }
+          if (kResidual) chunk_add_residual(o, x, g.gate, nc, g.N);
           const uint32_t box = box0 + box_sel * 4096;
           if (kBoxes > 1) box_sel ^= 1u;
           // the store that last read this box must have finished reading it
@@ -310,11 +314,12 @@ int tc2_config() {
 }
 
 int qgemm_tc2_setup(std::string* why) {
-  cudaError_t a = cudaFuncSetAttribute(qgemm_tc2_kernel<6, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       smem_bytes2(6, 1));
-  if (a == cudaSuccess)
-    a = cudaFuncSetAttribute(qgemm_tc2_kernel<5, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem_bytes2(5, 2));
+  cudaError_t a = cudaSuccess;
+  const void* kernels[4] = {(const void*)qgemm_tc2_kernel<6, 1, false>, (const void*)qgemm_tc2_kernel<6, 1, true>,
+                            (const void*)qgemm_tc2_kernel<5, 2, false>, (const void*)qgemm_tc2_kernel<5, 2, true>};
+  for (int i = 0; i < 4 && a == cudaSuccess; i++)
+    a = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             i < 2 ? smem_bytes2(6, 1) : smem_bytes2(5, 2));
   if (a != cudaSuccess) {
     if (why) *why = std::string("cudaFuncSetAttribute(2-CTA GEMM, max dynamic smem): ") + cudaGetErrorString(a);
     return SDQ_ERR_CUDA;
@@ -330,6 +335,7 @@ bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count) {
     return v ? atoi(v) : 0;
   }();
   if (g.acc_dump) return false;
+  if (g.residual && (g.out_copies > 0 || (reinterpret_cast<uintptr_t>(g.residual) & 15) != 0)) return false;
   if (g.out_copies > 0) {
     // every destination 16-byte aligned with a 16-byte row pitch and column offset
     if (g.out_ld % 4 != 0 || g.out_col0 % 4 != 0) return false;
@@ -377,8 +383,12 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, st
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   count_launch();
-  if (deep) return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1>, ta, tb, outs, num_outs, g);
-  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2>, ta, tb, outs, num_outs, g);
+  if (g.residual) {
+    if (deep) return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1, true>, ta, tb, outs, num_outs, g);
+    return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2, true>, ta, tb, outs, num_outs, g);
+  }
+  if (deep) return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1, false>, ta, tb, outs, num_outs, g);
+  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2, false>, ta, tb, outs, num_outs, g);
 }
 
 }  // namespace sdq

@@ -224,10 +224,10 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
       if (idx < k4) {
         const float4 sc = __ldg(reinterpret_cast<const float4*>(scale) + idx);
         const float4 sh = __ldg(reinterpret_cast<const float4*>(shift) + idx);
-        v[i].x = __fadd_rn(__fmul_rn(__fmul_rn(v[i].x - mu, inv), 1.0f + sc.x), sh.x);
-        v[i].y = __fadd_rn(__fmul_rn(__fmul_rn(v[i].y - mu, inv), 1.0f + sc.y), sh.y);
-        v[i].z = __fadd_rn(__fmul_rn(__fmul_rn(v[i].z - mu, inv), 1.0f + sc.z), sh.z);
-        v[i].w = __fadd_rn(__fmul_rn(__fmul_rn(v[i].w - mu, inv), 1.0f + sc.w), sh.w);
+        v[i].x = fmaf(__fmul_rn(v[i].x - mu, inv), 1.0f + sc.x, sh.x);
+        v[i].y = fmaf(__fmul_rn(v[i].y - mu, inv), 1.0f + sc.y, sh.y);
+        v[i].z = fmaf(__fmul_rn(v[i].z - mu, inv), 1.0f + sc.z, sh.z);
+        v[i].w = fmaf(__fmul_rn(v[i].w - mu, inv), 1.0f + sc.w, sh.w);
         mx = fold_abs(fold_abs(fold_abs(fold_abs(mx, v[i].x), v[i].y), v[i].z), v[i].w);
         if (h_out) reinterpret_cast<float4*>(h_out + row * K)[idx] = v[i];
       }

@@ -97,11 +97,13 @@ int check_status_word() {
 }
 
 int run_gemm(const Weight& w, const int8_t* aq, const float* a_scale, int64_t M, float* out,
-             const float* bias, int32_t* acc_dump, uint32_t flags, cudaStream_t s) {
+             const float* bias, int32_t* acc_dump, uint32_t flags, cudaStream_t s,
+             const float* residual = nullptr, const float* gate = nullptr) {
   GemmArgs g;
   g.aq = aq; g.a_scale = a_scale; g.bq = w.q; g.b_scale = w.scale; g.bias = bias; g.out = out;
   g.acc_dump = acc_dump; g.M = M; g.N = w.N; g.K = w.K; g.flags = flags & SDQ_GELU_TANH;
   g.status = g_ctx->status;
+  g.residual = residual; g.gate = residual ? gate : nullptr;
   if (!(flags & SDQ_FORCE_SIMT) && qgemm_tc_supported(g)) {
     std::string why;
     const int splits = qgemm_tc_plan_splits(g, g_ctx->sm_count);
@@ -515,6 +517,31 @@ int sdq_qgemm(sdq_weight_t h, const float* A, int64_t M, float* out, const float
   return SDQ_OK;
 }
 
+int sdq_qgemm_residual(sdq_weight_t h, const float* A_dev, int64_t M, const float* residual_dev,
+                       const float* gate_dev, float* out_dev, const float* bias_dev,
+                       uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm_residual: bad weight handle");
+  if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_qgemm_residual: negative M");
+  if (flags & (SDQ_A_HOST | SDQ_OUT_HOST))
+    return fail(SDQ_ERR_INVALID, "sdq_qgemm_residual: device pointers only");
+  if (M == 0) return SDQ_OK;
+  if (!A_dev || !residual_dev || !out_dev) return fail(SDQ_ERR_INVALID, "sdq_qgemm_residual: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  if (int rc = grow(&ws->aq, &ws->aq_bytes, (size_t)M * w->K)) return rc;
+  if (int rc = grow(&ws->a_scale, &ws->a_scale_bytes, (size_t)M * 4)) return rc;
+  SDQ_CUDA(launch_act_quant(A_dev, M, w->K, ws->aq, ws->a_scale, g_ctx->sm_count, s));
+  if (int rc = run_gemm(*w, ws->aq, ws->a_scale, M, out_dev, bias_dev, nullptr, flags, s, residual_dev, gate_dev))
+    return rc;
+  return (flags & SDQ_SYNC) ? sdq_stream_sync(stream) : SDQ_OK;
+}
+
 // ---- column split across GPUs ----
 int sdq_ipc_export(const void* dptr, unsigned char handle[64]) {
   if (int rc = need_ctx()) return rc;
@@ -676,6 +703,43 @@ int sdq_ffn_pair(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, const
   SDQ_CUDA(cudaStreamWaitEvent(s, c->ev_out_done[1], 0));
   SDQ_CUDA(cudaStreamSynchronize(c->copy_out));
   return sdq_stream_sync(stream);
+}
+
+int sdq_ffn_block(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, const float* bias2_dev,
+                  float* x_dev, int64_t M, const float* shift_dev, const float* scale_dev,
+                  const float* gate_dev, float eps, uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w1 = get_weight(h1);
+  Weight* w2 = get_weight(h2);
+  if (!w1 || !w2) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: bad weight handle");
+  if (w2->K != w1->N) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: fc2 input width differs from fc1 output width");
+  if (w2->N != w1->K) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: fc2 output width differs from the width of x");
+  if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: negative M");
+  if (flags & (SDQ_A_HOST | SDQ_OUT_HOST)) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: device pointers only");
+  if (M == 0) return SDQ_OK;
+  if (!x_dev || !shift_dev || !scale_dev || !gate_dev) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  const int64_t D = w1->K, F = w1->N;
+  if (int rc = grow(&ws->aq, &ws->aq_bytes, (size_t)M * std::max(D, F))) return rc;
+  if (int rc = grow(&ws->a_scale, &ws->a_scale_bytes, (size_t)M * 4)) return rc;
+  if (int rc = grow(&ws->out_stage, &ws->out_stage_bytes, (size_t)M * F * 4)) return rc;
+  float* hbuf = ws->out_stage;
+  // layernorm + modulation + quantization of x in one pass: fp32 h is never written
+  cudaError_t e = launch_ln_mod_quant(x_dev, M, D, shift_dev, scale_dev, eps, ws->aq, ws->a_scale,
+                                      nullptr, g_ctx->sm_count, s);
+  if (e == cudaErrorInvalidValue)
+    return fail(SDQ_ERR_INVALID, "sdq_ffn_block: needs a width with K % 4 == 0, K <= 16384 and 16-byte aligned pointers");
+  SDQ_CUDA(e);
+  if (int rc = run_gemm(*w1, ws->aq, ws->a_scale, M, hbuf, bias1_dev, nullptr, SDQ_GELU_TANH, s)) return rc;
+  SDQ_CUDA(launch_act_quant(hbuf, M, F, ws->aq, ws->a_scale, g_ctx->sm_count, s));
+  // fc2 + bias, then x += y * gate in the same epilogue (x is read and written in place)
+  if (int rc = run_gemm(*w2, ws->aq, ws->a_scale, M, x_dev, bias2_dev, nullptr, 0, s, x_dev, gate_dev)) return rc;
+  return (flags & SDQ_SYNC) ? sdq_stream_sync(stream) : SDQ_OK;
 }
 
 // ---- weight quantizers ----

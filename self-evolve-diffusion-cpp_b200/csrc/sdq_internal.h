@@ -53,6 +53,10 @@ struct GemmArgs {
   int64_t out_col0 = 0, out_ld = 0;
   int out_copies = 0;
   float* out_all[8] = {};
+  // Residual epilogue: out = residual + y * gate[j] (gate null: residual + y), y being the
+  // value the epilogue would otherwise store.  residual is fp32 [M,N] and may be `out` itself.
+  const float* residual = nullptr;
+  const float* gate = nullptr;    // [N] or null; only read when residual is set
   int32_t* splitk_acc = nullptr;  // [M,N] zeroed int32 sums when K is split, else null
   int k_splits = 1;               // >1 only together with splitk_acc
 };

@@ -274,6 +274,38 @@ __device__ __forceinline__ void chunk_values(const uint32_t (&r)[32], float a_s,
   }
 }
 
+// The 32 values of x (the residual) that belong to one thread's chunk, loaded with ordinary
+// coherent loads: x may be the output buffer itself (the update is in place in the reference),
+// and each element is read only by the thread that later writes it.
+__device__ __forceinline__ void chunk_load_residual(const float* __restrict__ res_row, bool row_ok,
+                                                    int64_t nc, int64_t N, float4 (&x)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    x[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row_ok && nc + 4 * j < N) x[j] = *reinterpret_cast<const float4*>(res_row + nc + 4 * j);
+  }
+}
+
+// o = x + o * gate[j] (one fused multiply-add) or x + o when there is no gate.
+__device__ __forceinline__ void chunk_add_residual(float (&o)[32], const float4 (&x)[8],
+                                                   const float* __restrict__ gate, int64_t nc,
+                                                   int64_t N) {
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float xs[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
+    if (gate) {
+      float4 gg = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (nc + 4 * j < N) gg = __ldg(reinterpret_cast<const float4*>(gate + nc + 4 * j));
+      const float gs[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+      for (int t = 0; t < 4; t++) o[4 * j + t] = fmaf(o[4 * j + t], gs[t], xs[t]);
+    } else {
+#pragma unroll
+      for (int t = 0; t < 4; t++) o[4 * j + t] = __fadd_rn(xs[t], o[4 * j + t]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

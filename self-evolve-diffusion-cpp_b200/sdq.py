@@ -85,6 +85,10 @@ _SIGS = {
     "sdq_ipc_close": (C.c_int, [C.c_void_p]),
     "sdq_ffn_pair": (C.c_int, [C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64,
                                C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_qgemm_residual": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_ffn_block": (C.c_int, [C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64,
+                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_static_scratch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
                                            C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_quantize_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_void_p,
@@ -364,6 +368,31 @@ class Sdq:
         self._ck(self.lib.sdq_ffn_pair(w1, d1.ptr if d1 else None, w2, d2.ptr if d2 else None, _np_ptr(x), M,
                                        None, _np_ptr(y), A_HOST | OUT_HOST, None))
         return y
+
+    def qgemm_residual_np(self, w, A, x, gate=None, bias=None, inplace=True, force_simt=False):
+        """numpy in, numpy out: x + (qgemm(A, W) + bias) * gate through sdq_qgemm_residual, with
+        the residual either updated in place (out == residual) or read from a second buffer."""
+        A, x = np.ascontiguousarray(A, np.float32), np.ascontiguousarray(x, np.float32)
+        M, N = x.shape
+        dA, dx = self.to_device(A), self.to_device(x)
+        dg = self.to_device(np.ascontiguousarray(gate, np.float32)) if gate is not None else None
+        db = self.to_device(np.ascontiguousarray(bias, np.float32)) if bias is not None else None
+        dout = dx if inplace else self.alloc(M * N * 4)
+        self._ck(self.lib.sdq_qgemm_residual(w, dA.ptr, M, dx.ptr, dg.ptr if dg else None, dout.ptr,
+                                             db.ptr if db else None,
+                                             SYNC | (FORCE_SIMT if force_simt else 0), None))
+        return dout.to_numpy(np.float32, (M, N))
+
+    def ffn_block_np(self, w1, b1, w2, b2, x, shift, scale, gate, eps=1e-6):
+        """numpy in, numpy out through sdq_ffn_block (the reference's ffn_fwd, in place on x)."""
+        x = np.ascontiguousarray(x, np.float32)
+        M, D = x.shape
+        dx = self.to_device(x)
+        dev = [self.to_device(np.ascontiguousarray(a, np.float32)) if a is not None else None
+               for a in (b1, b2, shift, scale, gate)]
+        p = [d.ptr if d else None for d in dev]
+        self._ck(self.lib.sdq_ffn_block(w1, p[0], w2, p[1], dx.ptr, M, p[2], p[3], p[4], eps, SYNC, None))
+        return dx.to_numpy(np.float32, (M, D))
 
     def qgemm_static_scratch(self, wq_ptr, ws_ptr, N, K, A_ptr, M, out_ptr, bias_ptr=None, flags=0,
                              stream=None):

@@ -150,6 +150,30 @@ def main():
         q[tag] = {"M": M, "K": K, "N": N, "seed": seed, "a_mul": a_mul, "A_sha256": sha(A),
                   "Bq_sha256": sha(wq), "bs_sha256": sha(ws), "out_sha256": sha(y)}
     out["qgemm_digests"] = q
+
+    # ---- 5. the caller side of the linear, from the compiled src/model/ovi_dit.cpp: mlin (qgemm +
+    # bias pass), gated_add_inplace / add_inplace on its output, and a whole ffn_fwd
+    blk = {}
+    rng = np.random.default_rng(15)
+    M, K, N = 70, 256, 384
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    wq, ws = orc.quant_rows_packer(orc.bf16_to_f32(weights_bf16(rng, N, K, orc)))
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    gate = rng.standard_normal(N).astype(np.float32)
+    x = rng.standard_normal((M, N)).astype(np.float32)
+    y = ref.mlin_i8(A, wq, ws, bias)
+    blk.update(lin_A=A, lin_Bq=wq, lin_bs=ws, lin_bias=bias, lin_gate=gate, lin_x=x, lin_y=y,
+               lin_gated=ref.gated_add(x, y, gate), lin_added=ref.add(x, y))
+    M, D, F = 96, 256, 640
+    x = (rng.standard_normal((M, D)) * 1.5 + 0.2).astype(np.float32)
+    e = (rng.standard_normal((6, D)) * 0.3).astype(np.float32)
+    q1, s1 = orc.quant_rows_packer(orc.bf16_to_f32(weights_bf16(rng, F, D, orc)))
+    q2, s2 = orc.quant_rows_packer(orc.bf16_to_f32(weights_bf16(rng, D, F, orc)))
+    b1 = (rng.standard_normal(F) * 0.02).astype(np.float32)
+    b2 = (rng.standard_normal(D) * 0.02).astype(np.float32)
+    blk.update(ffn_x=x, ffn_e=e, ffn_q1=q1, ffn_s1=s1, ffn_b1=b1, ffn_q2=q2, ffn_s2=s2, ffn_b2=b2,
+               ffn_out=ref.ffn_fwd(x, e, q1, s1, b1, q2, s2, b2))
+    np.savez(os.path.join(HERE, "dit_caller.npz"), **blk)
     out["numpy"] = np.__version__
     json.dump(out, open(os.path.join(HERE, "golden.json"), "w"), indent=1, sort_keys=True)
     print("wrote fixtures to", HERE)

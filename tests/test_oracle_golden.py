@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 from oracle import pack_oracle
-from util import bits_equal, cosine, sha, weights_bf16
+from util import bits_equal, cosine, max_rel_err, sha, weights_bf16
 
 
 @pytest.fixture(scope="module")
@@ -115,8 +115,37 @@ def test_layernorm_restates_reference(oracle, reference):
     # modulation: y = ln * (1 + scale) + shift, per channel (src/model/ovi_dit.cpp:162-173)
     shift = rng.standard_normal(3072).astype(np.float32)
     scale = (rng.standard_normal(3072) * 0.1).astype(np.float32)
+    # the compiled reference fuses the multiply and the add into one operation
     ln = reference.layernorm(x, 1e-6)
-    assert bits_equal(oracle.layernorm_mod(x, shift, scale, 1e-6), ln * (np.float32(1) + scale) + shift)
+    assert bits_equal(oracle.layernorm_mod(x, shift, scale, 1e-6), reference.mod_rows(ln, shift, scale))
+
+
+def test_caller_side_matches_reference_fixture(oracle, golden_dir):
+    """mlin's bias pass, gated_add_inplace / add_inplace and a whole ffn_fwd, against outputs of
+    the compiled src/model/ovi_dit.cpp (tests/golden/dit_caller.npz)."""
+    z = np.load(os.path.join(golden_dir, "dit_caller.npz"))
+    y = oracle.bias_add(oracle.qgemm(z["lin_A"], z["lin_Bq"], z["lin_bs"]), z["lin_bias"])
+    assert bits_equal(y, z["lin_y"])
+    assert bits_equal(oracle.residual_add(z["lin_x"], y, z["lin_gate"]), z["lin_gated"])
+    assert bits_equal(oracle.residual_add(z["lin_x"], y), z["lin_added"])
+    # and the fused form really is what the compiled code does: mul-then-add differs
+    assert not bits_equal(z["lin_x"] + y * z["lin_gate"][None, :], z["lin_gated"])
+    # ffn_fwd: exact up to the GELU (tanhf vs the reference build's), so a tolerance of 1e-5 here
+    e = z["ffn_e"]
+    h = oracle.layernorm_mod(z["ffn_x"], e[3], e[4], 1e-6)
+    u = oracle.gelu_tanh(oracle.bias_add(oracle.qgemm(h, z["ffn_q1"], z["ffn_s1"]), z["ffn_b1"]))
+    v = oracle.bias_add(oracle.qgemm(u, z["ffn_q2"], z["ffn_s2"]), z["ffn_b2"])
+    got = oracle.residual_add(z["ffn_x"], v, e[5])
+    assert max_rel_err(got, z["ffn_out"]) < 1e-5
+
+
+def test_caller_side_live_reference(oracle, reference):
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((33, 130)).astype(np.float32)
+    y = rng.standard_normal((33, 130)).astype(np.float32)
+    g = rng.standard_normal(130).astype(np.float32)
+    assert bits_equal(oracle.residual_add(x, y, g), reference.gated_add(x, y, g))
+    assert bits_equal(oracle.residual_add(x, y), reference.add(x, y))
 
 
 def test_pack_file_matches_reference_packer(oracle, gold, golden_dir, tmp_path):
