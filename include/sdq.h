@@ -54,6 +54,9 @@ typedef uint64_t sdq_weight_t;
 #define SDQ_GELU_TANH 0x4u   /* apply GELU (tanh form) after the bias in the epilogue */
 #define SDQ_FORCE_SIMT 0x8u  /* use the portable CUDA-core kernel instead of tcgen05 */
 #define SDQ_SYNC 0x10u       /* wait for the stream before returning */
+#define SDQ_LN_TREE_SUMS 0x20u /* layernorm mean/variance as block-wide tree sums (one pass over
+                                  x, equal to the CPU to rounding error) instead of the
+                                  reference's left-to-right sums (bit-identical, two more passes) */
 
 /* source element types of sdq_quantize_rows (the packer's SRC table,
  * tools/quantize/pack_sdcpp.py:26-35) */
@@ -147,15 +150,19 @@ SDQ_API int sdq_quantize_activations(const float* A_dev, int64_t M, int64_t K, i
  * sd::qgemm: LayerNorm without affine parameters (blk::layernorm, src/model/blocks.cpp:18-43),
  * the per-channel modulation h = ln * (1 + scale[c]) + shift[c] (mod_rows,
  * src/model/ovi_dit.cpp:162-173; call sites :205-217) and the activation quantization
- * (src/core/qgemm.cpp:82-96), in one pass over x: fp32 `h` is never written unless
- * `h_out_dev` (fp32 [M,K], may be NULL) asks for it.  Feed aq / a_scale to
- * sdq_qgemm_prequantized.  The row mean and variance are tree sums, so h matches the CPU to
- * rounding error rather than bit for bit (an int8 value may differ by one step); the linear's
- * output stays within the 1e-3 bound.  K % 4 == 0, K <= 16384, pointers 16-byte aligned. */
+ * (src/core/qgemm.cpp:82-96): fp32 `h` is never written unless `h_out_dev` (fp32 [M,K], may be
+ * NULL) asks for it.  Feed aq / a_scale to sdq_qgemm_prequantized.
+ * By default the row mean and variance are the reference's own left-to-right fp32 sums (a
+ * first kernel runs one row per lane through the same chain of additions), the modulation is
+ * the single fused multiply-add of the reference's -O3 build, and h, aq and a_scale are
+ * bit-identical to the CPU's.  With SDQ_LN_TREE_SUMS the sums are block-wide trees in the same
+ * pass as everything else: about twice as fast for this step, h equal to rounding error, and an
+ * int8 value may differ by one step where h lands on a rounding boundary.
+ * K % 4 == 0, K <= 16384, pointers 16-byte aligned. */
 SDQ_API int sdq_layernorm_mod_quantize(const float* X_dev, int64_t M, int64_t K,
                                        const float* shift_dev, const float* scale_dev, float eps,
                                        int8_t* aq_dev, float* a_scale_dev, float* h_out_dev,
-                                       void* stream);
+                                       uint32_t flags, void* stream);
 
 /* Second half of sd::qgemm (src/core/qgemm.cpp:98-138) on activations that are
  * already quantized: lets a caller quantize x once and run the q, k and v
@@ -216,9 +223,10 @@ SDQ_API int sdq_qgemm_residual(sdq_weight_t w, const float* A_dev, int64_t M,
  *   h = layernorm(x) * (1 + scale) + shift;  y = fc2(gelu_tanh(fc1(h)));  x += y * gate
  * as four launches: layernorm + modulation + quantization fused (sdq_layernorm_mod_quantize),
  * fc1 + bias + GELU, quantization, fc2 + bias + gated residual.  shift / scale / gate are
- * fp32 [D] (rows 3, 4, 5 of the block's modulation table).  The layernorm sums are tree sums
- * and the GELU uses the device's ex2/rcp, so x matches the CPU within the 1e-3 bound rather
- * than bit for bit.  D % 4 == 0, D <= 16384; device pointers only. */
+ * fp32 [D] (rows 3, 4, 5 of the block's modulation table).  Everything is bit-identical to
+ * the CPU's except the GELU (the device's ex2/rcp against libm's tanh), so x matches the CPU
+ * within the 1e-3 bound; SDQ_LN_TREE_SUMS in `flags` trades the exact layernorm sums for one
+ * pass less over x.  D % 4 == 0, D <= 16384; device pointers only. */
 SDQ_API int sdq_ffn_block(sdq_weight_t w1, const float* bias1_dev, sdq_weight_t w2,
                           const float* bias2_dev, float* x_dev, int64_t M, const float* shift_dev,
                           const float* scale_dev, const float* gate_dev, float eps, uint32_t flags,

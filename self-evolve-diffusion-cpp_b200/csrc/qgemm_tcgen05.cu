@@ -411,6 +411,7 @@ Plan plan_small(const GemmArgs& g, int sm_count, bool allow_split) {
     for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
       if (splits > 1 && (!allow_split || kb / splits < 4 || g.N % 4 != 0)) continue;
       const int kbs = (kb + splits - 1) / splits;
+      if (splits > 1 && (splits - 1) * kbs >= kb) continue;  // the last slice would be empty
       const int64_t work = mb * ((g.N + bn - 1) / bn) * splits;
       const double waves = (double)((work + sm_count - 1) / sm_count);
       const double stage_bytes = BLOCK_M * BLOCK_K * rows_frac + (double)bn * BLOCK_K;

@@ -168,6 +168,11 @@ __global__ void __launch_bounds__(kThreads) act_quant_generic(const float* __res
 // The means and variances are block-wide tree sums, not the CPU's left-to-right sums, so
 // `h` agrees with the CPU to rounding error (not bit for bit) and an int8 value can differ
 // by one step where h lands on a rounding boundary.
+// (x - mu) * inv * 1.f + 0.f of blk::layernorm without affine parameters: the multiply by one
+// is exact, the add of +0 turns a -0 into +0.
+__device__ __forceinline__ float ln_value(float x, float mu, float inv) {
+  return __fadd_rn(__fmul_rn(__fsub_rn(x, mu), inv), 0.0f);
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -183,13 +188,98 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return warp_sum(r);
 }
 
+// ---- the reference's own row statistics, bit for bit ----
+// blk::layernorm adds the K values of a row left to right in fp32 (mean), then the squared
+// deviations left to right (variance): two dependent chains of K additions whose roundings
+// no tree sum reproduces.  Here one LANE owns one row and runs the same two chains, so a warp
+// carries 32 rows at once; the rows stream through a small ring of shared-memory tiles
+// (32 rows x 128 bytes, filled with 16-byte cp.async copies, 16-byte slots XOR-swizzled by
+// row so that both the row-major fill and the lane-per-row reads are conflict-free).
+// stats[row] = (mean, 1/sqrt(var + eps)).  Two passes over x (HBM-bound); the chains themselves
+// cost ~4 cycles per element per row and overlap the copies.
+constexpr int kStatStages = 4;
+constexpr int kStatWarps = 2;
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__global__ void __launch_bounds__(kStatWarps * 32)
+    row_stats_seq_kernel(const float* __restrict__ X, int64_t M, int64_t K, float eps,
+                         float2* __restrict__ stats) {
+  __shared__ __align__(128) uint8_t ring_mem[kStatWarps * kStatStages * 4096];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r0 = ((int64_t)blockIdx.x * kStatWarps + warp) * 32;
+  if (r0 >= M) return;
+  const uint32_t ring = smem_addr(ring_mem) + (uint32_t)(warp * kStatStages * 4096);
+  const int ntiles = (int)((K + 31) / 32);
+  const int sub = lane >> 3, piece = lane & 7;
+  const float kf = (float)K;
+
+  auto issue = [&](int t) {  // tile t: columns [32t, 32t+32) of the warp's 32 rows
+    if (t < ntiles) {
+      const uint32_t st = ring + (uint32_t)((t % kStatStages) * 4096);
+      const int64_t col = (int64_t)t * 32 + piece * 4;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int row = i * 4 + sub;
+        const bool ok = (r0 + row < M) && (col < K);  // K % 4 == 0: a 16-byte piece is all in or out
+        const float* src = ok ? X + (r0 + row) * K + col : X;
+        const uint32_t dst = st + (uint32_t)(row * 128 + ((piece ^ (row & 7)) << 4));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0)
+                     : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");  // one group per slot, empty or not
+  };
+
+  float mu = 0.0f, acc = 0.0f;
+  for (int pass = 0; pass < 2; pass++) {
+    acc = 0.0f;
+    for (int t = 0; t < kStatStages - 1; t++) issue(t);
+    for (int t = 0; t < ntiles; t++) {
+      issue(t + kStatStages - 1);  // into the stage every lane finished reading last iteration
+      asm volatile("cp.async.wait_group %0;" ::"n"(kStatStages - 1) : "memory");
+      __syncwarp();  // every lane's pieces of tile t have landed
+      const uint32_t mine = ring + (uint32_t)((t % kStatStages) * 4096 + lane * 128);
+      float x[32];
+#pragma unroll
+      for (int p = 0; p < 8; p++) {
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "r"(mine + (uint32_t)((p ^ (lane & 7)) << 4)));
+        x[4 * p] = v.x; x[4 * p + 1] = v.y; x[4 * p + 2] = v.z; x[4 * p + 3] = v.w;
+      }
+      const int n = (int)min((int64_t)32, K - (int64_t)t * 32);
+      if (pass == 0) {
+#pragma unroll
+        for (int c = 0; c < 32; c++)
+          if (c < n) acc = __fadd_rn(acc, x[c]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; c++) {
+          if (c < n) {
+            const float d = __fsub_rn(x[c], mu);
+            acc = __fadd_rn(acc, __fmul_rn(d, d));  // not fused: the reference's build does not fuse it
+          }
+        }
+      }
+      __syncwarp();  // the stage may be refilled from the next iteration on
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (pass == 0) mu = __fdiv_rn(acc, kf);
+  }
+  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(acc, kf), eps)));
+  if (r0 + lane < M) stats[r0 + lane] = make_float2(mu, inv);
+}
+
 template <int VPT>
 __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __restrict__ X, int64_t M,
                                                               int64_t K, const float* __restrict__ shift,
                                                               const float* __restrict__ scale, float eps,
                                                               int8_t* __restrict__ aq,
                                                               float* __restrict__ a_scale,
-                                                              float* __restrict__ h_out) {
+                                                              float* __restrict__ h_out,
+                                                              const float2* __restrict__ stats) {
   allow_dependent_launch();
   __shared__ float red[kThreads / 32];
   const int k4 = (int)(K >> 2);
@@ -206,17 +296,24 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
         s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
       }
     }
-    const float mu = block_sum(s, red) * inv_n;
-    float q = 0.0f;
+    float mu, inv;
+    if (stats) {  // the reference's left-to-right sums, from row_stats_seq_kernel
+      const float2 st = __ldg(stats + row);
+      mu = st.x;
+      inv = st.y;
+    } else {      // block-wide tree sums
+      mu = block_sum(s, red) * inv_n;
+      float q = 0.0f;
 #pragma unroll
-    for (int i = 0; i < VPT; i++) {
-      const int idx = threadIdx.x + i * kThreads;
-      if (idx < k4) {
-        const float a = v[i].x - mu, b = v[i].y - mu, c = v[i].z - mu, d = v[i].w - mu;
-        q += (a * a + b * b) + (c * c + d * d);
+      for (int i = 0; i < VPT; i++) {
+        const int idx = threadIdx.x + i * kThreads;
+        if (idx < k4) {
+          const float a = v[i].x - mu, b = v[i].y - mu, c = v[i].z - mu, d = v[i].w - mu;
+          q += (a * a + b * b) + (c * c + d * d);
+        }
       }
+      inv = 1.0f / sqrtf(block_sum(q, red) * inv_n + eps);
     }
-    const float inv = 1.0f / sqrtf(block_sum(q, red) * inv_n + eps);
     float mx = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
@@ -224,10 +321,10 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
       if (idx < k4) {
         const float4 sc = __ldg(reinterpret_cast<const float4*>(scale) + idx);
         const float4 sh = __ldg(reinterpret_cast<const float4*>(shift) + idx);
-        v[i].x = fmaf(__fmul_rn(v[i].x - mu, inv), 1.0f + sc.x, sh.x);
-        v[i].y = fmaf(__fmul_rn(v[i].y - mu, inv), 1.0f + sc.y, sh.y);
-        v[i].z = fmaf(__fmul_rn(v[i].z - mu, inv), 1.0f + sc.z, sh.z);
-        v[i].w = fmaf(__fmul_rn(v[i].w - mu, inv), 1.0f + sc.w, sh.w);
+        v[i].x = fmaf(ln_value(v[i].x, mu, inv), __fadd_rn(1.0f, sc.x), sh.x);
+        v[i].y = fmaf(ln_value(v[i].y, mu, inv), __fadd_rn(1.0f, sc.y), sh.y);
+        v[i].z = fmaf(ln_value(v[i].z, mu, inv), __fadd_rn(1.0f, sc.z), sh.z);
+        v[i].w = fmaf(ln_value(v[i].w, mu, inv), __fadd_rn(1.0f, sc.w), sh.w);
         mx = fold_abs(fold_abs(fold_abs(fold_abs(mx, v[i].x), v[i].y), v[i].z), v[i].w);
         if (h_out) reinterpret_cast<float4*>(h_out + row * K)[idx] = v[i];
       }
@@ -477,7 +574,7 @@ cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, f
 
 cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const float* shift,
                                 const float* scale, float eps, int8_t* aq, float* a_scale,
-                                float* h_out, int sm_count, cudaStream_t s) {
+                                float* h_out, float2* stats, int sm_count, cudaStream_t s) {
   if (M <= 0 || K <= 0) return cudaSuccess;
   const int64_t per_thread = (K / 4 + kThreads - 1) / kThreads;
   const bool ok = (K % 4 == 0) && per_thread <= 16 && ((reinterpret_cast<uintptr_t>(X) & 15) == 0) &&
@@ -486,14 +583,23 @@ cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const floa
                   ((reinterpret_cast<uintptr_t>(aq) & 3) == 0) &&
                   (!h_out || (reinterpret_cast<uintptr_t>(h_out) & 15) == 0);
   if (!ok) return cudaErrorInvalidValue;
+  if (stats) {
+    if ((reinterpret_cast<uintptr_t>(stats) & 7) != 0) return cudaErrorInvalidValue;
+    const int64_t groups = (M + 31) / 32;
+    count_launch();
+    row_stats_seq_kernel<<<(unsigned)((groups + kStatWarps - 1) / kStatWarps), kStatWarps * 32, 0, s>>>(
+        X, M, K, eps, stats);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
   int64_t blocks = M < (int64_t)sm_count * 8 ? M : (int64_t)sm_count * 8;
   count_launch();
   if (per_thread <= 3)
-    ln_mod_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out);
+    ln_mod_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats);
   else if (per_thread <= 8)
-    ln_mod_quant_regs<8><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out);
+    ln_mod_quant_regs<8><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats);
   else
-    ln_mod_quant_regs<16><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out);
+    ln_mod_quant_regs<16><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats);
   return cudaGetLastError();
 }
 

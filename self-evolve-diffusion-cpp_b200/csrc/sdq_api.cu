@@ -34,6 +34,7 @@ struct Workspace {
   float* a_stage = nullptr; size_t a_stage_bytes = 0;
   float* out_stage = nullptr; size_t out_stage_bytes = 0;
   int32_t* acc = nullptr; size_t acc_bytes = 0;   // split-K partial sums
+  float2* ln_stats = nullptr; size_t ln_stats_bytes = 0;  // per-row mean and 1/sqrt(var+eps)
 };
 
 struct Context {
@@ -448,16 +449,32 @@ int sdq_quantize_activations(const float* A_dev, int64_t M, int64_t K, int8_t* a
   return SDQ_OK;
 }
 
+// Scratch for the exact row statistics of stream s, or null when tree sums were asked for.
+static int ln_stats_for(cudaStream_t s, int64_t M, uint32_t flags, float2** out) {
+  *out = nullptr;
+  if (flags & SDQ_LN_TREE_SUMS) return SDQ_OK;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  if (int rc = grow(&ws->ln_stats, &ws->ln_stats_bytes, (size_t)M * sizeof(float2))) return rc;
+  *out = ws->ln_stats;
+  return SDQ_OK;
+}
+
 int sdq_layernorm_mod_quantize(const float* X_dev, int64_t M, int64_t K, const float* shift_dev,
                                const float* scale_dev, float eps, int8_t* aq_dev,
-                               float* a_scale_dev, float* h_out_dev, void* stream) {
+                               float* a_scale_dev, float* h_out_dev, uint32_t flags, void* stream) {
   if (int rc = need_ctx()) return rc;
   if (M < 0 || K < 0) return fail(SDQ_ERR_INVALID, "sdq_layernorm_mod_quantize: negative shape");
   if (M == 0 || K == 0) return SDQ_OK;
   if (!X_dev || !shift_dev || !scale_dev || !aq_dev || !a_scale_dev)
     return fail(SDQ_ERR_INVALID, "sdq_layernorm_mod_quantize: null pointer");
+  float2* stats;
+  if (int rc = ln_stats_for((cudaStream_t)stream, M, flags, &stats)) return rc;
   cudaError_t e = launch_ln_mod_quant(X_dev, M, K, shift_dev, scale_dev, eps, aq_dev, a_scale_dev,
-                                      h_out_dev, g_ctx->sm_count, (cudaStream_t)stream);
+                                      h_out_dev, stats, g_ctx->sm_count, (cudaStream_t)stream);
   if (e == cudaErrorInvalidValue)
     return fail(SDQ_ERR_INVALID, "sdq_layernorm_mod_quantize: needs K % 4 == 0, K <= 16384 and 16-byte aligned pointers");
   SDQ_CUDA(e);
@@ -730,8 +747,10 @@ int sdq_ffn_block(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, cons
   if (int rc = grow(&ws->out_stage, &ws->out_stage_bytes, (size_t)M * F * 4)) return rc;
   float* hbuf = ws->out_stage;
   // layernorm + modulation + quantization of x in one pass: fp32 h is never written
+  float2* stats;
+  if (int rc = ln_stats_for(s, M, flags, &stats)) return rc;
   cudaError_t e = launch_ln_mod_quant(x_dev, M, D, shift_dev, scale_dev, eps, ws->aq, ws->a_scale,
-                                      nullptr, g_ctx->sm_count, s);
+                                      nullptr, stats, g_ctx->sm_count, s);
   if (e == cudaErrorInvalidValue)
     return fail(SDQ_ERR_INVALID, "sdq_ffn_block: needs a width with K % 4 == 0, K <= 16384 and 16-byte aligned pointers");
   SDQ_CUDA(e);

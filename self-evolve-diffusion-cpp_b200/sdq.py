@@ -12,7 +12,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 # flags / codes of include/sdq.h
-A_HOST, OUT_HOST, GELU_TANH, FORCE_SIMT, SYNC = 0x1, 0x2, 0x4, 0x8, 0x10
+A_HOST, OUT_HOST, GELU_TANH, FORCE_SIMT, SYNC, LN_TREE_SUMS = 0x1, 0x2, 0x4, 0x8, 0x10, 0x20
 F32, BF16, F16 = 0, 1, 2
 MODE_PACKER, MODE_ROWWISE = 0, 1
 SRC_HOST, DST_HOST = 0x1, 0x2
@@ -75,7 +75,7 @@ _SIGS = {
     "sdq_qgemm": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_quantize_activations": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sdq_layernorm_mod_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_float,
-                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_prequantized": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_colsplit": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_void_p),
@@ -309,7 +309,7 @@ class Sdq:
         self.sync()
         return dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,))
 
-    def layernorm_mod_quantize(self, X, shift, scale, eps=1e-6, want_h=False):
+    def layernorm_mod_quantize(self, X, shift, scale, eps=1e-6, want_h=False, tree_sums=False):
         """numpy [M,K] -> (aq, a_scale[, h]) through the fused LayerNorm+modulation+quantize kernel."""
         X = np.ascontiguousarray(X, np.float32)
         M, K = X.shape
@@ -318,7 +318,8 @@ class Sdq:
         dq, ds = self.alloc(M * K), self.alloc(M * 4)
         dh = self.alloc(M * K * 4) if want_h else None
         self._ck(self.lib.sdq_layernorm_mod_quantize(dX.ptr, M, K, dsh.ptr, dsc.ptr, eps, dq.ptr, ds.ptr,
-                                                     dh.ptr if dh else None, None))
+                                                     dh.ptr if dh else None,
+                                                     LN_TREE_SUMS if tree_sums else 0, None))
         self.sync()
         out = (dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,)))
         return out + (dh.to_numpy(np.float32, (M, K)),) if want_h else out
@@ -383,7 +384,7 @@ class Sdq:
                                              SYNC | (FORCE_SIMT if force_simt else 0), None))
         return dout.to_numpy(np.float32, (M, N))
 
-    def ffn_block_np(self, w1, b1, w2, b2, x, shift, scale, gate, eps=1e-6):
+    def ffn_block_np(self, w1, b1, w2, b2, x, shift, scale, gate, eps=1e-6, tree_sums=False):
         """numpy in, numpy out through sdq_ffn_block (the reference's ffn_fwd, in place on x)."""
         x = np.ascontiguousarray(x, np.float32)
         M, D = x.shape
@@ -391,7 +392,8 @@ class Sdq:
         dev = [self.to_device(np.ascontiguousarray(a, np.float32)) if a is not None else None
                for a in (b1, b2, shift, scale, gate)]
         p = [d.ptr if d else None for d in dev]
-        self._ck(self.lib.sdq_ffn_block(w1, p[0], w2, p[1], dx.ptr, M, p[2], p[3], p[4], eps, SYNC, None))
+        self._ck(self.lib.sdq_ffn_block(w1, p[0], w2, p[1], dx.ptr, M, p[2], p[3], p[4], eps,
+                                        SYNC | (LN_TREE_SUMS if tree_sums else 0), None))
         return dx.to_numpy(np.float32, (M, D))
 
     def qgemm_static_scratch(self, wq_ptr, ws_ptr, N, K, A_ptr, M, out_ptr, bias_ptr=None, flags=0,

@@ -119,17 +119,36 @@ def test_dequant_rows(sdq, oracle):
     assert np.all(np.abs(sdq.dequant_rows(qq, ss) - W) < ss[:, None])
 
 
+@pytest.mark.parametrize("M,K", [(300, 3072), (64, 14336), (1000, 512), (33, 100), (1, 4), (2049, 3072)])
+def test_fused_layernorm_modulation_quantize_is_exact(sdq, oracle, M, K):
+    """LayerNorm + modulation + activation quantization with the reference's left-to-right row
+    sums (the default): h, the int8 bytes and the scales are bit-identical to the CPU chain."""
+    rng = np.random.default_rng(M + K)
+    x = (rng.standard_normal((M, K)) * 2 + 0.3).astype(np.float32)
+    if M > 2:
+        x[1, :] = 0.25                     # constant row: variance 0, h = shift
+        x[2, :] *= 1e-20
+    shift = (rng.standard_normal(K) * 0.5).astype(np.float32)
+    scale = (rng.standard_normal(K) * 0.1).astype(np.float32)
+    aq, a_s, h = sdq.layernorm_mod_quantize(x, shift, scale, 1e-6, want_h=True)
+    h_c = oracle.layernorm_mod(x, shift, scale, 1e-6)
+    aq_c, as_c = oracle.act_quant_rows(h_c)
+    assert bits_equal(h, h_c)
+    assert bits_equal(a_s, as_c)
+    assert bits_equal(aq, aq_c)
+
+
 @pytest.mark.parametrize("M,K", [(300, 3072), (64, 14336), (1000, 512)])
-def test_fused_layernorm_modulation_quantize(sdq, pkg, oracle, M, K):
-    """LayerNorm + modulation + activation quantization in one kernel.  The row sums are tree
-    sums while the CPU adds K fp32 values left to right (whose own rounding error grows with K),
-    so h is compared under a tolerance -- 5e-5 of the row's max -- and an int8 value may differ
-    by one step on a rounding boundary; the linear fed with it stays inside the 1e-3 bound."""
+def test_fused_layernorm_modulation_quantize_tree_sums(sdq, pkg, oracle, M, K):
+    """The one-pass variant (SDQ_LN_TREE_SUMS).  The row sums are tree sums while the CPU adds K
+    fp32 values left to right (whose own rounding error grows with K), so h is compared under a
+    tolerance -- 5e-5 of the row's max -- and an int8 value may differ by one step on a rounding
+    boundary; the linear fed with it stays inside the 1e-3 bound."""
     rng = np.random.default_rng(M + K)
     x = (rng.standard_normal((M, K)) * 2 + 0.3).astype(np.float32)
     shift = (rng.standard_normal(K) * 0.5).astype(np.float32)
     scale = (rng.standard_normal(K) * 0.1).astype(np.float32)
-    aq, a_s, h = sdq.layernorm_mod_quantize(x, shift, scale, 1e-6, want_h=True)
+    aq, a_s, h = sdq.layernorm_mod_quantize(x, shift, scale, 1e-6, want_h=True, tree_sums=True)
     h_c = oracle.layernorm_mod(x, shift, scale, 1e-6)
     aq_c, as_c = oracle.act_quant_rows(h_c)
     assert np.max(np.abs(h - h_c) / np.max(np.abs(h_c), axis=1, keepdims=True)) < 5e-5

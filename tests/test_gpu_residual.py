@@ -2,8 +2,8 @@
 
 The fused multiply-add of the gated update is bit-identical to the reference's own build
 (fixtures from the compiled src/model/ovi_dit.cpp: tests/golden/dit_caller.npz), on every
-kernel and store path; the chained block is held to the 1e-3 bound (its GELU and layernorm
-sums are not bit-reproducible across implementations).
+kernel and store path; the chained block is held to the 1e-3 bound (its GELU is not
+bit-reproducible across math libraries; everything else in it is exact).
 """
 import os
 
@@ -100,12 +100,11 @@ def test_ffn_block_full_width_matches_oracle_chain(sdq, pkg, oracle):
     v = oracle.bias_add(oracle.qgemm(u, q2, s2), b2)
     want = oracle.residual_add(x, v, gate)
     assert max_rel_err(got, want) < 1e-3
-    # The update alone (x cancels) is a stricter view: the fused layernorm's tree sums flip a
-    # few int8 steps of h, which two chained int8 linears carry to ~2.5e-3 of the largest update;
-    # with the CPU's own h the same chain stays inside 1e-3.
-    assert max_rel_err(got - x, want - x) < 5e-3
-    y_exact_h = sdq.ffn_pair_host(w1, b1, w2, b2, h)
-    assert max_rel_err(y_exact_h, v) < 1e-3
+    assert max_rel_err(got - x, want - x) < 1e-3          # the update alone (x cancels)
+    # With tree sums in the layernorm a few int8 steps of h flip (about 1 % of the rows have
+    # one), which two chained int8 linears carry to ~2.5e-3 of the largest update on those rows.
+    fast = sdq.ffn_block_np(w1, b1, w2, b2, x, shift, scale, gate, tree_sums=True)
+    assert max_rel_err(fast - x, want - x) < 5e-3
     # and the block equals its parts run one by one through the other entry points
     aq, a_s = sdq.layernorm_mod_quantize(x, shift, scale, 1e-6)
     dq, ds = sdq.to_device(aq), sdq.to_device(a_s)
