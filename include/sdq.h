@@ -58,6 +58,9 @@ typedef uint64_t sdq_weight_t;
                                   x, equal to the CPU to rounding error) instead of the
                                   reference's left-to-right sums (bit-identical, two more passes) */
 
+#define SDQ_LN_AFFINE 0x40u  /* sdq_layernorm_mod_quantize: `scale` and `shift` are the layernorm's
+                                own weight and bias, h = ln * weight + bias */
+
 /* source element types of sdq_quantize_rows (the packer's SRC table,
  * tools/quantize/pack_sdcpp.py:26-35) */
 #define SDQ_F32 0
@@ -158,6 +161,9 @@ SDQ_API int sdq_quantize_activations(const float* A_dev, int64_t M, int64_t K, i
  * bit-identical to the CPU's.  With SDQ_LN_TREE_SUMS the sums are block-wide trees in the same
  * pass as everything else: about twice as fast for this step, h equal to rounding error, and an
  * int8 value may differ by one step where h lands on a rounding boundary.
+ * With SDQ_LN_AFFINE the same kernels serve the layernorm that HAS parameters, in front of the
+ * cross-attention projections (src/model/ovi_dit.cpp:241, :264): scale_dev is its weight and
+ * shift_dev its bias, h = ln * weight + bias (one fused multiply-add, as in the reference's build).
  * K % 4 == 0, K <= 16384, pointers 16-byte aligned. */
 SDQ_API int sdq_layernorm_mod_quantize(const float* X_dev, int64_t M, int64_t K,
                                        const float* shift_dev, const float* scale_dev, float eps,

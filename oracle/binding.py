@@ -46,7 +46,7 @@ class Oracle:
                      "orc_bias_add", "orc_gelu_tanh", "orc_quantize_rowwise",
                      "orc_quant_rows_packer", "orc_dequant_rows", "orc_f32_to_bf16",
                      "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads", "orc_layernorm_mod",
-                     "orc_residual_add"):
+                     "orc_residual_add", "orc_layernorm_affine"):
             getattr(L, name).restype = None
 
     def threads(self):
@@ -134,6 +134,13 @@ class Oracle:
         M, K = x.shape
         y = np.empty((M, K), np.float32)
         self.lib.orc_layernorm_mod(_ptr(x), i64(M), i64(K), _ptr(shift), _ptr(scale), C.c_float(eps), _ptr(y))
+        return y
+
+    def layernorm_affine(self, x, weight, bias, eps=1e-6):
+        x, weight, bias = _c(x, np.float32), _c(weight, np.float32), _c(bias, np.float32)
+        M, K = x.shape
+        y = np.empty((M, K), np.float32)
+        self.lib.orc_layernorm_affine(_ptr(x), i64(M), i64(K), _ptr(weight), _ptr(bias), C.c_float(eps), _ptr(y))
         return y
 
     def f32_to_bf16(self, x):
@@ -269,6 +276,14 @@ class Reference:
                                None if b1 is None else _ptr(b1), _ptr(q2), _ptr(s2),
                                None if b2 is None else _ptr(b2))
         return x
+
+    def layernorm_affine(self, x, w, b, eps=1e-6):
+        x, w, b = _c(x, np.float32), _c(w, np.float32), _c(b, np.float32)
+        M, K = x.shape
+        y = np.empty((M, K), np.float32)
+        self.lib.sdref_layernorm_affine.restype = None
+        self.lib.sdref_layernorm_affine(_ptr(x), i64(M), i64(K), _ptr(w), _ptr(b), C.c_float(eps), _ptr(y))
+        return y
 
     def load_sdcpp_listing(self, path):
         """(count, listing) or raises RuntimeError with the loader's message."""

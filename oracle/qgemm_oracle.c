@@ -324,7 +324,7 @@ void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t
 }
 
 /* src/model/blocks.cpp:18-43 (w = b = null) then src/model/ovi_dit.cpp:162-173. */
-typedef struct { const float* x; const float* shift; const float* scale; float* y; int64_t K; float eps; } ln_t;
+typedef struct { const float* x; const float* shift; const float* scale; float* y; int64_t K; float eps; int affine; } ln_t;
 
 static void ln_range(int64_t b, int64_t e, void* p) {
   ln_t* j = (ln_t*)p;
@@ -342,6 +342,12 @@ static void ln_range(int64_t b, int64_t e, void* p) {
     const float inv = 1.0f / sqrtf(var / (float)N + j->eps);
     float* o = j->y + i * N;
     for (int64_t k = 0; k < N; k++) {
+      if (j->affine) {
+        /* blk::layernorm with weight and bias (src/model/blocks.cpp:39-40): the reference's
+         * build fuses the last multiply and the add, as checked against the compiled function */
+        o[k] = fmaf((r[k] - mu) * inv, j->scale[k], j->shift[k]);
+        continue;
+      }
       const float ln = (r[k] - mu) * inv * 1.0f + 0.0f;
       /* mod_rows (src/model/ovi_dit.cpp:162-173): one fused multiply-add in the reference's
        * -O3 build for an FMA target, as checked against the compiled function */
@@ -352,6 +358,12 @@ static void ln_range(int64_t b, int64_t e, void* p) {
 
 void orc_layernorm_mod(const float* x, int64_t M, int64_t K, const float* shift,
                        const float* scale, float eps, float* y) {
-  ln_t j = {x, shift, scale, y, K, eps};
+  ln_t j = {x, shift, scale, y, K, eps, 0};
+  par_rows(M, ln_range, &j);
+}
+
+void orc_layernorm_affine(const float* x, int64_t M, int64_t K, const float* weight,
+                          const float* bias, float eps, float* y) {
+  ln_t j = {x, bias, weight, y, K, eps, 1};
   par_rows(M, ln_range, &j);
 }

@@ -67,6 +67,11 @@ void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t
 void orc_layernorm_mod(const float* x, int64_t M, int64_t K, const float* shift,
                        const float* scale, float eps, float* y);
 
+/* LayerNorm WITH its affine parameters, y = ln(x) * weight[c] + bias[c]
+ * (src/model/blocks.cpp:18-43 with w, b given; call sites src/model/ovi_dit.cpp:241, :264). */
+void orc_layernorm_affine(const float* x, int64_t M, int64_t K, const float* weight,
+                          const float* bias, float eps, float* y);
+
 /* Threads used by the loops above; <=0 restores the default. */
 void orc_set_threads(int n);
 int orc_threads(void);

@@ -67,6 +67,19 @@ void sdref_layernorm(const float* x, int64_t M, int64_t K, float eps, float* y) 
   std::memcpy(y, o.data, o.nbytes);
 }
 
+// blk::layernorm with its affine parameters (weight, bias: fp32 [K]), as block_vanilla_fwd and
+// fusion_cross_ffn call it in front of the cross-attention projections
+// (src/model/ovi_dit.cpp:241, :264).
+void sdref_layernorm_affine(const float* x, int64_t M, int64_t K, const float* w, const float* b,
+                            float eps, float* y) {
+  sd::Tensor t = view(x, {M, K}, sd::DType::F32, (size_t)M * K * 4);
+  sd::Tensor wt = view(w, {K}, sd::DType::F32, (size_t)K * 4);
+  sd::Tensor bt = view(b, {K}, sd::DType::F32, (size_t)K * 4);
+  sd::Tensor o;
+  sd::blk::layernorm(t, o, &wt, &bt, eps);
+  std::memcpy(y, o.data, o.nbytes);
+}
+
 void sdref_to_bf16(const float* src, uint16_t* dst, int64_t n) {
   sd::Tensor s = view(src, {n}, sd::DType::F32, (size_t)n * 4);
   sd::Tensor o;

@@ -173,6 +173,14 @@ __global__ void __launch_bounds__(kThreads) act_quant_generic(const float* __res
 __device__ __forceinline__ float ln_value(float x, float mu, float inv) {
   return __fadd_rn(__fmul_rn(__fsub_rn(x, mu), inv), 0.0f);
 }
+// Modulated form (mod_rows after a layernorm without parameters): fma(ln, 1 + scale, shift).
+// Affine form (blk::layernorm with weight and bias, src/model/blocks.cpp:39-40): the
+// reference's build fuses (x - mu) * inv * w + b into fma((x - mu) * inv, w, b).
+__device__ __forceinline__ float mod_value(float x, float mu, float inv, float scale, float shift,
+                                           int affine) {
+  if (affine) return fmaf(__fmul_rn(__fsub_rn(x, mu), inv), scale, shift);
+  return fmaf(ln_value(x, mu, inv), __fadd_rn(1.0f, scale), shift);
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -279,7 +287,8 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
                                                               int8_t* __restrict__ aq,
                                                               float* __restrict__ a_scale,
                                                               float* __restrict__ h_out,
-                                                              const float2* __restrict__ stats) {
+                                                              const float2* __restrict__ stats,
+                                                              int affine) {
   allow_dependent_launch();
   __shared__ float red[kThreads / 32];
   const int k4 = (int)(K >> 2);
@@ -321,10 +330,10 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
       if (idx < k4) {
         const float4 sc = __ldg(reinterpret_cast<const float4*>(scale) + idx);
         const float4 sh = __ldg(reinterpret_cast<const float4*>(shift) + idx);
-        v[i].x = fmaf(ln_value(v[i].x, mu, inv), __fadd_rn(1.0f, sc.x), sh.x);
-        v[i].y = fmaf(ln_value(v[i].y, mu, inv), __fadd_rn(1.0f, sc.y), sh.y);
-        v[i].z = fmaf(ln_value(v[i].z, mu, inv), __fadd_rn(1.0f, sc.z), sh.z);
-        v[i].w = fmaf(ln_value(v[i].w, mu, inv), __fadd_rn(1.0f, sc.w), sh.w);
+        v[i].x = mod_value(v[i].x, mu, inv, sc.x, sh.x, affine);
+        v[i].y = mod_value(v[i].y, mu, inv, sc.y, sh.y, affine);
+        v[i].z = mod_value(v[i].z, mu, inv, sc.z, sh.z, affine);
+        v[i].w = mod_value(v[i].w, mu, inv, sc.w, sh.w, affine);
         mx = fold_abs(fold_abs(fold_abs(fold_abs(mx, v[i].x), v[i].y), v[i].z), v[i].w);
         if (h_out) reinterpret_cast<float4*>(h_out + row * K)[idx] = v[i];
       }
@@ -574,7 +583,8 @@ cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, f
 
 cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const float* shift,
                                 const float* scale, float eps, int8_t* aq, float* a_scale,
-                                float* h_out, float2* stats, int sm_count, cudaStream_t s) {
+                                float* h_out, float2* stats, int affine, int sm_count,
+                                cudaStream_t s) {
   if (M <= 0 || K <= 0) return cudaSuccess;
   const int64_t per_thread = (K / 4 + kThreads - 1) / kThreads;
   const bool ok = (K % 4 == 0) && per_thread <= 16 && ((reinterpret_cast<uintptr_t>(X) & 15) == 0) &&
@@ -595,11 +605,11 @@ cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const floa
   int64_t blocks = M < (int64_t)sm_count * 8 ? M : (int64_t)sm_count * 8;
   count_launch();
   if (per_thread <= 3)
-    ln_mod_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats);
+    ln_mod_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats, affine);
   else if (per_thread <= 8)
-    ln_mod_quant_regs<8><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats);
+    ln_mod_quant_regs<8><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats, affine);
   else
-    ln_mod_quant_regs<16><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats);
+    ln_mod_quant_regs<16><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats, affine);
   return cudaGetLastError();
 }
 

@@ -474,7 +474,8 @@ int sdq_layernorm_mod_quantize(const float* X_dev, int64_t M, int64_t K, const f
   float2* stats;
   if (int rc = ln_stats_for((cudaStream_t)stream, M, flags, &stats)) return rc;
   cudaError_t e = launch_ln_mod_quant(X_dev, M, K, shift_dev, scale_dev, eps, aq_dev, a_scale_dev,
-                                      h_out_dev, stats, g_ctx->sm_count, (cudaStream_t)stream);
+                                      h_out_dev, stats, (flags & SDQ_LN_AFFINE) ? 1 : 0,
+                                      g_ctx->sm_count, (cudaStream_t)stream);
   if (e == cudaErrorInvalidValue)
     return fail(SDQ_ERR_INVALID, "sdq_layernorm_mod_quantize: needs K % 4 == 0, K <= 16384 and 16-byte aligned pointers");
   SDQ_CUDA(e);
@@ -750,7 +751,7 @@ int sdq_ffn_block(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, cons
   float2* stats;
   if (int rc = ln_stats_for(s, M, flags, &stats)) return rc;
   cudaError_t e = launch_ln_mod_quant(x_dev, M, D, shift_dev, scale_dev, eps, ws->aq, ws->a_scale,
-                                      nullptr, stats, g_ctx->sm_count, s);
+                                      nullptr, stats, 0, g_ctx->sm_count, s);
   if (e == cudaErrorInvalidValue)
     return fail(SDQ_ERR_INVALID, "sdq_ffn_block: needs a width with K % 4 == 0, K <= 16384 and 16-byte aligned pointers");
   SDQ_CUDA(e);

@@ -28,10 +28,12 @@ cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, f
 // With `stats` (scratch, M float2) a first kernel computes each row's mean and 1/sqrt(var+eps)
 // with the reference's left-to-right sums and the result is bit-identical to the CPU's; with
 // stats null the sums are block-wide trees (one kernel, one pass, equal to rounding error).
+// affine != 0: `scale` / `shift` are the layernorm's own weight and bias, h = ln * w + b.
 // cudaErrorInvalidValue when K % 4 != 0, K > 16384 or a pointer is not 16-byte aligned.
 cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const float* shift,
                                 const float* scale, float eps, int8_t* aq, float* a_scale,
-                                float* h_out, float2* stats, int sm_count, cudaStream_t s);
+                                float* h_out, float2* stats, int affine, int sm_count,
+                                cudaStream_t s);
 // src_dtype SDQ_F32/BF16/F16, mode SDQ_MODE_*; all device pointers.
 cudaError_t launch_quantize_rows(const void* src, int src_dtype, int64_t rows, int64_t last,
                                  int mode, int8_t* q, float* scale, int sm_count, cudaStream_t s);

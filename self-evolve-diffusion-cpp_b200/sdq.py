@@ -12,7 +12,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 # flags / codes of include/sdq.h
-A_HOST, OUT_HOST, GELU_TANH, FORCE_SIMT, SYNC, LN_TREE_SUMS = 0x1, 0x2, 0x4, 0x8, 0x10, 0x20
+A_HOST, OUT_HOST, GELU_TANH, FORCE_SIMT, SYNC, LN_TREE_SUMS, LN_AFFINE = 0x1, 0x2, 0x4, 0x8, 0x10, 0x20, 0x40
 F32, BF16, F16 = 0, 1, 2
 MODE_PACKER, MODE_ROWWISE = 0, 1
 SRC_HOST, DST_HOST = 0x1, 0x2
@@ -309,7 +309,8 @@ class Sdq:
         self.sync()
         return dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,))
 
-    def layernorm_mod_quantize(self, X, shift, scale, eps=1e-6, want_h=False, tree_sums=False):
+    def layernorm_mod_quantize(self, X, shift, scale, eps=1e-6, want_h=False, tree_sums=False,
+                               affine=False):
         """numpy [M,K] -> (aq, a_scale[, h]) through the fused LayerNorm+modulation+quantize kernel."""
         X = np.ascontiguousarray(X, np.float32)
         M, K = X.shape
@@ -319,7 +320,8 @@ class Sdq:
         dh = self.alloc(M * K * 4) if want_h else None
         self._ck(self.lib.sdq_layernorm_mod_quantize(dX.ptr, M, K, dsh.ptr, dsc.ptr, eps, dq.ptr, ds.ptr,
                                                      dh.ptr if dh else None,
-                                                     LN_TREE_SUMS if tree_sums else 0, None))
+                                                     (LN_TREE_SUMS if tree_sums else 0) |
+                                                     (LN_AFFINE if affine else 0), None))
         self.sync()
         out = (dq.to_numpy(np.int8, (M, K)), ds.to_numpy(np.float32, (M,)))
         return out + (dh.to_numpy(np.float32, (M, K)),) if want_h else out

@@ -138,6 +138,19 @@ def test_fused_layernorm_modulation_quantize_is_exact(sdq, oracle, M, K):
     assert bits_equal(aq, aq_c)
 
 
+def test_fused_affine_layernorm_quantize_is_exact(sdq, oracle):
+    """The layernorm that has a weight and a bias (cross-attention input), SDQ_LN_AFFINE."""
+    rng = np.random.default_rng(40)
+    for (M, K) in [(512, 3072), (77, 260)]:
+        x = (rng.standard_normal((M, K)) * 2 + 0.3).astype(np.float32)
+        w = (1 + rng.standard_normal(K) * 0.2).astype(np.float32)
+        b = (rng.standard_normal(K) * 0.3).astype(np.float32)
+        aq, a_s, h = sdq.layernorm_mod_quantize(x, b, w, 1e-6, want_h=True, affine=True)
+        h_c = oracle.layernorm_affine(x, w, b, 1e-6)
+        aq_c, as_c = oracle.act_quant_rows(h_c)
+        assert bits_equal(h, h_c) and bits_equal(a_s, as_c) and bits_equal(aq, aq_c)
+
+
 @pytest.mark.parametrize("M,K", [(300, 3072), (64, 14336), (1000, 512)])
 def test_fused_layernorm_modulation_quantize_tree_sums(sdq, pkg, oracle, M, K):
     """The one-pass variant (SDQ_LN_TREE_SUMS).  The row sums are tree sums while the CPU adds K

@@ -139,6 +139,15 @@ def test_caller_side_matches_reference_fixture(oracle, golden_dir):
     assert max_rel_err(got, z["ffn_out"]) < 1e-5
 
 
+def test_affine_layernorm_restates_reference(oracle, reference):
+    """blk::layernorm with weight and bias (in front of the cross-attention projections)."""
+    rng = np.random.default_rng(16)
+    x = (rng.standard_normal((48, 3072)) * 2 + 0.4).astype(np.float32)
+    w = (1 + rng.standard_normal(3072) * 0.2).astype(np.float32)
+    b = (rng.standard_normal(3072) * 0.3).astype(np.float32)
+    assert bits_equal(oracle.layernorm_affine(x, w, b, 1e-6), reference.layernorm_affine(x, w, b, 1e-6))
+
+
 def test_caller_side_live_reference(oracle, reference):
     rng = np.random.default_rng(31)
     x = rng.standard_normal((33, 130)).astype(np.float32)
