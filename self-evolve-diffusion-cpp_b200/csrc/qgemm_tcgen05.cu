@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const int num_k_blocks = (int)((g.K + BLOCK_K - 1) / BLOCK_K);
   const int num_tiles = num_m_blocks * num_n_blocks;
   // Split-K: a work item is (tile, K slice).  Slices of one tile add their int32 partial
-  // sums into g.splitk_acc with atomics (integer addition: exact in any order); a second
+  // sums into g.splitk_acc with bulk tensor reductions (integer addition: exact in any order); a second
   // kernel turns the sums into fp32.  k_splits == 1 is the ordinary case.
   const int k_splits = g.k_splits > 1 ? g.k_splits : 1;
   const int kb_per_split = (num_k_blocks + k_splits - 1) / k_splits;
@@ -418,7 +418,7 @@ Plan plan_small(const GemmArgs& g, int sm_count, bool allow_split) {
       const double t_fetch = stage_bytes / 120e3;               // us at ~120 GB/s per SM
       const double t_mma = 4.0 * (bn / 256.0) * 128.0 / 1.9e3;  // us: 128 cycles per N=256 MMA
       double t = waves * (kbs * (t_fetch > t_mma ? t_fetch : t_mma) + 1.5 + 0.25 * bn / 32.0);
-      if (splits > 1) t += 5.0 + (double)g.M * g.N * 4.0 * 3.0 / 3e6;  // memset + atomics + finalize
+      if (splits > 1) t += 5.0 + (double)g.M * g.N * 4.0 * 3.0 / 3e6;  // memset + reductions + finalize
       if (t < best_t) { best_t = t; best = {bn, splits}; }
     }
   }

@@ -71,8 +71,8 @@ def test_intermediates_match_oracle(sdq, oracle, M, K, N):
 
 
 def test_split_k_host_path_matches_oracle(sdq, oracle):
-    """The few-rows / long-K shapes take the split-K plan (int32 partial sums added with
-    atomics, then a finalize pass); bias and the host-pointer path included."""
+    """The few-rows / long-K shapes take the split-K plan (int32 partial sums added by bulk
+    tensor reductions, then a finalize pass); bias and the host-pointer path included."""
     rng = np.random.default_rng(77)
     for (M, K, N) in [(192, 14336, 3072), (64, 14336, 512)]:
         A = rng.standard_normal((M, K)).astype(np.float32)
