@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=M_720P, help="token rows per GPU")
-    ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch", "libcompare"])
+    ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch", "libcompare", "block"])
     ap.add_argument("--blocks", type=int, default=30, help="branch workload: number of DiT blocks")
     ap.add_argument("--pack-file-blocks", type=int, default=0,
                     help="branch workload: also write this many blocks as a .sdcpp file and time the load")
@@ -746,8 +746,146 @@ def run_branch(args):
     return 0
 
 
+def run_block(args):
+    """One DiT block's int8 linears at M = --rows tokens (K/V of the text cross-attention at 512
+    rows) in three call patterns: (a) eight bare sdq_qgemm calls; (b) the reference's call pattern
+    with every pass it runs around the linears -- layernorm, modulation, bias adds, GELU, gated and
+    plain residual adds -- as separate elementwise passes (torch) around bare sdq_qgemm calls;
+    (c) the same work through the fused entry points (layernorm + modulation + quantize once for
+    q/k/v, bias / GELU / residual in the GEMM epilogues, sdq_ffn_block).  Attention itself is not
+    on this path: the projections' inputs stand in for its outputs.  One GPU; one JSON line."""
+    import ctypes as C
+
+    import torch
+
+    import __graft_entry__ as ge
+
+    torch.cuda.set_device(0)
+    pkg = ge.load_package()
+    s = pkg.Sdq(0)
+    S, lib = pkg.sdq, s.lib
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    M, D, F, T = args.rows, D_MODEL, D_FFN, 512
+
+    def p(t):
+        return C.c_void_p(t.data_ptr())
+
+    def weight(n, k):
+        q = torch.randint(-127, 128, (n, k), device=dev, dtype=torch.int8, generator=g)
+        sc = torch.rand(n, device=dev, generator=g) * 2e-4 + 1e-5
+        return (q, sc, s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), n, k),
+                torch.randn(n, device=dev, generator=g) * 0.02)
+    W = {name: weight(N, K) for (name, K, N, _) in BLOCK_LINEARS}
+    x = torch.randn(M, D, device=dev, generator=g)
+    att = torch.randn(M, D, device=dev, generator=g)        # stands in for the attention outputs
+    ctx = torch.randn(T, D, device=dev, generator=g)
+    e = torch.randn(6, D, device=dev, generator=g) * 0.1     # modulation table of the block
+    ln3_w = 1 + torch.randn(D, device=dev, generator=g) * 0.1
+    ln3_b = torch.randn(D, device=dev, generator=g) * 0.1
+    qkv = torch.empty(M, 3 * D, device=dev)
+    y = torch.empty(M, D, device=dev)
+    kv = torch.empty(T, D, device=dev)
+    hid = torch.empty(M, F, device=dev)
+    aq = torch.empty(M, D, device=dev, dtype=torch.int8)
+    a_s = torch.empty(M, device=dev)
+    aqt = torch.empty(T, D, device=dev, dtype=torch.int8)
+    a_st = torch.empty(T, device=dev)
+
+    def lin(name, a, m, out, bias=False, flags=0):
+        s._ck(lib.sdq_qgemm(W[name][2], p(a), m, p(out), p(W[name][3]) if bias else None, flags, sp))
+
+    def pre(name, q8, sc, m, out, flags=0):
+        s._ck(lib.sdq_qgemm_prequantized(W[name][2], p(q8), p(sc), m, p(out), p(W[name][3]), None, flags, sp))
+
+    def bare():
+        for name, a, m, out in (("self_attn.qkv", x, M, qkv), ("self_attn.o", att, M, y),
+                                ("cross_attn.q", x, M, y), ("cross_attn.k", ctx, T, kv),
+                                ("cross_attn.v", ctx, T, kv), ("cross_attn.o", att, M, y),
+                                ("ffn.0", x, M, hid), ("ffn.2", hid, M, y)):
+            lin(name, a, m, out)
+
+    def lin_bias(name, a, m, out):
+        lin(name, a, m, out)
+        out.add_(W[name][3])                              # mlin's separate bias pass
+
+    def unfused(xx):
+        ln = torch.nn.functional.layer_norm
+        h = ln(xx, (D,)) * (1 + e[1]) + e[0]
+        lin_bias("self_attn.qkv", h, M, qkv)
+        lin_bias("self_attn.o", att, M, y)
+        xx.addcmul_(y, e[2])
+        h = ln(xx, (D,), ln3_w, ln3_b)
+        lin_bias("cross_attn.q", h, M, y)
+        lin_bias("cross_attn.k", ctx, T, kv)
+        lin_bias("cross_attn.v", ctx, T, kv)
+        lin_bias("cross_attn.o", att, M, y)
+        xx.add_(y)
+        h = ln(xx, (D,)) * (1 + e[4]) + e[3]
+        lin_bias("ffn.0", h, M, hid)
+        hid.copy_(torch.nn.functional.gelu(hid, approximate="tanh"))
+        lin_bias("ffn.2", hid, M, y)
+        xx.addcmul_(y, e[5])
+
+    def fused(xx):
+        eps = C.c_float(1e-6)
+        s._ck(lib.sdq_layernorm_mod_quantize(p(xx), M, D, p(e[0]), p(e[1]), eps, p(aq), p(a_s), None, 0, sp))
+        pre("self_attn.qkv", aq, a_s, M, qkv)
+        s._ck(lib.sdq_qgemm_residual(W["self_attn.o"][2], p(att), M, p(xx), p(e[2]), p(xx), p(W["self_attn.o"][3]), 0, sp))
+        s._ck(lib.sdq_layernorm_mod_quantize(p(xx), M, D, p(ln3_b), p(ln3_w), eps, p(aq), p(a_s), None, S.LN_AFFINE, sp))
+        pre("cross_attn.q", aq, a_s, M, y)
+        s._ck(lib.sdq_quantize_activations(p(ctx), T, D, p(aqt), p(a_st), sp))
+        pre("cross_attn.k", aqt, a_st, T, kv)
+        pre("cross_attn.v", aqt, a_st, T, kv)
+        s._ck(lib.sdq_qgemm_residual(W["cross_attn.o"][2], p(att), M, p(xx), None, p(xx), p(W["cross_attn.o"][3]), 0, sp))
+        s._ck(lib.sdq_ffn_block(W["ffn.0"][2], p(W["ffn.0"][3]), W["ffn.2"][2], p(W["ffn.2"][3]), p(xx), M,
+                                p(e[3]), p(e[4]), p(e[5]), eps, 0, sp))
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        n0 = s.launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        s.sync(sp)
+        return e0.elapsed_time(e1) / args.steps, (s.launches() - n0) // args.steps
+    # the two in-place patterns agree within the GELU bound on the same input
+    xa, xb = x.clone(), x.clone()
+    unfused(xa)
+    fused(xb)
+    torch.cuda.synchronize()
+    agree = float((xa - xb).abs().max() / xa.abs().max())
+    ops = sum(2.0 * (M if rows is None else rows) * N * K for (_, K, N, rows) in BLOCK_LINEARS)
+    xw = x.clone()
+    t_bare, l_bare = timed(bare)
+    t_unf, l_unf = timed(lambda: unfused(xw))
+    xw.copy_(x)
+    t_fus, l_fus = timed(lambda: fused(xw))
+    print(json.dumps({"metric": "int8_qgemm_throughput", "value": ops / (t_fus * 1e-3) / 1e12, "unit": "TOPS",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t_fus,
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8",
+                      "data": "synthetic",
+                      "config": {"workload": "dit_block_linears_fused_call_pattern", "rows": M,
+                                 "l2": "inputs larger than L2 (x %d MB)" % (M * D * 4 // 1000000)},
+                      "gpu_launches": l_fus * args.steps,
+                      "patterns_ms": {"bare_linears": t_bare, "unfused_with_elementwise_passes": t_unf,
+                                      "fused_entry_points": t_fus},
+                      "launches_per_block": {"bare_linears": l_bare, "unfused_own_kernels": l_unf, "fused": l_fus},
+                      "fused_vs_unfused_max_rel_diff": agree}))
+    return 0
+
+
 if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         sys.exit(run_reference(a))
-    sys.exit({"sweep": run_sweep, "branch": run_branch, "libcompare": run_libcompare}.get(a.workload, run_b200)(a))
+    sys.exit({"sweep": run_sweep, "branch": run_branch, "libcompare": run_libcompare,
+              "block": run_block}.get(a.workload, run_b200)(a))

@@ -176,10 +176,16 @@ __device__ __forceinline__ float ln_value(float x, float mu, float inv) {
 // Modulated form (mod_rows after a layernorm without parameters): fma(ln, 1 + scale, shift).
 // Affine form (blk::layernorm with weight and bias, src/model/blocks.cpp:39-40): the
 // reference's build fuses (x - mu) * inv * w + b into fma((x - mu) * inv, w, b).
-__device__ __forceinline__ float mod_value(float x, float mu, float inv, float scale, float shift,
+// `mult` is the column's multiplier from column_multiplier(): 1 + scale, or the weight.
+__device__ __forceinline__ float mod_value(float x, float mu, float inv, float mult, float shift,
                                            int affine) {
-  if (affine) return fmaf(__fmul_rn(__fsub_rn(x, mu), inv), scale, shift);
-  return fmaf(ln_value(x, mu, inv), __fadd_rn(1.0f, scale), shift);
+  if (affine) return fmaf(__fmul_rn(__fsub_rn(x, mu), inv), mult, shift);
+  return fmaf(ln_value(x, mu, inv), mult, shift);
+}
+__device__ __forceinline__ float4 column_multiplier(float4 scale, int affine) {
+  if (affine) return scale;
+  return make_float4(__fadd_rn(1.0f, scale.x), __fadd_rn(1.0f, scale.y), __fadd_rn(1.0f, scale.z),
+                     __fadd_rn(1.0f, scale.w));
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -205,7 +211,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // row so that both the row-major fill and the lane-per-row reads are conflict-free).
 // stats[row] = (mean, 1/sqrt(var + eps)).  Two passes over x (HBM-bound); the chains themselves
 // cost ~4 cycles per element per row and overlap the copies.
-constexpr int kStatStages = 4;
+constexpr int kStatStages = 6;
 constexpr int kStatWarps = 2;
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -293,6 +299,20 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
   __shared__ float red[kThreads / 32];
   const int k4 = (int)(K >> 2);
   const float inv_n = 1.0f / (float)K;
+  // A thread meets the same columns in every row: for short rows their multipliers
+  // (1 + scale, or the layernorm's weight) and addends stay in registers across the rows.
+  constexpr bool kHoist = VPT <= 3;
+  float4 mul_c[kHoist ? VPT : 1], add_c[kHoist ? VPT : 1];
+  if (kHoist) {
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < k4) {
+        mul_c[i] = column_multiplier(__ldg(reinterpret_cast<const float4*>(scale) + idx), affine);
+        add_c[i] = __ldg(reinterpret_cast<const float4*>(shift) + idx);
+      }
+    }
+  }
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
     const float4* src = reinterpret_cast<const float4*>(X + row * K);
     float4 v[VPT];
@@ -328,8 +348,9 @@ __global__ void __launch_bounds__(kThreads) ln_mod_quant_regs(const float* __res
     for (int i = 0; i < VPT; i++) {
       const int idx = threadIdx.x + i * kThreads;
       if (idx < k4) {
-        const float4 sc = __ldg(reinterpret_cast<const float4*>(scale) + idx);
-        const float4 sh = __ldg(reinterpret_cast<const float4*>(shift) + idx);
+        const float4 sc = kHoist ? mul_c[i]
+                                 : column_multiplier(__ldg(reinterpret_cast<const float4*>(scale) + idx), affine);
+        const float4 sh = kHoist ? add_c[i] : __ldg(reinterpret_cast<const float4*>(shift) + idx);
         v[i].x = mod_value(v[i].x, mu, inv, sc.x, sh.x, affine);
         v[i].y = mod_value(v[i].y, mu, inv, sc.y, sh.y, affine);
         v[i].z = mod_value(v[i].z, mu, inv, sc.z, sh.z, affine);
@@ -602,8 +623,8 @@ cudaError_t launch_ln_mod_quant(const float* X, int64_t M, int64_t K, const floa
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
-  int64_t blocks = M < (int64_t)sm_count * 8 ? M : (int64_t)sm_count * 8;
   count_launch();
+  int64_t blocks = M < (int64_t)sm_count * 8 ? M : (int64_t)sm_count * 8;
   if (per_thread <= 3)
     ln_mod_quant_regs<3><<<(unsigned)blocks, kThreads, 0, s>>>(X, M, K, shift, scale, eps, aq, a_scale, h_out, stats, affine);
   else if (per_thread <= 8)

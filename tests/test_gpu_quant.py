@@ -119,7 +119,8 @@ def test_dequant_rows(sdq, oracle):
     assert np.all(np.abs(sdq.dequant_rows(qq, ss) - W) < ss[:, None])
 
 
-@pytest.mark.parametrize("M,K", [(300, 3072), (64, 14336), (1000, 512), (33, 100), (1, 4), (2049, 3072)])
+@pytest.mark.parametrize("M,K", [(300, 3072), (64, 14336), (1000, 512), (33, 100), (1, 4), (2049, 3072),
+                                 (2500, 3072), (2400, 516), (3000, 1024)])   # many rows: one warp per row
 def test_fused_layernorm_modulation_quantize_is_exact(sdq, oracle, M, K):
     """LayerNorm + modulation + activation quantization with the reference's left-to-right row
     sums (the default): h, the int8 bytes and the scales are bit-identical to the CPU chain."""
@@ -141,7 +142,7 @@ def test_fused_layernorm_modulation_quantize_is_exact(sdq, oracle, M, K):
 def test_fused_affine_layernorm_quantize_is_exact(sdq, oracle):
     """The layernorm that has a weight and a bias (cross-attention input), SDQ_LN_AFFINE."""
     rng = np.random.default_rng(40)
-    for (M, K) in [(512, 3072), (77, 260)]:
+    for (M, K) in [(512, 3072), (77, 260), (2600, 3072)]:
         x = (rng.standard_normal((M, K)) * 2 + 0.3).astype(np.float32)
         w = (1 + rng.standard_normal(K) * 0.2).astype(np.float32)
         b = (rng.standard_normal(K) * 0.3).astype(np.float32)
