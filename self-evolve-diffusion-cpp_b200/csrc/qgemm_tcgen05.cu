@@ -231,15 +231,17 @@ __global__ void __launch_bounds__(kNumThreads, 1)
               case 2: chunk_values<false, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
               default: chunk_values<true, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
             }
-            if (g.residual) {
-              float4 x[8];
-              chunk_load_residual(g.residual + row * g.N, row_ok, nc, g.N, x);
-              chunk_add_residual(o, x, g.gate, nc, g.N);
-            }
+            float4 x[8];
+            if (g.residual) chunk_load_residual(g.residual, row0, g.M, g.N, nc, lane, x);
             // The values go through a swizzled 32x32 fp32 box in shared memory; one bulk
             // tensor store then writes full 128-byte lines and clips rows >= M, columns >= N.
             if (lane == 0) bulk_wait_read<0>();  // the previous store has finished reading the box
             __syncwarp();
+            if (g.residual) {  // x passes through the box so that each thread gets its own row
+              chunk_stage_residual(box, lane, x);
+              __syncwarp();
+              chunk_apply_residual(box, lane, o, g.gate, nc, g.N);
+            }
 #pragma unroll
             for (int j = 0; j < 32; j += 4)  // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
               st_shared_v4(box + (uint32_t)(lane * 128 + (((j >> 2) ^ (lane & 7)) << 4)),

@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           tmem_ld_32x32(tmem_base + abuf * kBlockN2 + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
           float4 x[8];
           if (kResidual)  // in flight while the accumulators arrive from tensor memory
-            chunk_load_residual(g.residual + row * g.N, row < g.M, nc, g.N, x);
+            chunk_load_residual(g.residual, row0, g.M, g.N, nc, lane, x);
           tmem_ld_wait();
           float o[32];
           switch (mode) {
@@ -256,12 +256,16 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             case 2: chunk_values<false, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
             default: chunk_values<true, true>(r, a_s, g.b_scale, g.bias, nc, g.N, o); break;
           }
-          if (kResidual) chunk_add_residual(o, x, g.gate, nc, g.N);
           const uint32_t box = box0 + box_sel * 4096;
           if (kBoxes > 1) box_sel ^= 1u;
           // the store that last read this box must have finished reading it
           if (lane == 0) bulk_wait_read<kBoxes - 1>();
           __syncwarp();
+          if (kResidual) {  // x passes through the box so that each thread gets its own row
+            chunk_stage_residual(box, lane, x);
+            __syncwarp();
+            chunk_apply_residual(box, lane, o, g.gate, nc, g.N);
+          }
 #pragma unroll
           for (int j = 0; j < 32; j += 4)
             st_shared_v4(box + (uint32_t)(lane * 128 + (((j >> 2) ^ (lane & 7)) << 4)),

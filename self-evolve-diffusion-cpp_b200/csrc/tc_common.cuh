@@ -274,25 +274,42 @@ __device__ __forceinline__ void chunk_values(const uint32_t (&r)[32], float a_s,
   }
 }
 
-// The 32 values of x (the residual) that belong to one thread's chunk, loaded with ordinary
+// Residual epilogue, three steps around the staging box of a 32x32 chunk.
+// (1) The warp fetches the chunk of x (the residual) with coalesced loads: one instruction
+// covers four whole 128-byte rows, lane l taking 16-byte piece l%8 of row 4i + l/8.  Ordinary
 // coherent loads: x may be the output buffer itself (the update is in place in the reference),
-// and each element is read only by the thread that later writes it.
-__device__ __forceinline__ void chunk_load_residual(const float* __restrict__ res_row, bool row_ok,
-                                                    int64_t nc, int64_t N, float4 (&x)[8]) {
+// and every element is read before the bulk store of the same chunk overwrites it.
+__device__ __forceinline__ void chunk_load_residual(const float* __restrict__ res, int64_t row0,
+                                                    int64_t M, int64_t N, int64_t nc, int lane,
+                                                    float4 (&x)[8]) {
+  const int64_t col = nc + (lane & 7) * 4;
 #pragma unroll
-  for (int j = 0; j < 8; j++) {
-    x[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row_ok && nc + 4 * j < N) x[j] = *reinterpret_cast<const float4*>(res_row + nc + 4 * j);
+  for (int i = 0; i < 8; i++) {
+    const int64_t row = row0 + i * 4 + (lane >> 3);
+    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < M && col < N) x[i] = *reinterpret_cast<const float4*>(res + row * N + col);
   }
 }
-
-// o = x + o * gate[j] (one fused multiply-add) or x + o when there is no gate.
-__device__ __forceinline__ void chunk_add_residual(float (&o)[32], const float4 (&x)[8],
-                                                   const float* __restrict__ gate, int64_t nc,
-                                                   int64_t N) {
+// (2) The pieces go into the (free) staging box at the swizzled positions the output will take.
+__device__ __forceinline__ void chunk_stage_residual(uint32_t box, int lane, const float4 (&x)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int r = i * 4 + (lane >> 3);
+    st_shared_v4(box + (uint32_t)(r * 128 + (((lane & 7) ^ (r & 7)) << 4)), x[i]);
+  }
+}
+// (3) Each thread reads its own row back (the same addresses its outputs are then written to)
+// and applies o = x + o * gate[j] (one fused multiply-add), or x + o when there is no gate.
+__device__ __forceinline__ void chunk_apply_residual(uint32_t box, int lane, float (&o)[32],
+                                                     const float* __restrict__ gate, int64_t nc,
+                                                     int64_t N) {
 #pragma unroll
   for (int j = 0; j < 8; j++) {
-    const float xs[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
+    float4 xv;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(xv.x), "=f"(xv.y), "=f"(xv.z), "=f"(xv.w)
+                 : "r"(box + (uint32_t)(lane * 128 + ((j ^ (lane & 7)) << 4))));
+    const float xs[4] = {xv.x, xv.y, xv.z, xv.w};
     if (gate) {
       float4 gg = make_float4(0.f, 0.f, 0.f, 0.f);
       if (nc + 4 * j < N) gg = __ldg(reinterpret_cast<const float4*>(gate + nc + 4 * j));
