@@ -688,7 +688,7 @@ int sdq_ffn_pair(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, const
   static const int64_t chunk_rows = [] {
     const char* v = std::getenv("SDQ_FFN_CHUNK_ROWS");
     const int64_t n = v ? std::atoll(v) : 0;
-    return n >= 128 ? n : 4096;
+    return n >= 128 ? n : 2048;
   }();
   const int64_t chunk = std::min<int64_t>(M, chunk_rows);
   for (int i = 0; i < 2; i++) {
