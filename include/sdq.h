@@ -238,6 +238,24 @@ SDQ_API int sdq_ffn_block(sdq_weight_t w1, const float* bias1_dev, sdq_weight_t 
                           const float* scale_dev, const float* gate_dev, float eps, uint32_t flags,
                           void* stream);
 
+/* ---- the fp32 linears beside the int8 ones ----
+ * out[M,N] = A[M,K] * W[K,N] + bias  -- replaces sd::matmul (src/core/tensor.h:46,
+ * src/core/gemm.cpp:115-160) as blk::linear calls it (src/model/blocks.cpp:13-16) for the
+ * tensors a pack keeps in fp32 (numel < 65536 or --dtype-preserve) and for unpacked
+ * checkpoints.  W is the reference's Linear layout, fp32 [K = in, N = out] row-major;
+ * sdq_fweight_upload (SDQ_A_HOST: `w` is host memory, else device) transposes it once into
+ * [N,K] and splits it into two tf32 planes.  sdq_fmatmul issues three tf32 tensor-core products
+ * per fp32 product (hi*hi + hi*lo + lo*hi into an fp32 accumulator), which gives fp32-level
+ * accuracy; the reference's own sums depend on its BLAS / SIMD order, so this path is held to
+ * the reference's matmul tolerance (max-abs error <= 1e-3 of the largest output,
+ * tests/test_core.cpp:82-84), not to bit equality.  The handle is released with
+ * sdq_weight_release; the int8 entry points reject it and vice versa.  A / out are device
+ * memory unless SDQ_A_HOST / SDQ_OUT_HOST; bias is device memory or NULL. */
+SDQ_API int sdq_fweight_upload(const float* w, int64_t K, int64_t N, uint32_t flags,
+                               sdq_weight_t* out);
+SDQ_API int sdq_fmatmul(sdq_weight_t w, const float* A, int64_t M, float* out,
+                        const float* bias_dev, uint32_t flags, void* stream);
+
 /* The same computation as sdq_qgemm for callers that cannot allocate device memory
  * while they run (a host that has given all HBM to its own pool, a plugin inside
  * another allocator, a section where cudaMalloc's implicit device-wide

@@ -46,7 +46,7 @@ class Oracle:
                      "orc_bias_add", "orc_gelu_tanh", "orc_quantize_rowwise",
                      "orc_quant_rows_packer", "orc_dequant_rows", "orc_f32_to_bf16",
                      "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads", "orc_layernorm_mod",
-                     "orc_residual_add", "orc_layernorm_affine"):
+                     "orc_residual_add", "orc_layernorm_affine", "orc_matmul_f32"):
             getattr(L, name).restype = None
 
     def threads(self):
@@ -142,6 +142,16 @@ class Oracle:
         y = np.empty((M, K), np.float32)
         self.lib.orc_layernorm_affine(_ptr(x), i64(M), i64(K), _ptr(weight), _ptr(bias), C.c_float(eps), _ptr(y))
         return y
+
+    def matmul_f32(self, a, w, bias=None):
+        a, w = _c(a, np.float32), _c(w, np.float32)
+        bias = None if bias is None else _c(bias, np.float32)
+        M, K = a.shape
+        N = w.shape[1]
+        out = np.empty((M, N), np.float32)
+        self.lib.orc_matmul_f32(_ptr(a), i64(M), i64(K), _ptr(w), i64(N),
+                                None if bias is None else _ptr(bias), _ptr(out))
+        return out
 
     def f32_to_bf16(self, x):
         x = _c(x, np.float32)
@@ -284,6 +294,18 @@ class Reference:
         self.lib.sdref_layernorm_affine.restype = None
         self.lib.sdref_layernorm_affine(_ptr(x), i64(M), i64(K), _ptr(w), _ptr(b), C.c_float(eps), _ptr(y))
         return y
+
+    def matmul(self, a, w, bias=None):
+        """sd::matmul: a[M,K] @ w[K,N] + bias, fp32."""
+        a, w = _c(a, np.float32), _c(w, np.float32)
+        bias = None if bias is None else _c(bias, np.float32)
+        M, K = a.shape
+        N = w.shape[1]
+        out = np.zeros((M, N), np.float32)
+        self.lib.sdref_matmul.restype = None
+        self.lib.sdref_matmul(_ptr(a), i64(M), i64(K), _ptr(w), i64(N),
+                              None if bias is None else _ptr(bias), _ptr(out))
+        return out
 
     def load_sdcpp_listing(self, path):
         """(count, listing) or raises RuntimeError with the loader's message."""

@@ -317,6 +317,26 @@ void orc_quant_rows_packer(const float* x, int64_t rows, int64_t last, int8_t* q
   par_rows(rows, packer_range, &j);
 }
 
+/* sd::matmul, the portable branch (src/core/gemm.cpp:100-110): out[i,j] = sum_k a[i,k]*w[k,j]
+ * added left to right in fp32, then the separate bias pass (src/core/gemm.cpp:33-40).  The
+ * reference's AVX2 / BLAS branches add in other orders, so every comparison with this function
+ * is under the reference's own matmul tolerance, never bit for bit. */
+typedef struct { const float* a; const float* w; const float* bias; float* out; int64_t N, K; } mm_t;
+static void mm_range(int64_t b, int64_t e, void* p) {
+  mm_t* j = (mm_t*)p;
+  for (int64_t i = b; i < e; i++)
+    for (int64_t c = 0; c < j->N; c++) {
+      float s = 0.0f;
+      for (int64_t k = 0; k < j->K; k++) s += j->a[i * j->K + k] * j->w[k * j->N + c];
+      j->out[i * j->N + c] = j->bias ? s + j->bias[c] : s;
+    }
+}
+void orc_matmul_f32(const float* a, int64_t M, int64_t K, const float* w, int64_t N,
+                    const float* bias_or_null, float* out) {
+  mm_t j = {a, w, bias_or_null, out, N, K};
+  par_rows(M, mm_range, &j);
+}
+
 /* src/model/ovi_dit.cpp:53-63. */
 void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last, float* w) {
   for (int64_t i = 0; i < rows; i++)

@@ -72,6 +72,12 @@ void orc_layernorm_mod(const float* x, int64_t M, int64_t K, const float* shift,
 void orc_layernorm_affine(const float* x, int64_t M, int64_t K, const float* weight,
                           const float* bias, float eps, float* y);
 
+/* sd::matmul, portable branch (src/core/gemm.cpp:100-110, 33-40): fp32 sums left to right,
+ * w is [K,N] row-major.  Tolerance-level comparisons only (the reference's SIMD / BLAS branches
+ * add in other orders). */
+void orc_matmul_f32(const float* a, int64_t M, int64_t K, const float* w, int64_t N,
+                    const float* bias_or_null, float* out);
+
 /* Threads used by the loops above; <=0 restores the default. */
 void orc_set_threads(int n);
 int orc_threads(void);

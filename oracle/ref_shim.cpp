@@ -80,6 +80,16 @@ void sdref_layernorm_affine(const float* x, int64_t M, int64_t K, const float* w
   std::memcpy(y, o.data, o.nbytes);
 }
 
+// sd::matmul (src/core/tensor.h:46, src/core/gemm.cpp:115-160): out[M,N] = a[M,K] * w[K,N] + bias.
+void sdref_matmul(const float* a, int64_t M, int64_t K, const float* w, int64_t N,
+                  const float* bias_or_null, float* out) {
+  sd::Tensor at = view(a, {M, K}, sd::DType::F32, (size_t)M * K * 4);
+  sd::Tensor wt = view(w, {K, N}, sd::DType::F32, (size_t)K * N * 4);
+  sd::Tensor o;
+  sd::matmul(at, wt, o, bias_or_null);
+  if (o.data && o.nbytes) std::memcpy(out, o.data, o.nbytes);
+}
+
 void sdref_to_bf16(const float* src, uint16_t* dst, int64_t n) {
   sd::Tensor s = view(src, {n}, sd::DType::F32, (size_t)n * 4);
   sd::Tensor o;

@@ -3,9 +3,9 @@
 // libsd_b200.so defines these symbols.  Object code built against the reference project's
 // own core header (src/core/tensor.h:13-61) links against it unchanged: the Tensor object has
 // the same members in the same order and every function has the same mangled name.  Only the
-// part of that header which lies on the quantized-linear path is provided -- the tensor
-// container, bf16 conversion, qgemm, quantize_rowwise and the host thread dispatch; the fp32
-// matmul, silu, rmsnorm and the test RNG are not on the path and are not defined here.
+// part of that header which lies on the linear path is provided -- the tensor container, bf16
+// conversion, qgemm, quantize_rowwise, the fp32 matmul and the host thread dispatch; silu,
+// rmsnorm and the test RNG are not on the path and are not defined here.
 #pragma once
 
 #include <cstddef>
@@ -73,6 +73,13 @@ void to_f32(const Tensor& bf16, Tensor& out);
 // and rescaled by a_scale[i] * bs[j].  The device copy of Bq that load_sdcpp made is found by
 // Bq.data; a weight that did not come from a pack is uploaded for the duration of the call.
 void qgemm(const Tensor& A, const Tensor& Bq, const Tensor& bs, Tensor& out);
+
+// The fp32 linear on the GPU: C[M,N] = A[M,K] * B[K,N] (+ bias[N]); C is replaced by a freshly
+// allocated tensor.  A and B are fp32 or bf16 (widened first).  B is looked up by B.data among
+// the weights already on the device and otherwise uploaded for the duration of the call.
+// Three tf32 tensor-core products per fp32 product: within the reference's matmul tolerance,
+// not bit-identical to any particular CPU summation order.
+void matmul(const Tensor& A, const Tensor& B, Tensor& C, const float* bias = nullptr);
 
 // fp32 [N,K] weights -> int8 [N,K] and one scale per row (absmax / 127; 1 for an all-zero row).
 void quantize_rowwise(const Tensor& W, Tensor& Wq, Tensor& scale);

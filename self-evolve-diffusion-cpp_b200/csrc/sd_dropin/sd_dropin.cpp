@@ -109,6 +109,42 @@ void qgemm(const Tensor& A, const Tensor& Bq, const Tensor& bs, Tensor& out) {
   if (rc != SDQ_OK) throw std::runtime_error(msg);
 }
 
+// ---- the fp32 linear (reference src/core/gemm.cpp:115-160) ----
+void matmul(const Tensor& A, const Tensor& B, Tensor& C, const float* bias) {
+  Tensor Af, Bf;
+  const Tensor* a = &A;
+  const Tensor* b = &B;
+  if (A.dtype == DType::BF16) { to_f32(A, Af); a = &Af; }
+  if (B.dtype == DType::BF16) { to_f32(B, Bf); b = &Bf; }
+  const int64_t M = a->rows(), K = a->cols(), N = b->cols();
+  C = Tensor({M, N}, DType::F32);
+  if (M == 0 || N == 0) return;
+  if (K == 0) {  // an empty sum: only the bias is left, as in the reference
+    if (bias)
+      for (int64_t i = 0; i < M; i++) std::memcpy(C.ptr<float>() + i * N, bias, (size_t)N * 4);
+    return;
+  }
+  ensure_device();
+  sdq_weight_t w = 0;
+  bool temporary = false;
+  if (b != &B || sdq_weight_lookup(B.data, &w) != SDQ_OK) {
+    if (sdq_fweight_upload(b->ptr<float>(), K, N, SDQ_A_HOST, &w) != SDQ_OK) raise_last();
+    temporary = true;
+  }
+  float* bias_dev = nullptr;
+  int rc = SDQ_OK;
+  if (bias) {
+    rc = sdq_malloc(reinterpret_cast<void**>(&bias_dev), (size_t)N * 4);
+    if (rc == SDQ_OK) rc = sdq_memcpy_h2d(bias_dev, bias, (size_t)N * 4, nullptr);
+  }
+  if (rc == SDQ_OK)
+    rc = sdq_fmatmul(w, a->ptr<float>(), M, C.ptr<float>(), bias_dev, SDQ_A_HOST | SDQ_OUT_HOST, nullptr);
+  const std::string msg = rc != SDQ_OK ? sdq_last_error() : "";
+  if (bias_dev) sdq_free(bias_dev);
+  if (temporary) sdq_weight_release(w);
+  if (rc != SDQ_OK) throw std::runtime_error(msg);
+}
+
 // reference src/core/tensor.cpp:63-78
 void quantize_rowwise(const Tensor& W, Tensor& Wq, Tensor& scale) {
   const int64_t N = W.rows(), K = W.cols();

@@ -21,7 +21,10 @@ struct Weight {
   const int8_t* q = nullptr;   // device [N,K]
   const float* scale = nullptr;  // device [N]
   int64_t N = 0, K = 0;
-  bool owned = false;          // q/scale were allocated by sdq_weight_upload
+  // an fp32 weight (sdq_fweight_upload): tf32 planes hi / lo, transposed to [N,K]; q is null
+  const float* f_hi = nullptr;
+  const float* f_lo = nullptr;
+  bool owned = false;          // q/scale (or f_hi/f_lo) were allocated by the upload
   const void* host_key = nullptr;
   bool live = false;
 };
@@ -35,6 +38,7 @@ struct Workspace {
   float* out_stage = nullptr; size_t out_stage_bytes = 0;
   int32_t* acc = nullptr; size_t acc_bytes = 0;   // split-K partial sums
   float2* ln_stats = nullptr; size_t ln_stats_bytes = 0;  // per-row mean and 1/sqrt(var+eps)
+  float* f_split = nullptr; size_t f_split_bytes = 0;     // tf32 planes of the fp32 activations
 };
 
 struct Context {
@@ -79,10 +83,18 @@ int need_ctx() {
   return SDQ_OK;
 }
 
-Weight* get_weight(sdq_weight_t h) {
+Weight* get_any_weight(sdq_weight_t h) {
   if (!g_ctx || h == 0 || h > g_ctx->weights.size()) return nullptr;
   Weight* w = &g_ctx->weights[h - 1];
   return w->live ? w : nullptr;
+}
+Weight* get_weight(sdq_weight_t h) {  // an int8 weight
+  Weight* w = get_any_weight(h);
+  return (w && w->q) ? w : nullptr;
+}
+Weight* get_fweight(sdq_weight_t h) {  // an fp32 weight
+  Weight* w = get_any_weight(h);
+  return (w && w->f_hi) ? w : nullptr;
 }
 
 int check_status_word() {
@@ -189,6 +201,7 @@ int sdq_init(int device) {
   if (e != cudaSuccess) { delete c; return cuda_fail(e, "status word"); }
   std::string why;
   int rc = qgemm_tc_setup(&why);
+  if (rc == SDQ_OK) rc = fgemm_setup(&why);
   if (rc != SDQ_OK) { cudaFree(c->status); delete c; return fail(rc, why); }
   g_ctx = c;
   return SDQ_OK;
@@ -199,10 +212,14 @@ int sdq_shutdown(void) {
   if (!g_ctx) return SDQ_OK;
   cudaDeviceSynchronize();
   for (auto& w : g_ctx->weights)
-    if (w.live && w.owned) { cudaFree(const_cast<int8_t*>(w.q)); cudaFree(const_cast<float*>(w.scale)); }
+    if (w.live && w.owned) {
+      cudaFree(const_cast<int8_t*>(w.q)); cudaFree(const_cast<float*>(w.scale));
+      cudaFree(const_cast<float*>(w.f_hi)); cudaFree(const_cast<float*>(w.f_lo));
+    }
   for (auto& kv : g_ctx->ws) {
     cudaFree(kv.second.aq); cudaFree(kv.second.a_scale);
     cudaFree(kv.second.a_stage); cudaFree(kv.second.out_stage); cudaFree(kv.second.acc);
+    cudaFree(kv.second.ln_stats); cudaFree(kv.second.f_split);
   }
   for (int i = 0; i < 2; i++) {
     cudaFree(g_ctx->pa[i]); cudaFree(g_ctx->py[i]);
@@ -427,9 +444,12 @@ int sdq_weight_info(sdq_weight_t h, int64_t* N, int64_t* K, const int8_t** q_dev
 int sdq_weight_release(sdq_weight_t h) {
   if (int rc = need_ctx()) return rc;
   std::lock_guard<std::mutex> lk(g_ctx->mu);
-  Weight* w = get_weight(h);
+  Weight* w = get_any_weight(h);
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_weight_release: bad weight handle");
-  if (w->owned) { cudaFree(const_cast<int8_t*>(w->q)); cudaFree(const_cast<float*>(w->scale)); }
+  if (w->owned) {
+    cudaFree(const_cast<int8_t*>(w->q)); cudaFree(const_cast<float*>(w->scale));
+    cudaFree(const_cast<float*>(w->f_hi)); cudaFree(const_cast<float*>(w->f_lo));
+  }
   if (w->host_key) {
     auto it = g_ctx->by_host.find(w->host_key);
     if (it != g_ctx->by_host.end() && it->second == h) g_ctx->by_host.erase(it);
@@ -533,6 +553,73 @@ int sdq_qgemm(sdq_weight_t h, const float* A, int64_t M, float* out, const float
   }
   if (flags & SDQ_SYNC) return sdq_stream_sync(stream);
   return SDQ_OK;
+}
+
+// ---- fp32 linears ----
+int sdq_fweight_upload(const float* w, int64_t K, int64_t N, uint32_t flags, sdq_weight_t* out) {
+  if (int rc = need_ctx()) return rc;
+  if (!w || !out || K <= 0 || N <= 0)
+    return fail(SDQ_ERR_INVALID, "sdq_fweight_upload: null pointer or non-positive shape");
+  const size_t bytes = (size_t)K * N * 4;
+  float* src = nullptr;
+  float *hi = nullptr, *lo = nullptr;
+  cudaError_t e = cudaSuccess;
+  if (flags & SDQ_A_HOST) {
+    e = cudaMalloc(reinterpret_cast<void**>(&src), bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(src, w, bytes, cudaMemcpyHostToDevice);
+  }
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&hi), bytes);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&lo), bytes);
+  if (e == cudaSuccess) e = launch_transpose_split(src ? src : w, K, N, hi, lo, nullptr);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+  cudaFree(src);
+  if (e != cudaSuccess) {
+    cudaFree(hi); cudaFree(lo);
+    return fail(e == cudaErrorMemoryAllocation ? SDQ_ERR_NOMEM : SDQ_ERR_CUDA,
+                std::string("sdq_fweight_upload: ") + cudaGetErrorString(e));
+  }
+  Weight wt; wt.f_hi = hi; wt.f_lo = lo; wt.N = N; wt.K = K; wt.owned = true; wt.live = true;
+  if (flags & SDQ_A_HOST) wt.host_key = w;
+  return register_weight(wt, out);
+}
+
+int sdq_fmatmul(sdq_weight_t h, const float* A, int64_t M, float* out, const float* bias_dev,
+                uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  Weight* w = get_fweight(h);
+  if (!w) return fail(SDQ_ERR_INVALID, "sdq_fmatmul: bad weight handle (not an fp32 weight)");
+  if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_fmatmul: negative M");
+  if (M == 0) return SDQ_OK;
+  if (!A || !out) return fail(SDQ_ERR_INVALID, "sdq_fmatmul: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t N = w->N, K = w->K;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  if (int rc = grow(&ws->f_split, &ws->f_split_bytes, (size_t)M * K * 8)) return rc;
+  const float* A_dev = A;
+  float* out_dev = out;
+  if (flags & SDQ_A_HOST) {
+    if (int rc = grow(&ws->a_stage, &ws->a_stage_bytes, (size_t)M * K * 4)) return rc;
+    SDQ_CUDA(cudaMemcpyAsync(ws->a_stage, A, (size_t)M * K * 4, cudaMemcpyHostToDevice, s));
+    A_dev = ws->a_stage;
+  }
+  if (flags & SDQ_OUT_HOST) {
+    if (int rc = grow(&ws->out_stage, &ws->out_stage_bytes, (size_t)M * N * 4)) return rc;
+    out_dev = ws->out_stage;
+  }
+  std::string why;
+  cudaError_t e = launch_fmatmul(A_dev, M, K, w->f_hi, w->f_lo, N, bias_dev, out_dev, ws->f_split,
+                                 ws->f_split + (size_t)M * K, g_ctx->status, flags, g_ctx->sm_count, s, &why);
+  if (e != cudaSuccess)
+    return fail(SDQ_ERR_CUDA, why.empty() ? std::string("fp32 GEMM launch: ") + cudaGetErrorString(e) : why);
+  if (flags & SDQ_OUT_HOST) {
+    SDQ_CUDA(cudaMemcpyAsync(out, out_dev, (size_t)M * N * 4, cudaMemcpyDeviceToHost, s));
+    return sdq_stream_sync(stream);
+  }
+  return (flags & SDQ_SYNC) ? sdq_stream_sync(stream) : SDQ_OK;
 }
 
 int sdq_qgemm_residual(sdq_weight_t h, const float* A_dev, int64_t M, const float* residual_dev,

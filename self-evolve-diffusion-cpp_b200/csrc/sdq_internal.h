@@ -84,6 +84,17 @@ int qgemm_tc2_setup(std::string* why);
 bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count);  // call only if qgemm_tc_supported(g)
 cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why);
 
+// ---- fp32 matmul on tcgen05, three tf32 products per fp32 product: fgemm_tcgen05.cu ----
+int fgemm_setup(std::string* why);
+// W [K,N] fp32 row-major (device) -> tf32 planes hi / lo, transposed to [N,K].
+cudaError_t launch_transpose_split(const float* w_kn, int64_t K, int64_t N, float* hi_nk, float* lo_nk,
+                                   cudaStream_t s);
+// out[M,N] = a[M,K] * W + bias.  a_hi / a_lo: scratch planes of M*K floats each (unused by the
+// CUDA-core path taken when K % 4 != 0, a pointer is unaligned or SDQ_FORCE_SIMT is set).
+cudaError_t launch_fmatmul(const float* a, int64_t M, int64_t K, const float* w_hi, const float* w_lo,
+                           int64_t N, const float* bias, float* out, float* a_hi, float* a_lo,
+                           int* status, uint32_t flags, int sm_count, cudaStream_t s, std::string* why);
+
 // MMA-issue-bound int8 rate of the device (mma_probe.cu).
 int int8_mma_probe(int sm_count, int iters, int* status_dev, double* seconds, double* ops);
 

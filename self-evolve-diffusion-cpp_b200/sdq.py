@@ -85,6 +85,8 @@ _SIGS = {
     "sdq_ipc_close": (C.c_int, [C.c_void_p]),
     "sdq_ffn_pair": (C.c_int, [C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64,
                                C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_fweight_upload": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.POINTER(C.c_uint64)]),
+    "sdq_fmatmul": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_residual": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_ffn_block": (C.c_int, [C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64,
@@ -371,6 +373,23 @@ class Sdq:
         self._ck(self.lib.sdq_ffn_pair(w1, d1.ptr if d1 else None, w2, d2.ptr if d2 else None, _np_ptr(x), M,
                                        None, _np_ptr(y), A_HOST | OUT_HOST, None))
         return y
+
+    def fweight_upload(self, w_kn):
+        """fp32 weight [K,N] (numpy) -> handle for fmatmul."""
+        w_kn = np.ascontiguousarray(w_kn, np.float32)
+        h = C.c_uint64(0)
+        self._ck(self.lib.sdq_fweight_upload(_np_ptr(w_kn), w_kn.shape[0], w_kn.shape[1], A_HOST, C.byref(h)))
+        return h.value
+
+    def fmatmul_host(self, w, A, N, bias=None, force_simt=False):
+        """numpy in, numpy out through the host-pointer path of sdq_fmatmul."""
+        A = np.ascontiguousarray(A, np.float32)
+        M = A.shape[0]
+        out = np.empty((M, N), np.float32)
+        db = self.to_device(np.ascontiguousarray(bias, np.float32)) if bias is not None else None
+        self._ck(self.lib.sdq_fmatmul(w, _np_ptr(A), M, _np_ptr(out), db.ptr if db else None,
+                                      A_HOST | OUT_HOST | (FORCE_SIMT if force_simt else 0), None))
+        return out
 
     def qgemm_residual_np(self, w, A, x, gate=None, bias=None, inplace=True, force_simt=False):
         """numpy in, numpy out: x + (qgemm(A, W) + bias) * gate through sdq_qgemm_residual, with

@@ -3,6 +3,7 @@
 // but against the B200 drop-in.  `test_dropin --cpu <golden_dir>` runs only what
 // needs no GPU (containers, loader format errors, thread dispatch);
 // `test_dropin <golden_dir>` runs everything.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -118,6 +119,27 @@ static void test_qgemm(int64_t M, int64_t K, int64_t N) {
   for (int64_t i = 0; i < M * N; i++) CHECK(std::isfinite(out.ptr<float>()[i]));
 }
 
+static void test_matmul(int64_t M, int64_t K, int64_t N, bool with_bias) {
+  // reference tests/test_core.cpp:51-91: matmul vs a naive triple loop, max-abs error / max-abs <= 1e-3
+  Tensor A({M, K}, DType::F32), B({K, N}, DType::F32), bias({N}, DType::F32), C;
+  fill_uniform(A, 21);
+  fill_uniform(B, 22);
+  fill_uniform(bias, 23);
+  matmul(A, B, C, with_bias ? bias.ptr<float>() : nullptr);
+  CHECK(C.rows() == M && C.cols() == N && C.owning);
+  double err = 0, mx = 0;
+  for (int64_t i = 0; i < M; i++)
+    for (int64_t j = 0; j < N; j++) {
+      double s = with_bias ? bias.ptr<float>()[j] : 0.0;
+      for (int64_t k = 0; k < K; k++) s += (double)A.ptr<float>()[i * K + k] * B.ptr<float>()[k * N + j];
+      err = std::max(err, std::fabs(s - C.ptr<float>()[i * N + j]));
+      mx = std::max(mx, std::fabs(s));
+    }
+  std::printf("matmul %lldx%lldx%lld max-abs err / max-abs %.2e\n", (long long)M, (long long)K, (long long)N,
+              err / (mx > 0 ? mx : 1));
+  CHECK(err <= 1e-3 * (mx > 0 ? mx : 1));
+}
+
 static void test_quantize_rowwise() {
   // reference tests/test_core.cpp:120-132: dequantization error below one scale unit
   Tensor W({37, 513}, DType::F32), Wq, sc;
@@ -169,6 +191,9 @@ int main(int argc, char** argv) {
     test_qgemm(64, 1024, 512);
     test_qgemm(300, 3072, 640);
     test_quantize_rowwise();
+    test_matmul(17, 31, 13, false);
+    test_matmul(64, 1024, 512, true);
+    test_matmul(300, 140, 3072, true);
     test_pack(golden);
   }
   if (g_fail) std::printf("test_dropin: %d FAILED\n", g_fail);

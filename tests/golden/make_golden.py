@@ -173,6 +173,14 @@ def main():
     b2 = (rng.standard_normal(D) * 0.02).astype(np.float32)
     blk.update(ffn_x=x, ffn_e=e, ffn_q1=q1, ffn_s1=s1, ffn_b1=b1, ffn_q2=q2, ffn_s2=s2, ffn_b2=b2,
                ffn_out=ref.ffn_fwd(x, e, q1, s1, b1, q2, s2, b2))
+    # sd::matmul (the fp32 linears): a time-embedding-sized case with bias and a ragged one
+    A = rng.standard_normal((40, 256)).astype(np.float32)
+    Wf = (rng.standard_normal((256, 384)) * 0.05).astype(np.float32)
+    bf = (rng.standard_normal(384) * 0.02).astype(np.float32)
+    blk.update(mm_A=A, mm_W=Wf, mm_bias=bf, mm_out=ref.matmul(A, Wf, bf))
+    A = rng.standard_normal((17, 31)).astype(np.float32)
+    Wf = rng.standard_normal((31, 13)).astype(np.float32)
+    blk.update(mm2_A=A, mm2_W=Wf, mm2_out=ref.matmul(A, Wf))
     np.savez(os.path.join(HERE, "dit_caller.npz"), **blk)
     out["numpy"] = np.__version__
     json.dump(out, open(os.path.join(HERE, "golden.json"), "w"), indent=1, sort_keys=True)
