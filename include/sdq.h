@@ -245,8 +245,9 @@ SDQ_API int sdq_ffn_block(sdq_weight_t w1, const float* bias1_dev, sdq_weight_t 
  * checkpoints.  W is the reference's Linear layout, fp32 [K = in, N = out] row-major;
  * sdq_fweight_upload (SDQ_A_HOST: `w` is host memory, else device) transposes it once into
  * [N,K] and splits it into two tf32 planes.  sdq_fmatmul issues three tf32 tensor-core products
- * per fp32 product (hi*hi + hi*lo + lo*hi into an fp32 accumulator), which gives fp32-level
- * accuracy; the reference's own sums depend on its BLAS / SIMD order, so this path is held to
+ * per fp32 product (hi*hi + hi*lo + lo*hi, K accumulated in groups of 256 that are added in
+ * fp32 registers): about 2e-6 of the largest output, the level of an fp32 BLAS, for any K.
+ * The reference's own sums depend on its BLAS / SIMD order, so this path is held to
  * the reference's matmul tolerance (max-abs error <= 1e-3 of the largest output,
  * tests/test_core.cpp:82-84), not to bit equality.  The handle is released with
  * sdq_weight_release; the int8 entry points reject it and vice versa.  A / out are device

@@ -7,10 +7,14 @@
 // therefore split into two tf32 numbers, x = hi + lo with hi = tf32(x) and lo = tf32(x - hi),
 // and every product is issued as three MMAs into one fp32 accumulator,
 //     hi*hi + hi*lo + lo*hi          (the dropped lo*lo term is ~2^-22 of the product),
-// which recovers fp32-level accuracy (measured ~1e-6 of the largest output) at a third of the
-// tf32 rate.  The reference's own result depends on its BLAS / SIMD summation order, so this
-// path is held to the reference's tolerance for matmul (max-abs error / max-abs output <= 1e-3,
-// tests/test_core.cpp:82-84), not to bit equality.
+// which removes the input rounding at a third of the tf32 rate.  The tensor core's accumulator
+// truncates, so a long chain of accumulations drifts (measured 7e-9 * K of the largest output
+// when all of K goes into one accumulator); the sum is therefore cut into groups of kFGroup
+// k-blocks (256 elements): each group is accumulated in tensor memory, then added into fp32
+// registers by the epilogue warps with IEEE additions while the next group's MMAs run into the
+// other accumulator buffer.  The reference's own result depends on its BLAS / SIMD summation
+// order, so this path is held to the reference's tolerance for matmul (max-abs error / max-abs
+// output <= 1e-3, tests/test_core.cpp:82-84), not to bit equality.
 //
 // Layout: A_hi / A_lo are [M,K] fp32 planes written by split_tf32_kernel; the weight is
 // transposed once at upload into [N,K] planes W_hi / W_lo (K-major "TN" operands, as in the
@@ -27,6 +31,7 @@ using namespace tc;
 constexpr int kFBlockN = 128;
 constexpr int kFBlockK = 32;   // fp32 elements: one 128-byte swizzle row
 constexpr int kFStages = 3;
+constexpr int kFGroup = 8;     // k-blocks per accumulation group (256 elements of K)
 constexpr int kFTile = BLOCK_M * kFBlockK * 4;  // 16 KiB; the four operand tiles have this size
 constexpr int kFStageBytes = 4 * kFTile;
 constexpr int kFTmemCols = 2 * kFBlockN;
@@ -135,32 +140,36 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t stage = 0, phase = 0, abuf = 0, aphase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        ok = mbar_wait(bar_tempty + 8 * abuf, aphase ^ 1u, abort_flag, g.status, 0x600 | 1);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + abuf * kFBlockN;
-        for (int kb = 0; kb < num_k_blocks; kb++) {
-          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x600 | 2);
+        for (int kb0 = 0; ok && kb0 < num_k_blocks; kb0 += kFGroup) {
+          // one accumulation group into one of the two accumulator buffers
+          ok = mbar_wait(bar_tempty + 8 * abuf, aphase ^ 1u, abort_flag, g.status, 0x600 | 1);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t st = base + stage * kFStageBytes;
-          const uint64_t a_hi = make_smem_desc(st), a_lo = make_smem_desc(st + kFTile);
-          const uint64_t b_hi = make_smem_desc(st + 2 * kFTile), b_lo = make_smem_desc(st + 3 * kFTile);
+          const uint32_t tmem_d = tmem_base + abuf * kFBlockN;
+          const int kb1 = min(kb0 + kFGroup, num_k_blocks);
+          for (int kb = kb0; kb < kb1; kb++) {
+            ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x600 | 2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = base + stage * kFStageBytes;
+            const uint64_t a_hi = make_smem_desc(st), a_lo = make_smem_desc(st + kFTile);
+            const uint64_t b_hi = make_smem_desc(st + 2 * kFTile), b_lo = make_smem_desc(st + 3 * kFTile);
 #pragma unroll
-          for (int k = 0; k < kFBlockK / 8; k++) {
-            // one kind::tf32 instruction covers 8 elements = 32 bytes of K: +2 in the address field
-            const uint64_t o = (uint64_t)(k * 2);
-            umma_tf32(tmem_d, a_lo + o, b_hi + o, kFIdesc, (uint32_t)((kb | k) != 0));  // small terms first
-            umma_tf32(tmem_d, a_hi + o, b_lo + o, kFIdesc, 1u);
-            umma_tf32(tmem_d, a_hi + o, b_hi + o, kFIdesc, 1u);
+            for (int k = 0; k < kFBlockK / 8; k++) {
+              // one kind::tf32 instruction covers 8 elements = 32 bytes of K: +2 in the address field
+              const uint64_t o = (uint64_t)(k * 2);
+              umma_tf32(tmem_d, a_lo + o, b_hi + o, kFIdesc, (uint32_t)(((kb - kb0) | k) != 0));  // small terms first
+              umma_tf32(tmem_d, a_hi + o, b_lo + o, kFIdesc, 1u);
+              umma_tf32(tmem_d, a_hi + o, b_hi + o, kFIdesc, 1u);
+            }
+            umma_commit(bar_empty + 8 * stage);
+            if (++stage == kFStages) { stage = 0; phase ^= 1u; }
           }
-          umma_commit(bar_empty + 8 * stage);
-          if (++stage == kFStages) { stage = 0; phase ^= 1u; }
+          if (!ok) break;
+          umma_commit(bar_tfull + 8 * abuf);
+          abuf ^= 1u;
+          if (abuf == 0) aphase ^= 1u;
         }
-        if (!ok) break;
-        umma_commit(bar_tfull + 8 * abuf);
-        abuf ^= 1u;
-        if (abuf == 0) aphase ^= 1u;
       }
     }
   } else {
@@ -174,26 +183,44 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(tile, num_m_blocks, num_n_blocks, m_blk, n_blk);
-      ok = mbar_wait_warp(bar_tfull + 8 * abuf, aphase, abort_flag, g.status, 0x700 | 1);
-      if (!ok) break;
-      tc_fence_after();
       const int64_t row0 = (int64_t)m_blk * BLOCK_M + quarter * 32;
       const int64_t row = row0 + lane;
       const int64_t n0 = (int64_t)n_blk * kFBlockN;
-      if (row0 < g.M) {
-#pragma unroll 1
-        for (int c = half; c < kFBlockN / 32; c += 2) {
-          const int64_t nc = n0 + c * 32;
-          if (nc >= g.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + abuf * kFBlockN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
-          tmem_ld_wait();
-          float o[32];
+      // this warp's two 32-column chunks of the tile, summed over the groups in registers
+      float acc[2][32];
 #pragma unroll
-          for (int j = 0; j < 32; j++) {
-            o[j] = __uint_as_float(r[j]);
-            // C += bias as a separate add, like add_bias (src/core/gemm.cpp:33-40)
-            if (g.bias && nc + j < g.N) o[j] = __fadd_rn(o[j], __ldg(g.bias + nc + j));
+      for (int c = 0; c < 2; c++)
+#pragma unroll
+        for (int j = 0; j < 32; j++) acc[c][j] = 0.0f;
+      for (int kb0 = 0; ok && kb0 < num_k_blocks; kb0 += kFGroup) {
+        ok = mbar_wait_warp(bar_tfull + 8 * abuf, aphase, abort_flag, g.status, 0x700 | 1);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + abuf * kFBlockN + (half + 2 * c) * 32 + ((uint32_t)(quarter * 32) << 16), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j++) acc[c][j] = __fadd_rn(acc[c][j], __uint_as_float(r[j]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * abuf);
+        abuf ^= 1u;
+        if (abuf == 0) aphase ^= 1u;
+      }
+      if (!ok) break;
+      if (row0 < g.M) {
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          const int64_t nc = n0 + (half + 2 * c) * 32;
+          if (nc >= g.N) break;
+          float (&o)[32] = acc[c];
+          if (g.bias) {  // C += bias as a separate add, like add_bias (src/core/gemm.cpp:33-40)
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (nc + j < g.N) o[j] = __fadd_rn(o[j], __ldg(g.bias + nc + j));
           }
           if (use_tma_store) {
             if (lane == 0) bulk_wait_read<0>();
@@ -216,11 +243,6 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * abuf);
-      abuf ^= 1u;
-      if (abuf == 0) aphase ^= 1u;
     }
   }
 

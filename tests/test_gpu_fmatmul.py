@@ -1,12 +1,13 @@
 """GPU: the fp32 linears (sd::matmul behind blk::linear) on the tensor cores.
 
-Three tf32 products per fp32 product remove the 2^-11 input rounding of a plain tf32 GEMM; what
-remains is the tensor core's accumulator, which truncates, so the error grows with the number
-of accumulation steps: measured 2e-6 of the largest output at K=256, 2.3e-5 at K=3072, 1.0e-4
-at K=14336 (about 7.3e-9 * K).  The reference's own sums depend on its SIMD / BLAS order and its
-test gates matmul at max-abs error <= 1e-3 of the largest output (tests/test_core.cpp:82-84).
-Here: that gate against the reference's outputs (fixtures from the compiled sd::matmul) and the
-left-to-right restatement, and the tighter K-proportional bound against a float64 product.
+Three tf32 products per fp32 product remove the 2^-11 input rounding of a plain tf32 GEMM, and
+K is accumulated in groups of 256 elements that are added in fp32 registers (the tensor core's
+own accumulator truncates, which over one long chain costs ~7e-9 * K): measured about 2e-6 of the
+largest output for every K from 36 to 14336 -- the level of an fp32 BLAS.  The reference's own
+sums depend on its SIMD / BLAS order and its test gates matmul at max-abs error <= 1e-3 of the
+largest output (tests/test_core.cpp:82-84).  Here: that gate against the reference's outputs
+(fixtures from the compiled sd::matmul) and the left-to-right restatement, and 4e-6 against a
+float64 product.
 """
 import os
 
@@ -21,8 +22,8 @@ REF_TOL = 1e-3      # the reference's own gate for matmul
 
 
 def acc_tol(K):
-    """Bound on max-abs error / max-abs output against float64: truncating accumulation over K."""
-    return 1.2e-8 * K + 1e-6
+    """Bound on max-abs error / max-abs output against float64 (independent of K)."""
+    return 4e-6
 
 
 @pytest.fixture(scope="module")
