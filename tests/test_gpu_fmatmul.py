@@ -101,3 +101,24 @@ def test_handles_are_typed(sdq, pkg, oracle):
     assert sdq.fmatmul_host(wf, np.zeros((0, 64), np.float32), 32).shape == (0, 32)   # M == 0
     sdq.weight_release(wf)
     sdq.weight_release(wq)
+
+
+def test_device_pointers_on_a_stream(sdq, pkg):
+    """Device-resident A / out / bias on a caller's stream, two calls back to back (the scratch
+    planes are per stream and reused)."""
+    rng = np.random.default_rng(9)
+    M, K, N = 700, 512, 384
+    W = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    w = sdq.fweight_upload(W)
+    st = sdq.stream_create()
+    db, dout = sdq.to_device(b), sdq.alloc(M * N * 4)
+    for seed in (1, 2):
+        A = np.random.default_rng(seed).standard_normal((M, K)).astype(np.float32)
+        dA = sdq.to_device(A)
+        sdq._ck(sdq.lib.sdq_fmatmul(w, dA.ptr, M, dout.ptr, db.ptr, 0, st))
+        sdq.sync(st)
+        want = (A.astype(np.float64) @ W.astype(np.float64) + b).astype(np.float32)
+        assert max_rel_err(dout.to_numpy(np.float32, (M, N)), want) < acc_tol(K)
+    sdq.stream_destroy(st)
+    sdq.weight_release(w)
