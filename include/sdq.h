@@ -257,6 +257,19 @@ SDQ_API int sdq_fweight_upload(const float* w, int64_t K, int64_t N, uint32_t fl
 SDQ_API int sdq_fmatmul(sdq_weight_t w, const float* A, int64_t M, float* out,
                         const float* bias_dev, uint32_t flags, void* stream);
 
+/* ---- attention between the projections ----
+ * out[Lq,C] = softmax(q k^T / sqrt(C/heads)) v for each of `heads` heads -- replaces blk::sdpa
+ * (src/model/blocks.h:60-66, src/model/blocks.cpp:113-199; the reference never sets its causal
+ * flag).  q is fp32 [Lq,C], k and v fp32 [Lk,C], all device memory; head h owns columns
+ * [h*C/heads, (h+1)*C/heads).  For head_dim 128 (the DiT's) the scores are computed on the
+ * tensor cores with three tf32 products per fp32 product, the softmax weights and v are rounded
+ * to tf32 once, and the row maximum comes from a first sweep over the keys, so no accumulator is
+ * rescaled; other head sizes take an fp32 CUDA-core kernel.  Held to the reference's 1e-3 bound
+ * (max-abs error / max-abs output); exp and the summation order are not bit-reproducible. */
+SDQ_API int sdq_sdpa(const float* q_dev, const float* k_dev, const float* v_dev, int64_t Lq,
+                     int64_t Lk, int64_t C, int heads, float* out_dev, uint32_t flags,
+                     void* stream);
+
 /* The same computation as sdq_qgemm for callers that cannot allocate device memory
  * while they run (a host that has given all HBM to its own pool, a plugin inside
  * another allocator, a section where cudaMalloc's implicit device-wide

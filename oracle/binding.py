@@ -46,7 +46,7 @@ class Oracle:
                      "orc_bias_add", "orc_gelu_tanh", "orc_quantize_rowwise",
                      "orc_quant_rows_packer", "orc_dequant_rows", "orc_f32_to_bf16",
                      "orc_bf16_to_f32", "orc_f16_to_f32", "orc_set_threads", "orc_layernorm_mod",
-                     "orc_residual_add", "orc_layernorm_affine", "orc_matmul_f32"):
+                     "orc_residual_add", "orc_layernorm_affine", "orc_matmul_f32", "orc_sdpa"):
             getattr(L, name).restype = None
 
     def threads(self):
@@ -151,6 +151,13 @@ class Oracle:
         out = np.empty((M, N), np.float32)
         self.lib.orc_matmul_f32(_ptr(a), i64(M), i64(K), _ptr(w), i64(N),
                                 None if bias is None else _ptr(bias), _ptr(out))
+        return out
+
+    def sdpa(self, q, k, v, heads):
+        q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+        Lq, Cc = q.shape
+        out = np.empty((Lq, Cc), np.float32)
+        self.lib.orc_sdpa(_ptr(q), _ptr(k), _ptr(v), i64(Lq), i64(k.shape[0]), i64(Cc), C.c_int(heads), _ptr(out))
         return out
 
     def f32_to_bf16(self, x):
@@ -305,6 +312,15 @@ class Reference:
         self.lib.sdref_matmul.restype = None
         self.lib.sdref_matmul(_ptr(a), i64(M), i64(K), _ptr(w), i64(N),
                               None if bias is None else _ptr(bias), _ptr(out))
+        return out
+
+    def sdpa(self, q, k, v, heads):
+        """blk::sdpa, exact fp32 attention."""
+        q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+        Lq, Cc = q.shape
+        out = np.zeros((Lq, Cc), np.float32)
+        self.lib.sdref_sdpa.restype = None
+        self.lib.sdref_sdpa(_ptr(q), _ptr(k), _ptr(v), i64(Lq), i64(k.shape[0]), i64(Cc), C.c_int(heads), _ptr(out))
         return out
 
     def load_sdcpp_listing(self, path):

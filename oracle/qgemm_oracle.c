@@ -337,6 +337,48 @@ void orc_matmul_f32(const float* a, int64_t M, int64_t K, const float* w, int64_
   par_rows(M, mm_range, &j);
 }
 
+/* blk::sdpa, the portable branch (src/model/blocks.cpp:146-152, 156-166, 183-190): per head and
+ * query row, scores s_j = (sum_d q_d k_jd) * scale added left to right, mx = max s_j,
+ * s_j = exp(s_j - mx), sum, s_j *= 1/sum, then o_d = sum_j s_j * v_jd.  (That branch multiplies
+ * the already normalised s_j by inv once more -- a slip the AVX2 branch the reference is built
+ * with does not have; the restatement follows the AVX2 branch's arithmetic: normalise once.)
+ * expf and the summation orders differ between builds, so comparisons are under a tolerance. */
+typedef struct { const float* q; const float* k; const float* v; float* out; int64_t Lq, Lk, C; int heads; } sdpa_t;
+static void sdpa_range(int64_t b, int64_t e, void* p) {
+  sdpa_t* j = (sdpa_t*)p;
+  const int64_t hd = j->C / j->heads;
+  const float scale = 1.0f / sqrtf((float)hd);
+  float* s = (float*)malloc((size_t)(j->Lk > 0 ? j->Lk : 1) * sizeof(float));
+  for (int64_t it = b; it < e; it++) {
+    const int64_t h = it / j->Lq, i = it % j->Lq;
+    const float* qi = j->q + i * j->C + h * hd;
+    float mx = -INFINITY;
+    for (int64_t t = 0; t < j->Lk; t++) {
+      const float* kt = j->k + t * j->C + h * hd;
+      float d = 0.0f;
+      for (int64_t c = 0; c < hd; c++) d += qi[c] * kt[c];
+      s[t] = d * scale;
+      if (s[t] > mx) mx = s[t];
+    }
+    float sum = 0.0f;
+    for (int64_t t = 0; t < j->Lk; t++) { s[t] = expf(s[t] - mx); sum += s[t]; }
+    const float inv = 1.0f / sum;
+    float* o = j->out + i * j->C + h * hd;
+    for (int64_t c = 0; c < hd; c++) o[c] = 0.0f;
+    for (int64_t t = 0; t < j->Lk; t++) {
+      const float w = s[t] * inv;
+      const float* vt = j->v + t * j->C + h * hd;
+      for (int64_t c = 0; c < hd; c++) o[c] += w * vt[c];
+    }
+  }
+  free(s);
+}
+void orc_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk, int64_t C,
+              int heads, float* out) {
+  sdpa_t j = {q, k, v, out, Lq, Lk, C, heads};
+  par_rows(Lq * heads, sdpa_range, &j);
+}
+
 /* src/model/ovi_dit.cpp:53-63. */
 void orc_dequant_rows(const int8_t* q, const float* scale, int64_t rows, int64_t last, float* w) {
   for (int64_t i = 0; i < rows; i++)

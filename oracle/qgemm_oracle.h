@@ -78,6 +78,12 @@ void orc_layernorm_affine(const float* x, int64_t M, int64_t K, const float* wei
 void orc_matmul_f32(const float* a, int64_t M, int64_t K, const float* w, int64_t N,
                     const float* bias_or_null, float* out);
 
+/* blk::sdpa (src/model/blocks.cpp:113-199): out[Lq,C] = softmax(q k^T / sqrt(C/heads)) v per head,
+ * q [Lq,C], k and v [Lk,C], fp32, no mask.  Tolerance-level comparisons only (expf and the
+ * summation orders differ between builds). */
+void orc_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk, int64_t C,
+              int heads, float* out);
+
 /* Threads used by the loops above; <=0 restores the default. */
 void orc_set_threads(int n);
 int orc_threads(void);

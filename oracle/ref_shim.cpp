@@ -90,6 +90,18 @@ void sdref_matmul(const float* a, int64_t M, int64_t K, const float* w, int64_t 
   if (o.data && o.nbytes) std::memcpy(out, o.data, o.nbytes);
 }
 
+// blk::sdpa (src/model/blocks.h:60-66, src/model/blocks.cpp:113-199): out[Lq,C] =
+// softmax(q k^T / sqrt(hd)) v per head, exact fp32, no causal mask.
+void sdref_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk, int64_t C,
+                int heads, float* out) {
+  sd::Tensor qt = view(q, {Lq, C}, sd::DType::F32, (size_t)Lq * C * 4);
+  sd::Tensor kt = view(k, {Lk, C}, sd::DType::F32, (size_t)Lk * C * 4);
+  sd::Tensor vt = view(v, {Lk, C}, sd::DType::F32, (size_t)Lk * C * 4);
+  sd::Tensor o;
+  sd::blk::sdpa(qt, kt, vt, heads, o, false);
+  if (o.data && o.nbytes) std::memcpy(out, o.data, o.nbytes);
+}
+
 void sdref_to_bf16(const float* src, uint16_t* dst, int64_t n) {
   sd::Tensor s = view(src, {n}, sd::DType::F32, (size_t)n * 4);
   sd::Tensor o;

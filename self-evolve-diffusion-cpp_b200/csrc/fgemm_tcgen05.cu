@@ -23,6 +23,7 @@
 // 32-element k-block), an MMA lane (4 k-steps x 3 products per stage), eight epilogue warps
 // (tcgen05.ld, + bias, staged bulk tensor stores), two accumulator buffers in tensor memory.
 #include "tc_common.cuh"
+#include "tf32_split.cuh"
 
 namespace sdq {
 namespace {
@@ -259,18 +260,6 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     __syncwarp();
     tmem_dealloc(tmem_base, kFTmemCols);
   }
-}
-
-// x = hi + lo with both parts representable in tf32 (10 explicit mantissa bits, low 13 bits of
-// the word zero).  Non-finite x: hi carries it, lo is zero.
-__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-  uint32_t h, l;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
-  hi = __uint_as_float(h);
-  const float rest = __fsub_rn(x, hi);
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
-  lo = (fabsf(hi) <= 3.4028234e38f) ? __uint_as_float(l) : 0.0f;
-  if (!(fabsf(hi) <= 3.4028234e38f)) hi = x;
 }
 
 __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ x, int64_t n,

@@ -39,6 +39,7 @@ struct Workspace {
   int32_t* acc = nullptr; size_t acc_bytes = 0;   // split-K partial sums
   float2* ln_stats = nullptr; size_t ln_stats_bytes = 0;  // per-row mean and 1/sqrt(var+eps)
   float* f_split = nullptr; size_t f_split_bytes = 0;     // tf32 planes of the fp32 activations
+  float* attn = nullptr; size_t attn_bytes = 0;           // attention: tf32 planes of k, v^T
 };
 
 struct Context {
@@ -202,6 +203,7 @@ int sdq_init(int device) {
   std::string why;
   int rc = qgemm_tc_setup(&why);
   if (rc == SDQ_OK) rc = fgemm_setup(&why);
+  if (rc == SDQ_OK) rc = sdpa_setup(&why);
   if (rc != SDQ_OK) { cudaFree(c->status); delete c; return fail(rc, why); }
   g_ctx = c;
   return SDQ_OK;
@@ -219,7 +221,7 @@ int sdq_shutdown(void) {
   for (auto& kv : g_ctx->ws) {
     cudaFree(kv.second.aq); cudaFree(kv.second.a_scale);
     cudaFree(kv.second.a_stage); cudaFree(kv.second.out_stage); cudaFree(kv.second.acc);
-    cudaFree(kv.second.ln_stats); cudaFree(kv.second.f_split);
+    cudaFree(kv.second.ln_stats); cudaFree(kv.second.f_split); cudaFree(kv.second.attn);
   }
   for (int i = 0; i < 2; i++) {
     cudaFree(g_ctx->pa[i]); cudaFree(g_ctx->py[i]);
@@ -619,6 +621,30 @@ int sdq_fmatmul(sdq_weight_t h, const float* A, int64_t M, float* out, const flo
     SDQ_CUDA(cudaMemcpyAsync(out, out_dev, (size_t)M * N * 4, cudaMemcpyDeviceToHost, s));
     return sdq_stream_sync(stream);
   }
+  return (flags & SDQ_SYNC) ? sdq_stream_sync(stream) : SDQ_OK;
+}
+
+// ---- attention ----
+int sdq_sdpa(const float* q_dev, const float* k_dev, const float* v_dev, int64_t Lq, int64_t Lk,
+             int64_t C, int heads, float* out_dev, uint32_t flags, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (Lq < 0 || Lk < 0 || C <= 0 || heads <= 0 || C % heads != 0)
+    return fail(SDQ_ERR_INVALID, "sdq_sdpa: bad shape (C must be a positive multiple of heads)");
+  if (flags & (SDQ_A_HOST | SDQ_OUT_HOST)) return fail(SDQ_ERR_INVALID, "sdq_sdpa: device pointers only");
+  if (Lq == 0) return SDQ_OK;
+  if (!q_dev || !out_dev || (Lk > 0 && (!k_dev || !v_dev))) return fail(SDQ_ERR_INVALID, "sdq_sdpa: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  Workspace* ws;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx->mu);
+    ws = &g_ctx->ws[s];
+  }
+  if (int rc = grow(&ws->attn, &ws->attn_bytes, sdpa_scratch_bytes(Lk, C) + 16)) return rc;
+  std::string why;
+  cudaError_t e = launch_sdpa(q_dev, k_dev, v_dev, Lq, Lk, C, heads, out_dev, ws->attn, g_ctx->status, flags,
+                              g_ctx->sm_count, s, &why);
+  if (e != cudaSuccess)
+    return fail(SDQ_ERR_CUDA, why.empty() ? std::string("attention launch: ") + cudaGetErrorString(e) : why);
   return (flags & SDQ_SYNC) ? sdq_stream_sync(stream) : SDQ_OK;
 }
 

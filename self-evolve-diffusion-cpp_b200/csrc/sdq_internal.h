@@ -95,6 +95,14 @@ cudaError_t launch_fmatmul(const float* a, int64_t M, int64_t K, const float* w_
                            int64_t N, const float* bias, float* out, float* a_hi, float* a_lo,
                            int* status, uint32_t flags, int sm_count, cudaStream_t s, std::string* why);
 
+// ---- exact-softmax attention (blk::sdpa) on tcgen05: sdpa_tcgen05.cu ----
+int sdpa_setup(std::string* why);
+size_t sdpa_scratch_bytes(int64_t Lk, int64_t C);  // tf32 planes of k and the transposed v
+// out[Lq,C] = softmax(q k^T / sqrt(C/heads)) v per head; q [Lq,C], k and v [Lk,C], all device fp32.
+cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk,
+                        int64_t C, int heads, float* out, float* scratch, int* status,
+                        uint32_t flags, int sm_count, cudaStream_t s, std::string* why);
+
 // MMA-issue-bound int8 rate of the device (mma_probe.cu).
 int int8_mma_probe(int sm_count, int iters, int* status_dev, double* seconds, double* ops);
 

@@ -87,6 +87,8 @@ _SIGS = {
                                C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_fweight_upload": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.POINTER(C.c_uint64)]),
     "sdq_fmatmul": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "sdq_sdpa": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int,
+                           C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_qgemm_residual": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_uint32, C.c_void_p]),
     "sdq_ffn_block": (C.c_int, [C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_int64,
@@ -390,6 +392,16 @@ class Sdq:
         self._ck(self.lib.sdq_fmatmul(w, _np_ptr(A), M, _np_ptr(out), db.ptr if db else None,
                                       A_HOST | OUT_HOST | (FORCE_SIMT if force_simt else 0), None))
         return out
+
+    def sdpa_np(self, q, k, v, heads, force_simt=False):
+        """numpy in, numpy out through sdq_sdpa."""
+        q, k, v = [np.ascontiguousarray(a, np.float32) for a in (q, k, v)]
+        Lq, Cc = q.shape
+        dq, dk, dv = self.to_device(q), self.to_device(k), self.to_device(v)
+        dout = self.alloc(max(Lq * Cc * 4, 4))
+        self._ck(self.lib.sdq_sdpa(dq.ptr, dk.ptr, dv.ptr, Lq, k.shape[0], Cc, heads, dout.ptr,
+                                   SYNC | (FORCE_SIMT if force_simt else 0), None))
+        return dout.to_numpy(np.float32, (Lq, Cc))
 
     def qgemm_residual_np(self, w, A, x, gate=None, bias=None, inplace=True, force_simt=False):
         """numpy in, numpy out: x + (qgemm(A, W) + bias) * gate through sdq_qgemm_residual, with

@@ -181,6 +181,11 @@ def main():
     A = rng.standard_normal((17, 31)).astype(np.float32)
     Wf = rng.standard_normal((31, 13)).astype(np.float32)
     blk.update(mm2_A=A, mm2_W=Wf, mm2_out=ref.matmul(A, Wf))
+    # blk::sdpa (exact fp32 attention): 3 heads of 128, ragged token counts
+    q = rng.standard_normal((70, 384)).astype(np.float32)
+    k = rng.standard_normal((130, 384)).astype(np.float32)
+    v = rng.standard_normal((130, 384)).astype(np.float32)
+    blk.update(at_q=q, at_k=k, at_v=v, at_out=ref.sdpa(q, k, v, 3))
     np.savez(os.path.join(HERE, "dit_caller.npz"), **blk)
     out["numpy"] = np.__version__
     json.dump(out, open(os.path.join(HERE, "golden.json"), "w"), indent=1, sort_keys=True)

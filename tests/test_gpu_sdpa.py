@@ -1,0 +1,90 @@
+"""GPU: exact-softmax attention (blk::sdpa) against the reference's outputs and the restatement.
+
+The reference gates attention like its other fp32 kernels: max-abs error <= 1e-3 of the largest
+output.  The tensor-core path computes the scores with three tf32 products per fp32 product and
+rounds the softmax weights and v to tf32 once; measured errors are a few 1e-5.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from util import max_rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+
+
+def attention64(q, k, v, heads):
+    Lq, C = q.shape
+    hd = C // heads
+    q64, k64, v64 = [x.astype(np.float64).reshape(-1, heads, hd).transpose(1, 0, 2) for x in (q, k, v)]
+    s = q64 @ k64.transpose(0, 2, 1) / np.sqrt(hd)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    return (p @ v64).transpose(1, 0, 2).reshape(Lq, C).astype(np.float32)
+
+
+def test_matches_reference_fixture(sdq, golden_dir):
+    z = np.load(os.path.join(golden_dir, "dit_caller.npz"))
+    for simt in (False, True):
+        got = sdq.sdpa_np(z["at_q"], z["at_k"], z["at_v"], 3, force_simt=simt)
+        assert max_rel_err(got, z["at_out"]) < TOL, simt
+        assert max_rel_err(got, z["at_out"]) < (1e-5 if simt else 6e-4), simt
+
+
+@pytest.mark.parametrize("Lq,Lk,heads", [
+    (1, 1, 1),            # one key: the output is that key's value row
+    (5, 63, 2), (128, 64, 1), (129, 65, 2), (300, 1000, 2),
+    (1024, 512, 24),      # the text cross-attention of a 1024-token tile: all 24 heads
+    (2048, 2048, 4),
+    (700, 4100, 3),       # many key blocks per row, ragged at both ends
+])
+def test_against_float64(sdq, Lq, Lk, heads):
+    rng = np.random.default_rng(Lq + Lk + heads)
+    C = heads * 128
+    q = rng.standard_normal((Lq, C)).astype(np.float32)
+    k = rng.standard_normal((Lk, C)).astype(np.float32)
+    v = rng.standard_normal((Lk, C)).astype(np.float32)
+    got = sdq.sdpa_np(q, k, v, heads)
+    want = attention64(q, k, v, heads)
+    assert np.isfinite(got).all()
+    assert max_rel_err(got, want) < TOL
+    assert max_rel_err(got, want) < 6e-4
+
+
+def test_peaked_and_shifted_scores(sdq):
+    """Large logits (one key dominates a row), a common offset on all keys, and rows whose best
+    key sits in the last, ragged key block."""
+    rng = np.random.default_rng(8)
+    heads, Lq, Lk = 2, 200, 333
+    C = heads * 128
+    q = (rng.standard_normal((Lq, C)) * 4).astype(np.float32)
+    k = (rng.standard_normal((Lk, C)) * 2 + 0.5).astype(np.float32)
+    v = rng.standard_normal((Lk, C)).astype(np.float32)
+    k[-1] = 3.0 * q[7]                                   # row 7's best key is the very last one
+    got = sdq.sdpa_np(q, k, v, heads)
+    want = attention64(q, k, v, heads)
+    assert np.isfinite(got).all()
+    assert max_rel_err(got, want) < TOL
+
+
+def test_other_head_sizes_take_the_cuda_core_kernel(sdq):
+    rng = np.random.default_rng(2)
+    for heads, hd, Lq, Lk in [(3, 64, 40, 77), (2, 96, 9, 130), (1, 20, 5, 3)]:
+        C = heads * hd
+        q, k, v = [rng.standard_normal((n, C)).astype(np.float32) for n in (Lq, Lk, Lk)]
+        assert max_rel_err(sdq.sdpa_np(q, k, v, heads), attention64(q, k, v, heads)) < 1e-5
+
+
+def test_arguments(sdq, pkg):
+    d = sdq.alloc(1024)
+    with pytest.raises(pkg.SdqError):
+        sdq._ck(sdq.lib.sdq_sdpa(d.ptr, d.ptr, d.ptr, 1, 1, 100, 3, d.ptr, 0, None))     # C % heads
+    with pytest.raises(pkg.SdqError):
+        sdq._ck(sdq.lib.sdq_sdpa(None, d.ptr, d.ptr, 1, 1, 128, 1, d.ptr, 0, None))
+    assert sdq.lib.sdq_sdpa(d.ptr, d.ptr, d.ptr, 0, 5, 128, 1, d.ptr, 0, None) == 0       # no queries
+    out = sdq.sdpa_np(np.ones((2, 128), np.float32), np.zeros((0, 128), np.float32),
+                      np.zeros((0, 128), np.float32), 1)
+    assert np.array_equal(out, np.zeros((2, 128), np.float32))                            # no keys

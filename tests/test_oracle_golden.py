@@ -156,6 +156,11 @@ def test_fp32_matmul_restatement_within_reference_tolerance(oracle, golden_dir):
     assert max_rel_err(oracle.matmul_f32(z["mm2_A"], z["mm2_W"]), z["mm2_out"]) < 1e-5
 
 
+def test_attention_restatement_within_reference_tolerance(oracle, golden_dir):
+    z = np.load(os.path.join(golden_dir, "dit_caller.npz"))
+    assert max_rel_err(oracle.sdpa(z["at_q"], z["at_k"], z["at_v"], 3), z["at_out"]) < 1e-5
+
+
 def test_caller_side_live_reference(oracle, reference):
     rng = np.random.default_rng(31)
     x = rng.standard_normal((33, 130)).astype(np.float32)
