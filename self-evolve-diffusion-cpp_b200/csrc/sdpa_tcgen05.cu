@@ -16,13 +16,13 @@
 // and accumulates P*V in tensor memory for the whole key range.  No accumulator is ever rescaled.
 //
 // One CTA per (128 query rows, head), persistent over these work items; 320 threads:
-//   warp 0 lane 0 : TMA producer.  Per 64-key block: k_hi (sweep 1) or k_hi, k_lo and v^T
-//                   (sweep 2) as 128-byte-swizzled boxes into a two-stage ring.
+//   warp 0 lane 0 : TMA producer.  128 keys of k_hi per stage in sweep 1; per 64-key block
+//                   k_hi, k_lo and v^T in sweep 2; 128-byte-swizzled boxes, two-stage ring.
 //   warp 1 lane 0 : MMA issuer.  S = Q K^T with Q (both tf32 planes) as the A operand in TENSOR
 //                   MEMORY, K from shared memory; O += P V with P in tensor memory (written in
 //                   place over S by the softmax warps), V^T from shared memory.
-//   warps 2..5    : softmax group A (one thread per query row): the even key blocks.
-//   warps 6..9    : softmax group B: the odd key blocks.  Both groups finish the tile together:
+//   warps 2..5    : softmax group A (one thread per query row): the first 32 keys of every block.
+//   warps 6..9    : softmax group B: the other 32 keys.  Both groups finish the tile together:
 //                   O / row sum -> staged boxes -> bulk tensor stores.
 // Tensor memory (512 columns): Q_hi 0..127, Q_lo 128..255, O 256..383, S/P buffers 384..447 and
 // 448..511.  Every mbarrier wait is bounded like the GEMM kernels'.
@@ -86,7 +86,8 @@ struct SdpaArgs {
 };
 
 __global__ void __launch_bounds__(kNumThreads, 1)
-    sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi,
+    sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi128,
+                   const __grid_constant__ CUtensorMap tmap_k_hi,
                    const __grid_constant__ CUtensorMap tmap_k_lo,
                    const __grid_constant__ CUtensorMap tmap_vt,
                    const __grid_constant__ CUtensorMap tmap_out, SdpaArgs g) {
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqt = (int)((g.Lq + kBq - 1) / kBq);
   const int nblk = (int)((g.Lk + kBkv - 1) / kBkv);
+  const int nblk1 = (int)((g.Lk + 2 * kBkv - 1) / (2 * kBkv));  // sweep 1 walks 128 keys at a time
   const int num_items = nqt * g.heads;
 
   if (threadIdx.x == 0) {
@@ -131,8 +133,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_empty + 8 * i, 1);
       mbar_init(bar_sfull + 8 * i, 1);
-      mbar_init(bar_s1free + 8 * i, 4);
-      mbar_init(bar_pready + 8 * i, 4);
+      mbar_init(bar_s1free + 8 * i, 8);
+      mbar_init(bar_pready + 8 * i, 8);
       mbar_init(bar_pvdone + 8 * i, 1);
     }
     mbar_init(bar_qready, 4);
@@ -143,6 +145,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    prefetch_tmap(&tmap_k_hi128);
     prefetch_tmap(&tmap_k_hi);
     prefetch_tmap(&tmap_k_lo);
     prefetch_tmap(&tmap_vt);
@@ -165,23 +168,31 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int h = item / nqt;
-        for (int sweep = 0; ok && sweep < 2; sweep++) {
-          for (int j = 0; j < nblk; j++) {
-            ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 1);
-            if (!ok) break;
-            const uint32_t full = bar_full + 8 * stage;
-            const uint32_t st = base + stage * kAStageBytes;
-            mbar_expect_tx(full, sweep == 0 ? kKTile : kAStageBytes);
-            for (int i = 0; i < 4; i++)  // 32 dims per box
-              tma_load_2d_hint(st + i * 8192, &tmap_k_hi, full, h * kHd + 32 * i, j * kBkv, keep);
-            if (sweep == 1) {
-              for (int i = 0; i < 4; i++)
-                tma_load_2d_hint(st + kKTile + i * 8192, &tmap_k_lo, full, h * kHd + 32 * i, j * kBkv, keep);
-              for (int i = 0; i < 2; i++)  // 32 keys per box
-                tma_load_2d_hint(st + 2 * kKTile + i * 16384, &tmap_vt, full, j * kBkv + 32 * i, h * kHd, keep);
-            }
-            if (++stage == kAStages) { stage = 0; phase ^= 1u; }
+        // sweep 1: k_hi only, 128 keys per stage (four boxes of 128 keys x 32 dims)
+        for (int j = 0; j < nblk1; j++) {
+          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 1);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t st = base + stage * kAStageBytes;
+          mbar_expect_tx(full, 2 * kKTile);
+          for (int i = 0; i < 4; i++)
+            tma_load_2d_hint(st + i * 16384, &tmap_k_hi128, full, h * kHd + 32 * i, j * 2 * kBkv, keep);
+          if (++stage == kAStages) { stage = 0; phase ^= 1u; }
+        }
+        // sweep 2: k_hi, k_lo (boxes of 64 keys x 32 dims) and v^T (boxes of 128 dims x 32 keys)
+        for (int j = 0; ok && j < nblk; j++) {
+          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 2);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t st = base + stage * kAStageBytes;
+          mbar_expect_tx(full, kAStageBytes);
+          for (int i = 0; i < 4; i++) {
+            tma_load_2d_hint(st + i * 8192, &tmap_k_hi, full, h * kHd + 32 * i, j * kBkv, keep);
+            tma_load_2d_hint(st + kKTile + i * 8192, &tmap_k_lo, full, h * kHd + 32 * i, j * kBkv, keep);
           }
+          for (int i = 0; i < 2; i++)
+            tma_load_2d_hint(st + 2 * kKTile + i * 16384, &tmap_vt, full, j * kBkv + 32 * i, h * kHd, keep);
+          if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -217,8 +228,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         q_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
-        // ---- sweep 1: plain tf32 scores, for the row maxima
-        for (int j = 0; j < nblk; j++) {
+        // the previous item's O has been read out: sweep 1 borrows its columns
+        ok = mbar_wait(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
+        ofree_ph ^= 1u;
+        if (!ok) break;
+        tc_fence_after();
+        // ---- sweep 1: plain tf32 scores for the row maxima, 128 keys per MMA, alternating
+        // between the score columns (384..511) and the idle O columns (256..383)
+        for (int j = 0; j < nblk1; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
           ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x900 | 2);
           if (!ok) break;
@@ -226,19 +243,21 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (!ok) break;
           sfree_ph[buf] ^= 1u;
           tc_fence_after();
-          issue_scores(base + stage * kAStageBytes, buf, false);
+          const uint32_t st = base + stage * kAStageBytes;
+          const uint32_t d = tmem_base + (buf ? kColO : kColS);
+#pragma unroll
+          for (int ks = 0; ks < kHd / 8; ks++) {
+            const uint64_t kd = make_smem_desc(st + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
+            umma_tf32_ts(d, tmem_base + kColQhi + ks * 8, kd, kIdescO, (uint32_t)(ks != 0));
+          }
           umma_commit(bar_empty + 8 * stage);
           umma_commit(bar_sfull + 8 * buf);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        // the softmax groups have read every score of sweep 1 and published the maxima;
-        // the previous item's O has been read out
+        // the softmax groups have read every score of sweep 1 and published the maxima
         ok = mbar_wait(bar_mready, m_ph, abort_flag, g.status, 0x900 | 4);
         m_ph ^= 1u;
-        if (!ok) break;
-        ok = mbar_wait(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
-        ofree_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
         // ---- sweep 2: accurate scores, P*V; the scores of block j+1 are issued before the
@@ -298,13 +317,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   } else {
     // -------------------------------------------------- softmax groups + epilogue (8 warps)
     const int quarter = warp & 3;
-    const int grp = (warp - 2) >> 2;        // 0: even key blocks, 1: odd key blocks
+    const int grp = (warp - 2) >> 2;        // 0: keys 0..31 of every block, 1: keys 32..63
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
     const uint64_t stream_policy = policy_evict_first();
-    const uint32_t s_col = tmem_base + kColS + (uint32_t)grp * kBkv + lane_base;
-    uint32_t sfull_ph = 0, m_ph = 0, l_ph = 0, ofull_ph = 0;
+    const uint32_t s_col = tmem_base + kColS + (uint32_t)grp * 32 + lane_base;  // + buffer * kBkv
+    uint32_t sfull_ph[2] = {0, 0};
+    uint32_t m_ph = 0, l_ph = 0, ofull_ph = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
       const int h = item / nqt, qt = item - h * nqt;
@@ -339,24 +359,27 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       }
       // ---- sweep 1: the row maximum over this group's blocks (raw dot products)
       float m = -INFINITY;
-      for (int j = grp; j < nblk; j += 2) {
-        ok = mbar_wait_warp(bar_sfull + 8 * grp, sfull_ph, abort_flag, g.status, 0xa00 | 1);
-        sfull_ph ^= 1u;
+      for (int j = 0; j < nblk1; j++) {
+        const uint32_t buf = (uint32_t)(j & 1);
+        ok = mbar_wait_warp(bar_sfull + 8 * buf, sfull_ph[buf], abort_flag, g.status, 0xa00 | 1);
+        sfull_ph[buf] ^= 1u;
         if (!ok) break;
         tc_fence_after();
+        // this group's 64 of the block's 128 keys
+        const uint32_t x_col = tmem_base + (buf ? kColO : kColS) + (uint32_t)grp * 64 + lane_base;
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(x_col, r0);
+        tmem_ld_32x32(x_col + 32, r1);
+        tmem_ld_wait();
+        const int64_t key0 = (int64_t)j * 2 * kBkv + grp * 64;
 #pragma unroll
-        for (int c = 0; c < kBkv / 32; c++) {
-          uint32_t r[32];
-          tmem_ld_32x32(s_col + c * 32, r);
-          tmem_ld_wait();
-          const int64_t key0 = (int64_t)j * kBkv + c * 32;
-#pragma unroll
-          for (int t = 0; t < 32; t++)
-            if (key0 + t < g.Lk) m = fmaxf(m, __uint_as_float(r[t]));
+        for (int t = 0; t < 32; t++) {
+          if (key0 + t < g.Lk) m = fmaxf(m, __uint_as_float(r0[t]));
+          if (key0 + 32 + t < g.Lk) m = fmaxf(m, __uint_as_float(r1[t]));
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_s1free + 8 * grp);
+        if (lane == 0) mbar_arrive(bar_s1free + 8 * buf);
       }
       if (!ok) break;
       x_max[grp * kBq + row_in_tile] = m;
@@ -368,17 +391,17 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       m = fmaxf(x_max[row_in_tile], x_max[kBq + row_in_tile]);
       // ---- sweep 2: weights p = exp((s - m) * scale), rounded to tf32, written over the scores
       float l = 0.0f;
-      for (int j = grp; j < nblk; j += 2) {
-        ok = mbar_wait_warp(bar_sfull + 8 * grp, sfull_ph, abort_flag, g.status, 0xa00 | 3);
-        sfull_ph ^= 1u;
+      for (int j = 0; j < nblk; j++) {
+        const uint32_t buf = (uint32_t)(j & 1);
+        ok = mbar_wait_warp(bar_sfull + 8 * buf, sfull_ph[buf], abort_flag, g.status, 0xa00 | 3);
+        sfull_ph[buf] ^= 1u;
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < kBkv / 32; c++) {
+        {
           uint32_t r[32];
-          tmem_ld_32x32(s_col + c * 32, r);
+          tmem_ld_32x32(s_col + buf * kBkv, r);
           tmem_ld_wait();
-          const int64_t key0 = (int64_t)j * kBkv + c * 32;
+          const int64_t key0 = (int64_t)j * kBkv + grp * 32;
 #pragma unroll
           for (int t = 0; t < 32; t++) {
             float p = 0.0f;
@@ -390,12 +413,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             l += p;
             r[t] = __float_as_uint(p);
           }
-          tmem_st_32x32(s_col + c * 32, r);
+          tmem_st_32x32(s_col + buf * kBkv, r);
         }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pready + 8 * grp);
+        if (lane == 0) mbar_arrive(bar_pready + 8 * buf);
       }
       if (!ok) break;
       x_sum[grp * kBq + row_in_tile] = l;
@@ -572,8 +595,9 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   transpose_round_kernel<<<tgrid, 256, 0, s>>>(v, Lk, C, ld, vt);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  CUtensorMap t_khi, t_klo, t_vt, t_out;
-  if (!make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_2d_f32(&t_klo, k_lo, Lk, C, C, kBkv, why) ||
+  CUtensorMap t_khi128, t_khi, t_klo, t_vt, t_out;
+  if (!make_tmap_2d_f32(&t_khi128, k_hi, Lk, C, C, 2 * kBkv, why) ||
+      !make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_2d_f32(&t_klo, k_lo, Lk, C, C, kBkv, why) ||
       !make_tmap_2d_f32(&t_vt, vt, C, ld, ld, kHd, why) || !make_out_tmap(&t_out, out, Lq, C, why))
     return cudaErrorInvalidValue;
   SdpaArgs g;
@@ -583,7 +607,7 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   const int64_t items = ((Lq + kBq - 1) / kBq) * heads;
   count_launch();
   sdpa_tc_kernel<<<(unsigned)(items < sm_count ? items : sm_count), kNumThreads, kASmemBytes, s>>>(
-      t_khi, t_klo, t_vt, t_out, g);
+      t_khi128, t_khi, t_klo, t_vt, t_out, g);
   return cudaGetLastError();
 }
 
