@@ -6,9 +6,11 @@
 // largest value, which a plain tf32 (10-bit mantissa) score cannot hold in the tails: an error of
 // 2^-11 in q or k moves a score by ~1e-3 and exp() turns that into the same relative error of the
 // weight.  So the scores are computed with three tf32 products per fp32 product (q = hi + lo,
-// k = hi + lo; hi*hi + hi*lo + lo*hi), the weights are rounded to tf32 once (round to nearest;
-// the row sums use the rounded values, so numerator and denominator agree) and multiplied with
-// v rounded to tf32 once.
+// k = hi + lo; hi*hi + hi*lo + lo*hi).  The softmax weights and v are each split into two bf16
+// numbers (16 mantissa bits together) and P*V is three bf16 MMAs (hi*hi + hi*lo + lo*hi): twice
+// the rate of tf32 per MMA, the same shared-memory and tensor-memory footprint as one tf32 plane,
+// and an error of ~1e-5 instead of the 3..6e-4 a single tf32 rounding of P and V leaves.  The row
+// sums add the split weights, so numerator and denominator agree.
 //
 // Softmax without rescaling.  A first sweep over the keys finds each row's maximum from plain
 // tf32 scores (any value near the true maximum serves as the offset, as long as numerator and
@@ -29,6 +31,8 @@
 #include "tc_common.cuh"
 #include "tf32_split.cuh"
 
+#include <cuda_bf16.h>
+
 namespace sdq {
 namespace {
 using namespace tc;
@@ -47,7 +51,10 @@ constexpr uint32_t kColQhi = 0, kColQlo = 128, kColO = 256, kColS = 384;
 constexpr uint32_t kIdescS = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kBkv >> 3) << 17) |
                              ((uint32_t)(kBq >> 4) << 24);
 constexpr uint32_t kIdescO = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kHd >> 3) << 17) |
-                             ((uint32_t)(kBq >> 4) << 24);
+                             ((uint32_t)(kBq >> 4) << 24);  // tf32, N = 128 (sweep 1)
+// P*V: kind::f16 with bf16 inputs (format 1), fp32 accumulator, N = 128
+constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kHd >> 3) << 17) |
+                              ((uint32_t)(kBq >> 4) << 24);
 
 // D[tmem] (+)= A[tmem] * B[smem]^T, tf32: the A operand (row i in lane i, K along the columns)
 // is read from tensor memory.
@@ -57,6 +64,16 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, u
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same with bf16 operands (two K elements per 32-bit column of the A operand).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
       "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -89,7 +106,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi128,
                    const __grid_constant__ CUtensorMap tmap_k_hi,
                    const __grid_constant__ CUtensorMap tmap_k_lo,
-                   const __grid_constant__ CUtensorMap tmap_vt,
+                   const __grid_constant__ CUtensorMap tmap_vt_hi,
+                   const __grid_constant__ CUtensorMap tmap_vt_lo,
                    const __grid_constant__ CUtensorMap tmap_out, SdpaArgs g) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -148,7 +166,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     prefetch_tmap(&tmap_k_hi128);
     prefetch_tmap(&tmap_k_hi);
     prefetch_tmap(&tmap_k_lo);
-    prefetch_tmap(&tmap_vt);
+    prefetch_tmap(&tmap_vt_hi);
+    prefetch_tmap(&tmap_vt_lo);
     prefetch_tmap(&tmap_out);
   }
   if (warp == 1) {
@@ -179,7 +198,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             tma_load_2d_hint(st + i * 16384, &tmap_k_hi128, full, h * kHd + 32 * i, j * 2 * kBkv, keep);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
-        // sweep 2: k_hi, k_lo (boxes of 64 keys x 32 dims) and v^T (boxes of 128 dims x 32 keys)
+        // sweep 2: k_hi, k_lo (boxes of 64 keys x 32 dims) and the two bf16 planes of v^T (one box
+        // of 128 dims x 64 keys each)
         for (int j = 0; ok && j < nblk; j++) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 2);
           if (!ok) break;
@@ -190,8 +210,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             tma_load_2d_hint(st + i * 8192, &tmap_k_hi, full, h * kHd + 32 * i, j * kBkv, keep);
             tma_load_2d_hint(st + kKTile + i * 8192, &tmap_k_lo, full, h * kHd + 32 * i, j * kBkv, keep);
           }
-          for (int i = 0; i < 2; i++)
-            tma_load_2d_hint(st + 2 * kKTile + i * 16384, &tmap_vt, full, j * kBkv + 32 * i, h * kHd, keep);
+          tma_load_2d_hint(st + 2 * kKTile, &tmap_vt_hi, full, j * kBkv, h * kHd, keep);
+          tma_load_2d_hint(st + 2 * kKTile + 16384, &tmap_vt_lo, full, j * kBkv, h * kHd, keep);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -290,11 +310,17 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           pready_ph[buf] ^= 1u;
           tc_fence_after();
           const uint32_t vt = base + st_cur * kAStageBytes + 2 * kKTile;
+          const uint32_t pcol = tmem_base + kColS + buf * kBkv;
 #pragma unroll
-          for (int ks = 0; ks < kBkv / 8; ks++) {
-            const uint64_t vdesc = make_smem_desc(vt + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
-            umma_tf32_ts(tmem_base + kColO, tmem_base + kColS + buf * kBkv + ks * 8, vdesc, kIdescO,
-                         (uint32_t)((j | ks) != 0));
+          for (int ks = 0; ks < kBkv / 16; ks++) {
+            // 16 keys per kind::f16 instruction = 32 bytes of a v^T row: +2 in the address field.
+            // The weights of keys 16ks.. sit in 8 columns: hi at (ks>>1)*32 + (ks&1)*8, lo 16 further.
+            const uint64_t v_hi = make_smem_desc(vt) + (uint64_t)(ks * 2);
+            const uint64_t v_lo = make_smem_desc(vt + 16384) + (uint64_t)(ks * 2);
+            const uint32_t p_hi = pcol + (uint32_t)((ks >> 1) * 32 + (ks & 1) * 8);
+            umma_bf16_ts(tmem_base + kColO, p_hi + 16, v_hi, kIdescPV, (uint32_t)((j | ks) != 0));
+            umma_bf16_ts(tmem_base + kColO, p_hi, v_lo, kIdescPV, 1u);
+            umma_bf16_ts(tmem_base + kColO, p_hi, v_hi, kIdescPV, 1u);
           }
           umma_commit(bar_empty + 8 * st_cur);
           umma_commit(bar_pvdone + 8 * buf);
@@ -402,18 +428,27 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           tmem_ld_32x32(s_col + buf * kBkv, r);
           tmem_ld_wait();
           const int64_t key0 = (int64_t)j * kBkv + grp * 32;
+          // this group's 32 columns become: 16 columns of bf16 pairs p_hi, then 16 of p_lo
+          uint32_t w[32];
 #pragma unroll
-          for (int t = 0; t < 32; t++) {
-            float p = 0.0f;
-            if (key0 + t < g.Lk) {
-              const float e = __fmul_rn(__fsub_rn(__uint_as_float(r[t]), m), g.scale_log2e);
-              asm("ex2.approx.f32 %0, %1;" : "=f"(p) : "f"(e));
-              p = round_tf32(p);
+          for (int t = 0; t < 32; t += 2) {
+            float p[2] = {0.0f, 0.0f}, hi[2], lo[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+              if (key0 + t + u < g.Lk) {
+                const float e = __fmul_rn(__fsub_rn(__uint_as_float(r[t + u]), m), g.scale_log2e);
+                asm("ex2.approx.f32 %0, %1;" : "=f"(p[u]) : "f"(e));
+              }
+              hi[u] = __bfloat162float(__float2bfloat16_rn(p[u]));
+              lo[u] = __bfloat162float(__float2bfloat16_rn(__fsub_rn(p[u], hi[u])));
+              l += __fadd_rn(hi[u], lo[u]);
             }
-            l += p;
-            r[t] = __float_as_uint(p);
+            const __nv_bfloat162 ph = __floats2bfloat162_rn(hi[0], hi[1]);  // lower key in the low half
+            const __nv_bfloat162 pl = __floats2bfloat162_rn(lo[0], lo[1]);
+            w[t >> 1] = *reinterpret_cast<const uint32_t*>(&ph);
+            w[16 + (t >> 1)] = *reinterpret_cast<const uint32_t*>(&pl);
           }
-          tmem_st_32x32(s_col + buf * kBkv, r);
+          tmem_st_32x32(s_col + buf * kBkv, w);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -481,18 +516,27 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float* __restri
     split_tf32(x[i], hi[i], lo[i]);
 }
 
-// v [Lk, C] -> v^T [C, ld] rounded to tf32 (ld >= Lk, a multiple of 4; the padding is zero).
-__global__ void __launch_bounds__(256) transpose_round_kernel(const float* __restrict__ v, int64_t Lk,
-                                                              int64_t C, int64_t ld,
-                                                              float* __restrict__ vt) {
+// v [Lk, C] -> two bf16 planes of v^T, each [C, ld] (ld >= Lk, a multiple of 8; the padding is
+// zero): hi = bf16(v), lo = bf16(v - hi).
+__global__ void __launch_bounds__(256) transpose_split_bf16_kernel(const float* __restrict__ v, int64_t Lk,
+                                                                   int64_t C, int64_t ld,
+                                                                   __nv_bfloat16* __restrict__ vt_hi,
+                                                                   __nv_bfloat16* __restrict__ vt_lo) {
   __shared__ float tile[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t k0 = (int64_t)blockIdx.y * 32, c0 = (int64_t)blockIdx.x * 32;
   for (int r = ty; r < 32; r += 8)
     tile[r][tx] = (k0 + r < Lk && c0 + tx < C) ? v[(k0 + r) * C + c0 + tx] : 0.0f;
   __syncthreads();
-  for (int r = ty; r < 32; r += 8)
-    if (c0 + r < C && k0 + tx < ld) vt[(c0 + r) * ld + k0 + tx] = round_tf32(tile[tx][r]);
+  for (int r = ty; r < 32; r += 8) {
+    if (c0 + r < C && k0 + tx < ld) {
+      const float x = tile[tx][r];
+      const __nv_bfloat16 h = __float2bfloat16_rn(x);
+      const float rest = isfinite(x) ? __fsub_rn(x, __bfloat162float(h)) : 0.0f;
+      vt_hi[(c0 + r) * ld + k0 + tx] = h;
+      vt_lo[(c0 + r) * ld + k0 + tx] = __float2bfloat16_rn(rest);
+    }
+  }
 }
 
 // Any head_dim / alignment: one warp per (query row, head), exact fp32 on the CUDA cores, three
@@ -532,6 +576,22 @@ __global__ void __launch_bounds__(256) sdpa_simt_kernel(const float* __restrict_
   }
 }
 
+// v^T plane [C, ld] bf16, box = 128 rows x 64 keys (128 bytes), 128-byte swizzle.
+bool make_tmap_vt(CUtensorMap* map, const void* ptr, int64_t C, int64_t Lk, int64_t ld, std::string* why) {
+  cuuint64_t dims[2] = {(cuuint64_t)Lk, (cuuint64_t)C};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBkv, (cuuint32_t)kHd};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (why) *why = "cuTensorMapEncodeTiled(v^T) failed with CUresult " + std::to_string((int)r);
+    return false;
+  }
+  return true;
+}
+
 bool make_tmap_2d_f32(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t pitch_elems,
                       int box_rows, std::string* why) {
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -561,8 +621,8 @@ int sdpa_setup(std::string* why) {
 }
 
 size_t sdpa_scratch_bytes(int64_t Lk, int64_t C) {
-  const int64_t ld = (Lk + 3) / 4 * 4;
-  return (size_t)(2 * Lk * C + C * ld) * 4;
+  const int64_t ld = (Lk + 7) / 8 * 8;
+  return (size_t)(2 * Lk * C) * 4 + (size_t)(2 * C * ld) * 2;  // k_hi, k_lo fp32; v^T hi, lo bf16
 }
 
 cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk,
@@ -583,22 +643,24 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
     sdpa_simt_kernel<<<(unsigned)blocks, 256, 0, s>>>(q, k, v, Lq, Lk, C, heads, scale, out);
     return cudaGetLastError();
   }
-  const int64_t ld = (Lk + 3) / 4 * 4;
+  const int64_t ld = (Lk + 7) / 8 * 8;
   float* k_hi = scratch;
   float* k_lo = scratch + Lk * C;
-  float* vt = scratch + 2 * Lk * C;
+  __nv_bfloat16* vt_hi = reinterpret_cast<__nv_bfloat16*>(scratch + 2 * Lk * C);
+  __nv_bfloat16* vt_lo = vt_hi + C * ld;
   int64_t blocks = (Lk * C + 255) / 256;
   if (blocks > (int64_t)sm_count * 16) blocks = (int64_t)sm_count * 16;
   count_launch(2);
   split_planes_kernel<<<(unsigned)blocks, 256, 0, s>>>(k, Lk * C, k_hi, k_lo);
   dim3 tgrid((unsigned)((C + 31) / 32), (unsigned)((ld + 31) / 32));
-  transpose_round_kernel<<<tgrid, 256, 0, s>>>(v, Lk, C, ld, vt);
+  transpose_split_bf16_kernel<<<tgrid, 256, 0, s>>>(v, Lk, C, ld, vt_hi, vt_lo);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  CUtensorMap t_khi128, t_khi, t_klo, t_vt, t_out;
+  CUtensorMap t_khi128, t_khi, t_klo, t_vt_hi, t_vt_lo, t_out;
   if (!make_tmap_2d_f32(&t_khi128, k_hi, Lk, C, C, 2 * kBkv, why) ||
       !make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_2d_f32(&t_klo, k_lo, Lk, C, C, kBkv, why) ||
-      !make_tmap_2d_f32(&t_vt, vt, C, ld, ld, kHd, why) || !make_out_tmap(&t_out, out, Lq, C, why))
+      !make_tmap_vt(&t_vt_hi, vt_hi, C, Lk, ld, why) || !make_tmap_vt(&t_vt_lo, vt_lo, C, Lk, ld, why) ||
+      !make_out_tmap(&t_out, out, Lq, C, why))
     return cudaErrorInvalidValue;
   SdpaArgs g;
   g.q = q; g.out = out; g.Lq = Lq; g.Lk = Lk; g.C = C; g.heads = heads;
@@ -607,7 +669,7 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   const int64_t items = ((Lq + kBq - 1) / kBq) * heads;
   count_launch();
   sdpa_tc_kernel<<<(unsigned)(items < sm_count ? items : sm_count), kNumThreads, kASmemBytes, s>>>(
-      t_khi128, t_khi, t_klo, t_vt, t_out, g);
+      t_khi128, t_khi, t_klo, t_vt_hi, t_vt_lo, t_out, g);
   return cudaGetLastError();
 }
 

@@ -2,7 +2,9 @@
 
 The reference gates attention like its other fp32 kernels: max-abs error <= 1e-3 of the largest
 output.  The tensor-core path computes the scores with three tf32 products per fp32 product and
-rounds the softmax weights and v to tf32 once; measured errors are a few 1e-5.
+P*V with three bf16 products on two-term splits of the weights and of v; measured errors are
+~1e-5 at a few thousand keys and 1.3e-4 at 27280 keys (the tensor core's accumulator truncates,
+so the error grows with the length of the key range accumulated in it).
 """
 import os
 
@@ -31,7 +33,7 @@ def test_matches_reference_fixture(sdq, golden_dir):
     for simt in (False, True):
         got = sdq.sdpa_np(z["at_q"], z["at_k"], z["at_v"], 3, force_simt=simt)
         assert max_rel_err(got, z["at_out"]) < TOL, simt
-        assert max_rel_err(got, z["at_out"]) < (1e-5 if simt else 6e-4), simt
+        assert max_rel_err(got, z["at_out"]) < (1e-5 if simt else 1e-4), simt
 
 
 @pytest.mark.parametrize("Lq,Lk,heads", [
@@ -51,7 +53,7 @@ def test_against_float64(sdq, Lq, Lk, heads):
     want = attention64(q, k, v, heads)
     assert np.isfinite(got).all()
     assert max_rel_err(got, want) < TOL
-    assert max_rel_err(got, want) < 6e-4
+    assert max_rel_err(got, want) < 1e-4
 
 
 def test_peaked_and_shifted_scores(sdq):
