@@ -11,6 +11,7 @@
 #include <thread>
 
 #include "core/tensor.h"
+#include "model/blocks.h"
 #include "sdq.h"
 #include "serde/sdcpp.h"
 
@@ -144,6 +145,32 @@ void matmul(const Tensor& A, const Tensor& B, Tensor& C, const float* bias) {
   if (temporary) sdq_weight_release(w);
   if (rc != SDQ_OK) throw std::runtime_error(msg);
 }
+
+// ---- attention (reference src/model/blocks.cpp:113-199) ----
+namespace blk {
+void sdpa(const Tensor& q, const Tensor& k, const Tensor& v, int num_heads, Tensor& out, bool causal) {
+  if (causal) throw std::runtime_error("sd (B200): causal attention is not provided (the reference never uses it)");
+  const int64_t Lq = q.rows(), Lk = k.rows(), C = q.cols();
+  out = Tensor({Lq, C}, DType::F32);
+  if (Lq == 0 || C == 0) return;
+  ensure_device();
+  const size_t qb = (size_t)Lq * C * 4, kb = (size_t)Lk * C * 4;
+  float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+  int rc = sdq_malloc(reinterpret_cast<void**>(&dq), qb);
+  if (rc == SDQ_OK) rc = sdq_malloc(reinterpret_cast<void**>(&dout), qb);
+  if (rc == SDQ_OK && kb) rc = sdq_malloc(reinterpret_cast<void**>(&dk), kb);
+  if (rc == SDQ_OK && kb) rc = sdq_malloc(reinterpret_cast<void**>(&dv), kb);
+  if (rc == SDQ_OK) rc = sdq_memcpy_h2d(dq, q.data, qb, nullptr);
+  if (rc == SDQ_OK && kb) rc = sdq_memcpy_h2d(dk, k.data, kb, nullptr);
+  if (rc == SDQ_OK && kb) rc = sdq_memcpy_h2d(dv, v.data, kb, nullptr);
+  if (rc == SDQ_OK) rc = sdq_sdpa(dq, dk, dv, Lq, Lk, C, num_heads, dout, 0, nullptr);
+  if (rc == SDQ_OK) rc = sdq_memcpy_d2h(out.data, dout, qb, nullptr);
+  if (rc == SDQ_OK) rc = sdq_stream_sync(nullptr);
+  const std::string msg = rc != SDQ_OK ? sdq_last_error() : "";
+  sdq_free(dq); sdq_free(dk); sdq_free(dv); sdq_free(dout);
+  if (rc != SDQ_OK) throw std::runtime_error(msg);
+}
+}  // namespace blk
 
 // reference src/core/tensor.cpp:63-78
 void quantize_rowwise(const Tensor& W, Tensor& Wq, Tensor& scale) {

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "core/tensor.h"
+#include "model/blocks.h"
 #include "serde/sdcpp.h"
 
 using namespace sd;
@@ -140,6 +141,38 @@ static void test_matmul(int64_t M, int64_t K, int64_t N, bool with_bias) {
   CHECK(err <= 1e-3 * (mx > 0 ? mx : 1));
 }
 
+static void test_sdpa(int64_t Lq, int64_t Lk, int heads) {
+  // reference tests/test_blocks.cpp: attention vs a naive softmax(q k^T / sqrt(hd)) v
+  const int64_t hd = 128, C = heads * hd;
+  Tensor q({Lq, C}, DType::F32), k({Lk, C}, DType::F32), v({Lk, C}, DType::F32), out;
+  fill_uniform(q, 31);
+  fill_uniform(k, 32);
+  fill_uniform(v, 33);
+  blk::sdpa(q, k, v, heads, out);
+  CHECK(out.rows() == Lq && out.cols() == C && out.owning);
+  double err = 0, mx = 0;
+  std::vector<double> s((size_t)Lk);
+  for (int h = 0; h < heads; h++)
+    for (int64_t i = 0; i < Lq; i++) {
+      double m = -1e300, sum = 0;
+      for (int64_t j = 0; j < Lk; j++) {
+        double d = 0;
+        for (int64_t c = 0; c < hd; c++) d += (double)q.ptr<float>()[i * C + h * hd + c] * k.ptr<float>()[j * C + h * hd + c];
+        s[j] = d / std::sqrt((double)hd);
+        m = std::max(m, s[j]);
+      }
+      for (int64_t j = 0; j < Lk; j++) { s[j] = std::exp(s[j] - m); sum += s[j]; }
+      for (int64_t c = 0; c < hd; c++) {
+        double o = 0;
+        for (int64_t j = 0; j < Lk; j++) o += s[j] / sum * v.ptr<float>()[j * C + h * hd + c];
+        err = std::max(err, std::fabs(o - out.ptr<float>()[i * C + h * hd + c]));
+        mx = std::max(mx, std::fabs(o));
+      }
+    }
+  std::printf("sdpa %lldx%lld heads %d max-abs err / max-abs %.2e\n", (long long)Lq, (long long)Lk, heads, err / mx);
+  CHECK(err <= 1e-3 * mx);
+}
+
 static void test_quantize_rowwise() {
   // reference tests/test_core.cpp:120-132: dequantization error below one scale unit
   Tensor W({37, 513}, DType::F32), Wq, sc;
@@ -194,6 +227,8 @@ int main(int argc, char** argv) {
     test_matmul(17, 31, 13, false);
     test_matmul(64, 1024, 512, true);
     test_matmul(300, 140, 3072, true);
+    test_sdpa(70, 130, 2);
+    test_sdpa(300, 257, 1);
     test_pack(golden);
   }
   if (g_fail) std::printf("test_dropin: %d FAILED\n", g_fail);

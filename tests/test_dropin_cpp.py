@@ -1,4 +1,5 @@
-"""The C++ drop-in (libsd_b200.so: sd::qgemm, sd::quantize_rowwise, sd::load_sdcpp, Tensor)
+"""The C++ drop-in (libsd_b200.so: sd::qgemm, sd::quantize_rowwise, sd::load_sdcpp, sd::matmul,
+sd::blk::sdpa, Tensor)
 exercised by a standalone C++ test binary written like the reference's own tests."""
 import os
 import subprocess
@@ -59,5 +60,7 @@ def test_dropin_exports_reference_symbols():
     for sym in ("sd::qgemm(sd::Tensor const&, sd::Tensor const&, sd::Tensor const&, sd::Tensor&)",
                 "sd::quantize_rowwise(sd::Tensor const&, sd::Tensor&, sd::Tensor&)",
                 "sd::load_sdcpp(", "sd::parallel_for(", "sd::set_nthreads(int)", "sd::nthreads()",
-                "sd::to_bf16(sd::Tensor const&, sd::Tensor&)", "sd::Tensor::reshape("):
+                "sd::to_bf16(sd::Tensor const&, sd::Tensor&)", "sd::Tensor::reshape(",
+                "sd::matmul(sd::Tensor const&, sd::Tensor const&, sd::Tensor&, float const*)",
+                "sd::blk::sdpa(sd::Tensor const&, sd::Tensor const&, sd::Tensor const&, int, sd::Tensor&, bool)"):
         assert sym in out, sym
