@@ -44,8 +44,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=M_720P, help="token rows per GPU")
-    ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch", "libcompare", "block"])
+    ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch", "libcompare", "block", "fp32"])
     ap.add_argument("--blocks", type=int, default=30, help="branch workload: number of DiT blocks")
+    ap.add_argument("--heads", type=int, default=24, help="fp32 workload: attention heads of 128")
     ap.add_argument("--pack-file-blocks", type=int, default=0,
                     help="branch workload: also write this many blocks as a .sdcpp file and time the load")
     ap.add_argument("--verify-blocks", type=int, default=1, help="branch workload: blocks whose packed bytes are compared with the CPU packer")
@@ -883,9 +884,88 @@ def run_block(args):
     return 0
 
 
+def run_fp32(args):
+    """The two fp32 kernels beside the int8 linears of a DiT block: exact-softmax attention
+    (blk::sdpa) over --rows x --rows tokens with --heads heads of 128, and the fp32 sd::matmul
+    at --rows x 3072 x 3072.  Times both with CUDA events, checks a sample of each result
+    against float64, and times torch's fp32 attention / matmul next to them.  One GPU; one JSON
+    line (value = attention TFLOP/s of algorithmic work, 4 * Lq * Lk * C)."""
+    import ctypes as C
+
+    import torch
+
+    import __graft_entry__ as ge
+
+    torch.cuda.set_device(0)
+    pkg = ge.load_package()
+    s = pkg.Sdq(0)
+    lib = s.lib
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    L, H = args.rows, args.heads
+    Cc = H * 128
+
+    def p(t):
+        return C.c_void_p(t.data_ptr())
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+    q, k, v = [torch.randn(L, Cc, device=dev, generator=g) for _ in range(3)]
+    out = torch.empty(L, Cc, device=dev)
+    n0 = s.launches()
+    t_att = timed(lambda: s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), 0, sp)))
+    att_launches = (s.launches() - n0) // (args.steps + max(args.warmup, 1))
+    rows = min(L, 1024)                                   # float64 check: two heads, the first rows
+    q64, k64, v64 = [x.view(L, H, 128).transpose(0, 1)[:2].double() for x in (q, k, v)]
+    ref = torch.softmax(q64[:, :rows] @ k64.transpose(1, 2) / 128 ** 0.5, -1) @ v64
+    err_att = float((out.view(L, H, 128).transpose(0, 1)[:2, :rows].double() - ref).abs().max() / ref.abs().max())
+    torch.backends.cuda.matmul.allow_tf32 = False
+    tq, tk, tv = [x.view(1, L, H, 128).transpose(1, 2) for x in (q, k, v)]
+    t_att_torch = timed(lambda: torch.nn.functional.scaled_dot_product_attention(tq, tk, tv))
+    del q64, k64, v64, ref
+    M, K, N = L, D_MODEL, D_MODEL
+    A = torch.randn(M, K, device=dev, generator=g)
+    W = torch.randn(K, N, device=dev, generator=g) * 0.05
+    o2 = torch.empty(M, N, device=dev)
+    h = C.c_uint64(0)
+    s._ck(lib.sdq_fweight_upload(p(W), K, N, 0, C.byref(h)))
+    t_mm = timed(lambda: s._ck(lib.sdq_fmatmul(h.value, p(A), M, p(o2), None, 0, sp)))
+    r64 = A[:rows].double() @ W.double()
+    err_mm = float((o2[:rows].double() - r64).abs().max() / r64.abs().max())
+    t_mm_torch = timed(lambda: torch.matmul(A, W, out=o2))
+    att_flop, mm_flop = 4.0 * L * L * Cc, 2.0 * M * K * N
+    pk, pk_kind = peaks()
+    bf16 = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    print(json.dumps({"metric": "fp32_attention_throughput", "value": att_flop / (t_att * 1e-3) / 1e12,
+                      "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
+                      "ms_per_step": t_att, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "tf32x3 scores, bf16x3 P*V, f32 accumulate", "data": "synthetic",
+                      "config": {"workload": "dit_attention_and_fp32_matmul", "tokens": L, "heads": H,
+                                 "l2": "q, k, v %d MB each" % (L * Cc * 4 // 1000000)},
+                      "gpu_launches": att_launches * args.steps,
+                      "attention": {"ms": t_att, "tflops": att_flop / (t_att * 1e-3) / 1e12,
+                                    "max_err_over_max_abs_vs_float64": err_att, "torch_fp32_sdpa_ms": t_att_torch,
+                                    "frac_of_measured_bf16_peak": att_flop / (t_att * 1e-3) / 1e12 / bf16, "of": pk_kind},
+                      "matmul": {"shape": [M, K, N], "ms": t_mm, "tflops": mm_flop / (t_mm * 1e-3) / 1e12,
+                                 "max_err_over_max_abs_vs_float64": err_mm, "torch_fp32_matmul_ms": t_mm_torch}}))
+    return 0
+
+
 if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         sys.exit(run_reference(a))
     sys.exit({"sweep": run_sweep, "branch": run_branch, "libcompare": run_libcompare,
-              "block": run_block}.get(a.workload, run_b200)(a))
+              "block": run_block, "fp32": run_fp32}.get(a.workload, run_b200)(a))
