@@ -5,8 +5,10 @@
 // Precision.  The reference is fp32 throughout and its outputs are compared at 1e-3 of the
 // largest value, which a plain tf32 (10-bit mantissa) score cannot hold in the tails: an error of
 // 2^-11 in q or k moves a score by ~1e-3 and exp() turns that into the same relative error of the
-// weight.  So the scores are computed with three tf32 products per fp32 product (q = hi + lo,
-// k = hi + lo; hi*hi + hi*lo + lo*hi).  The softmax weights and v are each split into two bf16
+// weight.  So the scores are computed with three products per fp32 product (q = hi + lo,
+// k = hi + lo with hi = tf32(x); hi*hi + lo*hi + hi*lo): the large term as tf32 MMAs, the two
+// small cross terms (2^-11 of the product, so 8 mantissa bits are plenty) as bf16 MMAs, which
+// take 16 instead of 8 elements of the head dimension per instruction.  The softmax weights and v are each split into two bf16
 // numbers (16 mantissa bits together) and P*V is three bf16 MMAs (hi*hi + hi*lo + lo*hi): twice
 // the rate of tf32 per MMA, the same shared-memory and tensor-memory footprint as one tf32 plane,
 // and an error of ~1e-5 instead of the 3..6e-4 a single tf32 rounding of P and V leaves.  The row
@@ -19,15 +21,16 @@
 //
 // One CTA per (128 query rows, head), persistent over these work items; 320 threads:
 //   warp 0 lane 0 : TMA producer.  128 keys of k_hi per stage in sweep 1; per 64-key block
-//                   k_hi, k_lo and v^T in sweep 2; 128-byte-swizzled boxes, two-stage ring.
+//                   k_hi, the bf16 planes of k and of v^T in sweep 2; 128-byte-swizzled boxes,
+//                   two-stage ring.
 //   warp 1 lane 0 : MMA issuer.  S = Q K^T with Q (both tf32 planes) as the A operand in TENSOR
 //                   MEMORY, K from shared memory; O += P V with P in tensor memory (written in
 //                   place over S by the softmax warps), V^T from shared memory.
 //   warps 2..5    : softmax group A (one thread per query row): the first 32 keys of every block.
 //   warps 6..9    : softmax group B: the other 32 keys.  Both groups finish the tile together:
 //                   O / row sum -> staged boxes -> bulk tensor stores.
-// Tensor memory (512 columns): Q_hi 0..127, Q_lo 128..255, O 256..383, S/P buffers 384..447 and
-// 448..511.  Every mbarrier wait is bounded like the GEMM kernels'.
+// Tensor memory (512 columns): Q_hi (tf32) 0..127, bf16(Q_lo) 128..191, bf16(Q_hi) 192..255,
+// O 256..383, S/P buffers 384..447 and 448..511.  Every mbarrier wait is bounded like the GEMM kernels'.
 #include "tc_common.cuh"
 #include "tf32_split.cuh"
 
@@ -47,11 +50,15 @@ constexpr int kAStages = 2;
 constexpr int kABookBytes = 2304;    // row maxima and sums of both groups (2 KiB) + barriers
 constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte boundary
 constexpr int kASmemBytes = kAStages * kAStageBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
-constexpr uint32_t kColQhi = 0, kColQlo = 128, kColO = 256, kColS = 384;
+constexpr uint32_t kColQhi = 0, kColQloB = 128, kColQhiB = 192, kColO = 256, kColS = 384;
+constexpr int kKbTile = kBkv * kHd * 2;         // 16 KiB: one bf16 plane of a key block
 constexpr uint32_t kIdescS = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kBkv >> 3) << 17) |
                              ((uint32_t)(kBq >> 4) << 24);
 constexpr uint32_t kIdescO = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kHd >> 3) << 17) |
                              ((uint32_t)(kBq >> 4) << 24);  // tf32, N = 128 (sweep 1)
+// cross terms of the scores: kind::f16 with bf16 inputs (format 1), N = 64
+constexpr uint32_t kIdescSb = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBkv >> 3) << 17) |
+                              ((uint32_t)(kBq >> 4) << 24);
 // P*V: kind::f16 with bf16 inputs (format 1), fp32 accumulator, N = 128
 constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kHd >> 3) << 17) |
                               ((uint32_t)(kBq >> 4) << 24);
@@ -105,7 +112,8 @@ struct SdpaArgs {
 __global__ void __launch_bounds__(kNumThreads, 1)
     sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi128,
                    const __grid_constant__ CUtensorMap tmap_k_hi,
-                   const __grid_constant__ CUtensorMap tmap_k_lo,
+                   const __grid_constant__ CUtensorMap tmap_k_hib,
+                   const __grid_constant__ CUtensorMap tmap_k_lob,
                    const __grid_constant__ CUtensorMap tmap_vt_hi,
                    const __grid_constant__ CUtensorMap tmap_vt_lo,
                    const __grid_constant__ CUtensorMap tmap_out, SdpaArgs g) {
@@ -165,7 +173,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     prefetch_tmap(&tmap_k_hi128);
     prefetch_tmap(&tmap_k_hi);
-    prefetch_tmap(&tmap_k_lo);
+    prefetch_tmap(&tmap_k_hib);
+    prefetch_tmap(&tmap_k_lob);
     prefetch_tmap(&tmap_vt_hi);
     prefetch_tmap(&tmap_vt_lo);
     prefetch_tmap(&tmap_out);
@@ -198,7 +207,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             tma_load_2d_hint(st + i * 16384, &tmap_k_hi128, full, h * kHd + 32 * i, j * 2 * kBkv, keep);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
-        // sweep 2: k_hi, k_lo (boxes of 64 keys x 32 dims) and the two bf16 planes of v^T (one box
+        // sweep 2: k_hi (boxes of 64 keys x 32 dims), bf16(k_hi) and bf16(k_lo) (boxes of 64 keys x
+        // 64 dims) and the two bf16 planes of v^T (one box
         // of 128 dims x 64 keys each)
         for (int j = 0; ok && j < nblk; j++) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 2);
@@ -206,9 +216,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           const uint32_t full = bar_full + 8 * stage;
           const uint32_t st = base + stage * kAStageBytes;
           mbar_expect_tx(full, kAStageBytes);
-          for (int i = 0; i < 4; i++) {
+          for (int i = 0; i < 4; i++)
             tma_load_2d_hint(st + i * 8192, &tmap_k_hi, full, h * kHd + 32 * i, j * kBkv, keep);
-            tma_load_2d_hint(st + kKTile + i * 8192, &tmap_k_lo, full, h * kHd + 32 * i, j * kBkv, keep);
+          for (int i = 0; i < 2; i++) {  // bf16 planes: boxes of 64 keys x 64 dims
+            tma_load_2d_hint(st + kKTile + i * 8192, &tmap_k_hib, full, h * kHd + 64 * i, j * kBkv, keep);
+            tma_load_2d_hint(st + kKTile + kKbTile + i * 8192, &tmap_k_lob, full, h * kHd + 64 * i, j * kBkv, keep);
           }
           tma_load_2d_hint(st + 2 * kKTile, &tmap_vt_hi, full, j * kBkv, h * kHd, keep);
           tma_load_2d_hint(st + 2 * kKTile + 16384, &tmap_vt_lo, full, j * kBkv, h * kHd, keep);
@@ -225,22 +237,23 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t pready_ph[2] = {0, 0};
       uint32_t q_ph = 0, m_ph = 0, ofree_ph = 0;
       bool ok = true;
-      // scores of block j from the operands in `st`: hi*hi only (sweep 1) or the three products
-      auto issue_scores = [&](uint32_t st, uint32_t buf, bool accurate) {
+      // scores of block j from the operands in `st`: the two small cross terms first (bf16, 16
+      // dims per instruction), then the large term (tf32, 8 dims per instruction)
+      auto issue_scores = [&](uint32_t st, uint32_t buf) {
         const uint32_t d = tmem_base + kColS + buf * kBkv;
 #pragma unroll
-        for (int ks = 0; ks < kHd / 8; ks++) {
+        for (int ks = 0; ks < kHd / 16; ks++) {
           const uint32_t off = (uint32_t)((ks >> 2) * 8192);
           const uint64_t adv = (uint64_t)((ks & 3) * 2);
-          const uint64_t k_hi = make_smem_desc(st + off) + adv;
-          if (accurate) {
-            const uint64_t k_lo = make_smem_desc(st + kKTile + off) + adv;
-            umma_tf32_ts(d, tmem_base + kColQlo + ks * 8, k_hi, kIdescS, (uint32_t)(ks != 0));
-            umma_tf32_ts(d, tmem_base + kColQhi + ks * 8, k_lo, kIdescS, 1u);
-            umma_tf32_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescS, 1u);
-          } else {
-            umma_tf32_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescS, (uint32_t)(ks != 0));
-          }
+          const uint64_t k_hib = make_smem_desc(st + kKTile + off) + adv;
+          const uint64_t k_lob = make_smem_desc(st + kKTile + kKbTile + off) + adv;
+          umma_bf16_ts(d, tmem_base + kColQloB + ks * 8, k_hib, kIdescSb, (uint32_t)(ks != 0));
+          umma_bf16_ts(d, tmem_base + kColQhiB + ks * 8, k_lob, kIdescSb, 1u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < kHd / 8; ks++) {
+          const uint64_t k_hi = make_smem_desc(st + (uint32_t)((ks >> 2) * 8192)) + (uint64_t)((ks & 3) * 2);
+          umma_tf32_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescS, 1u);
         }
       };
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
@@ -286,7 +299,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         ok = mbar_wait(bar_full + 8 * st_cur, ph_cur, abort_flag, g.status, 0x900 | 6);
         if (!ok) break;
         tc_fence_after();
-        issue_scores(base + st_cur * kAStageBytes, 0, true);
+        issue_scores(base + st_cur * kAStageBytes, 0);
         umma_commit(bar_sfull + 0);
         for (int j = 0; j < nblk; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
@@ -302,7 +315,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
               pv_ph[nbuf] ^= 1u;
             }
             tc_fence_after();
-            issue_scores(base + st_next * kAStageBytes, nbuf, true);
+            issue_scores(base + st_next * kAStageBytes, nbuf);
             umma_commit(bar_sfull + 8 * nbuf);
           }
           ok = mbar_wait(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
@@ -357,26 +370,38 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const int64_t q0 = (int64_t)qt * kBq;
       const int64_t row = q0 + row_in_tile;
       if (grp == 0) {
-        // this thread's query row -> two tf32 planes in tensor memory (zeros past Lq)
+        // this thread's query row -> tensor memory (zeros past Lq): the tf32 plane q_hi, and
+        // bf16(q - q_hi) and bf16(q_hi) for the cross terms, two elements per column
         const float* qrow = g.q + row * g.C + (int64_t)h * kHd;
 #pragma unroll 1
-        for (int c = 0; c < kHd / 32; c++) {
-          uint32_t hi[32], lo[32];
+        for (int c = 0; c < kHd / 64; c++) {
+          uint32_t lob[32], hib[32];
+#pragma unroll 1
+          for (int half_c = 0; half_c < 2; half_c++) {
+            uint32_t hi[32];
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (row < g.Lq) v = *reinterpret_cast<const float4*>(qrow + c * 32 + j);
-            const float xs[4] = {v.x, v.y, v.z, v.w};
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (row < g.Lq) v = *reinterpret_cast<const float4*>(qrow + c * 64 + half_c * 32 + j);
+              const float xs[4] = {v.x, v.y, v.z, v.w};
+              float a[4], b[4];
 #pragma unroll
-            for (int t = 0; t < 4; t++) {
-              float a, b;
-              split_tf32(xs[t], a, b);
-              hi[j + t] = __float_as_uint(a);
-              lo[j + t] = __float_as_uint(b);
+              for (int t = 0; t < 4; t++) {
+                split_tf32(xs[t], a[t], b[t]);
+                hi[j + t] = __float_as_uint(a[t]);
+              }
+#pragma unroll
+              for (int t = 0; t < 4; t += 2) {
+                const __nv_bfloat162 pl = __floats2bfloat162_rn(b[t], b[t + 1]);  // lower dim in the low half
+                const __nv_bfloat162 ph = __floats2bfloat162_rn(a[t], a[t + 1]);
+                lob[half_c * 16 + ((j + t) >> 1)] = *reinterpret_cast<const uint32_t*>(&pl);
+                hib[half_c * 16 + ((j + t) >> 1)] = *reinterpret_cast<const uint32_t*>(&ph);
+              }
             }
+            tmem_st_32x32(tmem_base + kColQhi + c * 64 + half_c * 32 + lane_base, hi);
           }
-          tmem_st_32x32(tmem_base + kColQhi + c * 32 + lane_base, hi);
-          tmem_st_32x32(tmem_base + kColQlo + c * 32 + lane_base, lo);
+          tmem_st_32x32(tmem_base + kColQloB + c * 32 + lane_base, lob);
+          tmem_st_32x32(tmem_base + kColQhiB + c * 32 + lane_base, hib);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -509,11 +534,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   }
 }
 
+// k -> the tf32 plane k_hi and, for the cross terms, bf16(k_hi) and bf16(k - k_hi).
 __global__ void __launch_bounds__(256) split_planes_kernel(const float* __restrict__ x, int64_t n,
                                                            float* __restrict__ hi,
-                                                           float* __restrict__ lo) {
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256)
-    split_tf32(x[i], hi[i], lo[i]);
+                                                           __nv_bfloat16* __restrict__ hib,
+                                                           __nv_bfloat16* __restrict__ lob) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    float a, b;
+    split_tf32(x[i], a, b);
+    hi[i] = a;
+    hib[i] = __float2bfloat16_rn(a);
+    lob[i] = __float2bfloat16_rn(b);
+  }
 }
 
 // v [Lk, C] -> two bf16 planes of v^T, each [C, ld] (ld >= Lk, a multiple of 8; the padding is
@@ -592,6 +624,22 @@ bool make_tmap_vt(CUtensorMap* map, const void* ptr, int64_t C, int64_t Lk, int6
   return true;
 }
 
+// bf16 plane of k [Lk, C], box = 64 keys x 64 dims (128 bytes), 128-byte swizzle.
+bool make_tmap_kb(CUtensorMap* map, const void* ptr, int64_t Lk, int64_t C, std::string* why) {
+  cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)Lk};
+  cuuint64_t strides[1] = {(cuuint64_t)C * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)kBkv};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (why) *why = "cuTensorMapEncodeTiled(bf16 k plane) failed with CUresult " + std::to_string((int)r);
+    return false;
+  }
+  return true;
+}
+
 bool make_tmap_2d_f32(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t pitch_elems,
                       int box_rows, std::string* why) {
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -622,7 +670,7 @@ int sdpa_setup(std::string* why) {
 
 size_t sdpa_scratch_bytes(int64_t Lk, int64_t C) {
   const int64_t ld = (Lk + 7) / 8 * 8;
-  return (size_t)(2 * Lk * C) * 4 + (size_t)(2 * C * ld) * 2;  // k_hi, k_lo fp32; v^T hi, lo bf16
+  return (size_t)(Lk * C) * 4 + (size_t)(2 * Lk * C + 2 * C * ld) * 2;  // k_hi fp32; k and v^T hi, lo bf16
 }
 
 cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk,
@@ -645,20 +693,22 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   }
   const int64_t ld = (Lk + 7) / 8 * 8;
   float* k_hi = scratch;
-  float* k_lo = scratch + Lk * C;
-  __nv_bfloat16* vt_hi = reinterpret_cast<__nv_bfloat16*>(scratch + 2 * Lk * C);
+  __nv_bfloat16* k_hib = reinterpret_cast<__nv_bfloat16*>(scratch + Lk * C);
+  __nv_bfloat16* k_lob = k_hib + Lk * C;
+  __nv_bfloat16* vt_hi = k_lob + Lk * C;
   __nv_bfloat16* vt_lo = vt_hi + C * ld;
   int64_t blocks = (Lk * C + 255) / 256;
   if (blocks > (int64_t)sm_count * 16) blocks = (int64_t)sm_count * 16;
   count_launch(2);
-  split_planes_kernel<<<(unsigned)blocks, 256, 0, s>>>(k, Lk * C, k_hi, k_lo);
+  split_planes_kernel<<<(unsigned)blocks, 256, 0, s>>>(k, Lk * C, k_hi, k_hib, k_lob);
   dim3 tgrid((unsigned)((C + 31) / 32), (unsigned)((ld + 31) / 32));
   transpose_split_bf16_kernel<<<tgrid, 256, 0, s>>>(v, Lk, C, ld, vt_hi, vt_lo);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  CUtensorMap t_khi128, t_khi, t_klo, t_vt_hi, t_vt_lo, t_out;
+  CUtensorMap t_khi128, t_khi, t_khib, t_klob, t_vt_hi, t_vt_lo, t_out;
   if (!make_tmap_2d_f32(&t_khi128, k_hi, Lk, C, C, 2 * kBkv, why) ||
-      !make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_2d_f32(&t_klo, k_lo, Lk, C, C, kBkv, why) ||
+      !make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_kb(&t_khib, k_hib, Lk, C, why) ||
+      !make_tmap_kb(&t_klob, k_lob, Lk, C, why) ||
       !make_tmap_vt(&t_vt_hi, vt_hi, C, Lk, ld, why) || !make_tmap_vt(&t_vt_lo, vt_lo, C, Lk, ld, why) ||
       !make_out_tmap(&t_out, out, Lq, C, why))
     return cudaErrorInvalidValue;
@@ -669,7 +719,7 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   const int64_t items = ((Lq + kBq - 1) / kBq) * heads;
   count_launch();
   sdpa_tc_kernel<<<(unsigned)(items < sm_count ? items : sm_count), kNumThreads, kASmemBytes, s>>>(
-      t_khi128, t_khi, t_klo, t_vt_hi, t_vt_lo, t_out, g);
+      t_khi128, t_khi, t_khib, t_klob, t_vt_hi, t_vt_lo, t_out, g);
   return cudaGetLastError();
 }
 
