@@ -20,7 +20,9 @@
 // and accumulates P*V in tensor memory for the whole key range.  No accumulator is ever rescaled.
 //
 // One CTA per (128 query rows, head), persistent over these work items; 320 threads:
-//   warp 0 lane 0 : TMA producer.  128 keys of k_hi per stage in sweep 1; per 64-key block
+//   warp 10 lane 0: TMA producer of v^T (its own two-stage ring, released by the P*V MMAs, so
+//                   the k ring -- released as soon as a block's scores are done -- runs ahead).
+//   warp 0 lane 0 : TMA producer of k.  128 keys of k_hi per stage in sweep 1; per 64-key block
 //                   k_hi, the bf16 planes of k and of v^T in sweep 2; 128-byte-swizzled boxes,
 //                   two-stage ring.
 //   warp 1 lane 0 : MMA issuer.  S = Q K^T with Q (both tf32 planes) as the A operand in TENSOR
@@ -45,8 +47,10 @@ constexpr int kBq = 128;            // query rows per work item
 constexpr int kBkv = 64;            // keys per block
 constexpr int kKTile = kBkv * kHd * 4;          // 32 KiB: one tf32 plane of a key block
 constexpr int kVTile = kHd * kBkv * 4;          // 32 KiB: v^T of a key block
-constexpr int kAStageBytes = 2 * kKTile + kVTile;
-constexpr int kAStages = 2;
+constexpr int kKStageBytes = 2 * kKTile;   // k_hi (tf32) + bf16(k_hi) + bf16(k_lo); sweep 1: 128 keys of k_hi
+constexpr int kAStages = 2;                // per ring
+constexpr int kAStageBytes = kKStageBytes + kVTile;  // both rings, one stage each
+constexpr int kAThreads = kNumThreads + 32;  // + one warp: the v^T producer
 constexpr int kABookBytes = 2304;    // row maxima and sums of both groups (2 KiB) + barriers
 constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte boundary
 constexpr int kASmemBytes = kAStages * kAStageBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
@@ -109,7 +113,7 @@ struct SdpaArgs {
   int* status;
 };
 
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kAThreads, 1)
     sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi128,
                    const __grid_constant__ CUtensorMap tmap_k_hi,
                    const __grid_constant__ CUtensorMap tmap_k_hib,
@@ -128,8 +132,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   float* x_sum = reinterpret_cast<float*>(book + 1024);   // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(book + 2048);
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t bar_full = bar0;               // [2]  TMA bytes landed
-  const uint32_t bar_empty = bar0 + 16;         // [2]  stage read by its last MMA
+  const uint32_t bar_full = bar0;               // [2]  k ring: TMA bytes landed
+  const uint32_t bar_empty = bar0 + 16;         // [2]  k ring: stage read by its last MMA
   const uint32_t bar_sfull = bar0 + 32;         // [2]  scores of a block complete
   const uint32_t bar_s1free = bar0 + 48;        // [2]  sweep 1: scores read by the softmax group
   const uint32_t bar_pready = bar0 + 64;        // [2]  sweep 2: weights written over the scores
@@ -139,7 +143,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const uint32_t bar_lready = bar0 + 112;       // both groups published their row sums
   const uint32_t bar_ofull = bar0 + 120;        // every MMA of the work item complete
   const uint32_t bar_ofree = bar0 + 128;        // O read out: the next item may overwrite it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  const uint32_t bar_vfull = bar0 + 136;        // [2]  v^T ring
+  const uint32_t bar_vempty = bar0 + 152;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (base - raw > (uint32_t)kAAlignSlack) {
@@ -162,6 +168,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       mbar_init(bar_s1free + 8 * i, 8);
       mbar_init(bar_pready + 8 * i, 8);
       mbar_init(bar_pvdone + 8 * i, 1);
+      mbar_init(bar_vfull + 8 * i, 1);
+      mbar_init(bar_vempty + 8 * i, 1);
     }
     mbar_init(bar_qready, 4);
     mbar_init(bar_mready, 8);
@@ -190,7 +198,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   if (warp == 0) {
     if (lane == 0) {
-      // ------------------------------------------------ TMA producer
+      // ------------------------------------------------ TMA producer of k
       const uint64_t keep = policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
@@ -201,29 +209,47 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 1);
           if (!ok) break;
           const uint32_t full = bar_full + 8 * stage;
-          const uint32_t st = base + stage * kAStageBytes;
-          mbar_expect_tx(full, 2 * kKTile);
+          const uint32_t st = base + stage * kKStageBytes;
+          mbar_expect_tx(full, kKStageBytes);
           for (int i = 0; i < 4; i++)
             tma_load_2d_hint(st + i * 16384, &tmap_k_hi128, full, h * kHd + 32 * i, j * 2 * kBkv, keep);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
-        // sweep 2: k_hi (boxes of 64 keys x 32 dims), bf16(k_hi) and bf16(k_lo) (boxes of 64 keys x
-        // 64 dims) and the two bf16 planes of v^T (one box
-        // of 128 dims x 64 keys each)
+        // sweep 2: k_hi (boxes of 64 keys x 32 dims), bf16(k_hi) and bf16(k_lo) (boxes of 64 keys
+        // x 64 dims)
         for (int j = 0; ok && j < nblk; j++) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 2);
           if (!ok) break;
           const uint32_t full = bar_full + 8 * stage;
-          const uint32_t st = base + stage * kAStageBytes;
-          mbar_expect_tx(full, kAStageBytes);
+          const uint32_t st = base + stage * kKStageBytes;
+          mbar_expect_tx(full, kKStageBytes);
           for (int i = 0; i < 4; i++)
             tma_load_2d_hint(st + i * 8192, &tmap_k_hi, full, h * kHd + 32 * i, j * kBkv, keep);
-          for (int i = 0; i < 2; i++) {  // bf16 planes: boxes of 64 keys x 64 dims
+          for (int i = 0; i < 2; i++) {
             tma_load_2d_hint(st + kKTile + i * 8192, &tmap_k_hib, full, h * kHd + 64 * i, j * kBkv, keep);
             tma_load_2d_hint(st + kKTile + kKbTile + i * 8192, &tmap_k_lob, full, h * kHd + 64 * i, j * kBkv, keep);
           }
-          tma_load_2d_hint(st + 2 * kKTile, &tmap_vt_hi, full, j * kBkv, h * kHd, keep);
-          tma_load_2d_hint(st + 2 * kKTile + 16384, &tmap_vt_lo, full, j * kBkv, h * kHd, keep);
+          if (++stage == kAStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 10) {
+    if (lane == 0) {
+      // ------------------------------------------------ TMA producer of v^T (sweep 2 only):
+      // the two bf16 planes, one box of 128 dims x 64 keys each
+      const uint64_t keep = policy_evict_last();
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        const int h = item / nqt;
+        for (int j = 0; j < nblk; j++) {
+          ok = mbar_wait(bar_vempty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 3);
+          if (!ok) break;
+          const uint32_t full = bar_vfull + 8 * stage;
+          const uint32_t st = base + kAStages * kKStageBytes + stage * kVTile;
+          mbar_expect_tx(full, kVTile);
+          tma_load_2d_hint(st, &tmap_vt_hi, full, j * kBkv, h * kHd, keep);
+          tma_load_2d_hint(st + 16384, &tmap_vt_lo, full, j * kBkv, h * kHd, keep);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -231,7 +257,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------ MMA issuer
-      uint32_t stage = 0, phase = 0;            // operand ring, shared by both sweeps
+      uint32_t stage = 0, phase = 0;            // k ring, shared by both sweeps
+      uint32_t vstage = 0, vphase = 0;          // v^T ring
       uint32_t sfree_ph[2] = {0, 0};            // completed phases of s1free per buffer
       uint32_t pv_ph[2] = {0, 0};               // completed phases of pvdone per buffer
       uint32_t pready_ph[2] = {0, 0};
@@ -276,7 +303,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (!ok) break;
           sfree_ph[buf] ^= 1u;
           tc_fence_after();
-          const uint32_t st = base + stage * kAStageBytes;
+          const uint32_t st = base + stage * kKStageBytes;
           const uint32_t d = tmem_base + (buf ? kColO : kColS);
 #pragma unroll
           for (int ks = 0; ks < kHd / 8; ks++) {
@@ -294,20 +321,20 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (!ok) break;
         tc_fence_after();
         // ---- sweep 2: accurate scores, P*V; the scores of block j+1 are issued before the
-        // weights of block j are waited for, so the two softmax groups and the MMAs overlap
-        uint32_t st_cur = stage, ph_cur = phase;  // ring position of block j
-        ok = mbar_wait(bar_full + 8 * st_cur, ph_cur, abort_flag, g.status, 0x900 | 6);
+        // weights of block j are waited for, so the softmax groups and the MMAs overlap.  A k
+        // stage is released when its scores are done, a v^T stage when its P*V is done.
+        ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x900 | 6);
         if (!ok) break;
         tc_fence_after();
-        issue_scores(base + st_cur * kAStageBytes, 0);
+        issue_scores(base + stage * kKStageBytes, 0);
+        umma_commit(bar_empty + 8 * stage);
         umma_commit(bar_sfull + 0);
+        if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         for (int j = 0; j < nblk; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
-          uint32_t st_next = st_cur + 1, ph_next = ph_cur;
-          if (st_next == kAStages) { st_next = 0; ph_next ^= 1u; }
           if (j + 1 < nblk) {
             const uint32_t nbuf = buf ^ 1u;
-            ok = mbar_wait(bar_full + 8 * st_next, ph_next, abort_flag, g.status, 0x900 | 7);
+            ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x900 | 7);
             if (!ok) break;
             if (j + 1 >= 2) {  // the weights that last lived in this buffer have been consumed
               ok = mbar_wait(bar_pvdone + 8 * nbuf, pv_ph[nbuf], abort_flag, g.status, 0x900 | 8);
@@ -315,14 +342,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
               pv_ph[nbuf] ^= 1u;
             }
             tc_fence_after();
-            issue_scores(base + st_next * kAStageBytes, nbuf);
+            issue_scores(base + stage * kKStageBytes, nbuf);
+            umma_commit(bar_empty + 8 * stage);
             umma_commit(bar_sfull + 8 * nbuf);
+            if (++stage == kAStages) { stage = 0; phase ^= 1u; }
           }
           ok = mbar_wait(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
           if (!ok) break;
           pready_ph[buf] ^= 1u;
+          ok = mbar_wait(bar_vfull + 8 * vstage, vphase, abort_flag, g.status, 0x900 | 11);
+          if (!ok) break;
           tc_fence_after();
-          const uint32_t vt = base + st_cur * kAStageBytes + 2 * kKTile;
+          const uint32_t vt = base + kAStages * kKStageBytes + vstage * kVTile;
           const uint32_t pcol = tmem_base + kColS + buf * kBkv;
 #pragma unroll
           for (int ks = 0; ks < kBkv / 16; ks++) {
@@ -335,14 +366,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             umma_bf16_ts(tmem_base + kColO, p_hi, v_lo, kIdescPV, 1u);
             umma_bf16_ts(tmem_base + kColO, p_hi, v_hi, kIdescPV, 1u);
           }
-          umma_commit(bar_empty + 8 * st_cur);
+          umma_commit(bar_vempty + 8 * vstage);
           umma_commit(bar_pvdone + 8 * buf);
-          st_cur = st_next;
-          ph_cur = ph_next;
+          if (++vstage == kAStages) { vstage = 0; vphase ^= 1u; }
         }
         if (!ok) break;
-        stage = st_cur;
-        phase = ph_cur;
         // drain the pvdone phases of the last two blocks so the parities stay in step
         for (int t = (nblk >= 2 ? nblk - 2 : 0); ok && t < nblk; t++) {
           const uint32_t buf = (uint32_t)(t & 1);
@@ -718,7 +746,7 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   g.status = status;
   const int64_t items = ((Lq + kBq - 1) / kBq) * heads;
   count_launch();
-  sdpa_tc_kernel<<<(unsigned)(items < sm_count ? items : sm_count), kNumThreads, kASmemBytes, s>>>(
+  sdpa_tc_kernel<<<(unsigned)(items < sm_count ? items : sm_count), kAThreads, kASmemBytes, s>>>(
       t_khi128, t_khi, t_khib, t_klob, t_vt_hi, t_vt_lo, t_out, g);
   return cudaGetLastError();
 }
