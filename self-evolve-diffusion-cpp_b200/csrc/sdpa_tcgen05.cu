@@ -15,14 +15,14 @@
 // sums add the split weights, so numerator and denominator agree.
 //
 // Softmax without rescaling.  A first sweep over the keys finds each row's maximum from plain
-// tf32 scores (any value near the true maximum serves as the offset, as long as numerator and
+// bf16 scores (any value near the true maximum serves as the offset, as long as numerator and
 // denominator use the same one); a second sweep recomputes the scores accurately, exponentiates
 // and accumulates P*V in tensor memory for the whole key range.  No accumulator is ever rescaled.
 //
 // One CTA per (128 query rows, head), persistent over these work items; 320 threads:
 //   warp 10 lane 0: TMA producer of v^T (its own two-stage ring, released by the P*V MMAs, so
 //                   the k ring -- released as soon as a block's scores are done -- runs ahead).
-//   warp 0 lane 0 : TMA producer of k.  128 keys of k_hi per stage in sweep 1; per 64-key block
+//   warp 0 lane 0 : TMA producer of k.  128 keys of bf16(k) per stage in sweep 1; per 64-key block
 //                   k_hi, the bf16 planes of k and of v^T in sweep 2; 128-byte-swizzled boxes,
 //                   two-stage ring.
 //   warp 1 lane 0 : MMA issuer.  S = Q K^T with Q (both tf32 planes) as the A operand in TENSOR
@@ -58,12 +58,10 @@ constexpr uint32_t kColQhi = 0, kColQloB = 128, kColQhiB = 192, kColO = 256, kCo
 constexpr int kKbTile = kBkv * kHd * 2;         // 16 KiB: one bf16 plane of a key block
 constexpr uint32_t kIdescS = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kBkv >> 3) << 17) |
                              ((uint32_t)(kBq >> 4) << 24);
-constexpr uint32_t kIdescO = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kHd >> 3) << 17) |
-                             ((uint32_t)(kBq >> 4) << 24);  // tf32, N = 128 (sweep 1)
 // cross terms of the scores: kind::f16 with bf16 inputs (format 1), N = 64
 constexpr uint32_t kIdescSb = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBkv >> 3) << 17) |
                               ((uint32_t)(kBq >> 4) << 24);
-// P*V: kind::f16 with bf16 inputs (format 1), fp32 accumulator, N = 128
+// P*V and the scores of sweep 1: kind::f16 with bf16 inputs (format 1), fp32 accumulator, N = 128
 constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kHd >> 3) << 17) |
                               ((uint32_t)(kBq >> 4) << 24);
 
@@ -114,7 +112,7 @@ struct SdpaArgs {
 };
 
 __global__ void __launch_bounds__(kAThreads, 1)
-    sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi128,
+    sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hib128,
                    const __grid_constant__ CUtensorMap tmap_k_hi,
                    const __grid_constant__ CUtensorMap tmap_k_hib,
                    const __grid_constant__ CUtensorMap tmap_k_lob,
@@ -179,7 +177,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    prefetch_tmap(&tmap_k_hi128);
+    prefetch_tmap(&tmap_k_hib128);
     prefetch_tmap(&tmap_k_hi);
     prefetch_tmap(&tmap_k_hib);
     prefetch_tmap(&tmap_k_lob);
@@ -204,15 +202,15 @@ __global__ void __launch_bounds__(kAThreads, 1)
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int h = item / nqt;
-        // sweep 1: k_hi only, 128 keys per stage (four boxes of 128 keys x 32 dims)
+        // sweep 1: bf16(k_hi) only, 128 keys per stage (two boxes of 128 keys x 64 dims)
         for (int j = 0; j < nblk1; j++) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 1);
           if (!ok) break;
           const uint32_t full = bar_full + 8 * stage;
           const uint32_t st = base + stage * kKStageBytes;
-          mbar_expect_tx(full, kKStageBytes);
-          for (int i = 0; i < 4; i++)
-            tma_load_2d_hint(st + i * 16384, &tmap_k_hi128, full, h * kHd + 32 * i, j * 2 * kBkv, keep);
+          mbar_expect_tx(full, 2 * kKbTile);
+          for (int i = 0; i < 2; i++)
+            tma_load_2d_hint(st + i * 16384, &tmap_k_hib128, full, h * kHd + 64 * i, j * 2 * kBkv, keep);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
         // sweep 2: k_hi (boxes of 64 keys x 32 dims), bf16(k_hi) and bf16(k_lo) (boxes of 64 keys
@@ -293,7 +291,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
         ofree_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
-        // ---- sweep 1: plain tf32 scores for the row maxima, 128 keys per MMA, alternating
+        // ---- sweep 1: bf16 scores for the row maxima (8 mantissa bits are ample for an offset),
+        // 128 keys and 16 dims per MMA, alternating
         // between the score columns (384..511) and the idle O columns (256..383)
         for (int j = 0; j < nblk1; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
@@ -306,9 +305,9 @@ __global__ void __launch_bounds__(kAThreads, 1)
           const uint32_t st = base + stage * kKStageBytes;
           const uint32_t d = tmem_base + (buf ? kColO : kColS);
 #pragma unroll
-          for (int ks = 0; ks < kHd / 8; ks++) {
+          for (int ks = 0; ks < kHd / 16; ks++) {
             const uint64_t kd = make_smem_desc(st + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
-            umma_tf32_ts(d, tmem_base + kColQhi + ks * 8, kd, kIdescO, (uint32_t)(ks != 0));
+            umma_bf16_ts(d, tmem_base + kColQhiB + ks * 8, kd, kIdescPV, (uint32_t)(ks != 0));
           }
           umma_commit(bar_empty + 8 * stage);
           umma_commit(bar_sfull + 8 * buf);
@@ -652,11 +651,11 @@ bool make_tmap_vt(CUtensorMap* map, const void* ptr, int64_t C, int64_t Lk, int6
   return true;
 }
 
-// bf16 plane of k [Lk, C], box = 64 keys x 64 dims (128 bytes), 128-byte swizzle.
-bool make_tmap_kb(CUtensorMap* map, const void* ptr, int64_t Lk, int64_t C, std::string* why) {
+// bf16 plane of k [Lk, C], box = box_keys keys x 64 dims (128 bytes), 128-byte swizzle.
+bool make_tmap_kb(CUtensorMap* map, const void* ptr, int64_t Lk, int64_t C, int box_keys, std::string* why) {
   cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)Lk};
   cuuint64_t strides[1] = {(cuuint64_t)C * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)kBkv};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_keys};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -734,9 +733,9 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   CUtensorMap t_khi128, t_khi, t_khib, t_klob, t_vt_hi, t_vt_lo, t_out;
-  if (!make_tmap_2d_f32(&t_khi128, k_hi, Lk, C, C, 2 * kBkv, why) ||
-      !make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_kb(&t_khib, k_hib, Lk, C, why) ||
-      !make_tmap_kb(&t_klob, k_lob, Lk, C, why) ||
+  if (!make_tmap_kb(&t_khi128, k_hib, Lk, C, 2 * kBkv, why) ||
+      !make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_kb(&t_khib, k_hib, Lk, C, kBkv, why) ||
+      !make_tmap_kb(&t_klob, k_lob, Lk, C, kBkv, why) ||
       !make_tmap_vt(&t_vt_hi, vt_hi, C, Lk, ld, why) || !make_tmap_vt(&t_vt_lo, vt_lo, C, Lk, ld, why) ||
       !make_out_tmap(&t_out, out, Lq, C, why))
     return cudaErrorInvalidValue;
