@@ -25,9 +25,12 @@
 //   warp 0 lane 0 : TMA producer of k.  128 keys of bf16(k) per stage in sweep 1; per 64-key block
 //                   k_hi, the bf16 planes of k and of v^T in sweep 2; 128-byte-swizzled boxes,
 //                   two-stage ring.
-//   warp 1 lane 0 : MMA issuer.  S = Q K^T with Q (both tf32 planes) as the A operand in TENSOR
-//                   MEMORY, K from shared memory; O += P V with P in tensor memory (written in
-//                   place over S by the softmax warps), V^T from shared memory.
+//   warp 1 lane 0 : MMA issuer of the scores.  S = Q K^T with Q as the A operand in TENSOR
+//                   MEMORY, K from shared memory.
+//   warp 11 lane 0: MMA issuer of O += P V, with P in tensor memory (written in place over S by
+//                   the softmax warps) and V^T from shared memory.  Issuing a small MMA costs the
+//                   issuing lane about as long as the tensor pipe needs for it, so the two
+//                   streams of instructions come from two lanes.
 //   warps 2..5    : softmax group A (one thread per query row): the first 32 keys of every block.
 //   warps 6..9    : softmax group B: the other 32 keys.  Both groups finish the tile together:
 //                   O / row sum -> staged boxes -> bulk tensor stores.
@@ -50,7 +53,7 @@ constexpr int kVTile = kHd * kBkv * 4;          // 32 KiB: v^T of a key block
 constexpr int kKStageBytes = 2 * kKTile;   // k_hi (tf32) + bf16(k_hi) + bf16(k_lo); sweep 1: 128 keys of k_hi
 constexpr int kAStages = 2;                // per ring
 constexpr int kAStageBytes = kKStageBytes + kVTile;  // both rings, one stage each
-constexpr int kAThreads = kNumThreads + 32;  // + one warp: the v^T producer
+constexpr int kAThreads = kNumThreads + 64;  // + two warps: the v^T producer and the P*V issuer
 constexpr int kABookBytes = 2304;    // row maxima and sums of both groups (2 KiB) + barriers
 constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte boundary
 constexpr int kASmemBytes = kAStages * kAStageBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
@@ -256,10 +259,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
     if (lane == 0) {
       // ------------------------------------------------ MMA issuer
       uint32_t stage = 0, phase = 0;            // k ring, shared by both sweeps
-      uint32_t vstage = 0, vphase = 0;          // v^T ring
       uint32_t sfree_ph[2] = {0, 0};            // completed phases of s1free per buffer
       uint32_t pv_ph[2] = {0, 0};               // completed phases of pvdone per buffer
-      uint32_t pready_ph[2] = {0, 0};
       uint32_t q_ph = 0, m_ph = 0, ofree_ph = 0;
       bool ok = true;
       // scores of block j from the operands in `st`: the two small cross terms first (bf16, 16
@@ -346,6 +347,28 @@ __global__ void __launch_bounds__(kAThreads, 1)
             umma_commit(bar_sfull + 8 * nbuf);
             if (++stage == kAStages) { stage = 0; phase ^= 1u; }
           }
+        }
+        if (!ok) break;
+        // drain the pvdone phases of the last two blocks so the parities stay in step
+        for (int t = (nblk >= 2 ? nblk - 2 : 0); ok && t < nblk; t++) {
+          const uint32_t buf = (uint32_t)(t & 1);
+          ok = mbar_wait(bar_pvdone + 8 * buf, pv_ph[buf], abort_flag, g.status, 0x900 | 10);
+          pv_ph[buf] ^= 1u;
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 11) {
+    if (lane == 0) {
+      // ------------------------------------------------ MMA issuer of P*V
+      uint32_t vstage = 0, vphase = 0;
+      uint32_t pready_ph[2] = {0, 0};
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        // (O is free: every softmax warp released the previous item's O before it could arrive
+        // on this item's first pready)
+        for (int j = 0; j < nblk; j++) {
+          const uint32_t buf = (uint32_t)(j & 1);
           ok = mbar_wait(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
           if (!ok) break;
           pready_ph[buf] ^= 1u;
@@ -370,14 +393,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
           if (++vstage == kAStages) { vstage = 0; vphase ^= 1u; }
         }
         if (!ok) break;
-        // drain the pvdone phases of the last two blocks so the parities stay in step
-        for (int t = (nblk >= 2 ? nblk - 2 : 0); ok && t < nblk; t++) {
-          const uint32_t buf = (uint32_t)(t & 1);
-          ok = mbar_wait(bar_pvdone + 8 * buf, pv_ph[buf], abort_flag, g.status, 0x900 | 10);
-          pv_ph[buf] ^= 1u;
-        }
-        if (!ok) break;
-        umma_commit(bar_ofull);
+        umma_commit(bar_ofull);  // every P*V of the item (and so every MMA before them) is complete
       }
     }
   } else {
