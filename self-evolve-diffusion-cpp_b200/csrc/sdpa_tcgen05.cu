@@ -25,12 +25,12 @@
 //   warp 0 lane 0 : TMA producer of k.  128 keys of bf16(k) per stage in sweep 1; per 64-key block
 //                   k_hi, the bf16 planes of k and of v^T in sweep 2; 128-byte-swizzled boxes,
 //                   two-stage ring.
-//   warp 1 lane 0 : MMA issuer of the scores.  S = Q K^T with Q as the A operand in TENSOR
-//                   MEMORY, K from shared memory.
+//   warp 1 lane 0 : MMA issuer of the scores of the even key blocks.  S = Q K^T with Q as the
+//   warp 12 lane 0: ... and of the odd key blocks.  A operand in TENSOR MEMORY, K from shared memory.
 //   warp 11 lane 0: MMA issuer of O += P V, with P in tensor memory (written in place over S by
 //                   the softmax warps) and V^T from shared memory.  Issuing a small MMA costs the
-//                   issuing lane about as long as the tensor pipe needs for it, so the two
-//                   streams of instructions come from two lanes.
+//                   issuing lane about as long as the tensor pipe needs for it, so the
+//                   instruction streams come from three lanes.
 //   warps 2..5    : softmax group A (one thread per query row): the first 32 keys of every block.
 //   warps 6..9    : softmax group B: the other 32 keys.  Both groups finish the tile together:
 //                   O / row sum -> staged boxes -> bulk tensor stores.
@@ -53,7 +53,7 @@ constexpr int kVTile = kHd * kBkv * 4;          // 32 KiB: v^T of a key block
 constexpr int kKStageBytes = 2 * kKTile;   // k_hi (tf32) + bf16(k_hi) + bf16(k_lo); sweep 1: 128 keys of k_hi
 constexpr int kAStages = 2;                // per ring
 constexpr int kAStageBytes = kKStageBytes + kVTile;  // both rings, one stage each
-constexpr int kAThreads = kNumThreads + 64;  // + two warps: the v^T producer and the P*V issuer
+constexpr int kAThreads = kNumThreads + 96;  // + three warps: v^T producer, P*V issuer, second score issuer
 constexpr int kABookBytes = 2304;    // row maxima and sums of both groups (2 KiB) + barriers
 constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte boundary
 constexpr int kASmemBytes = kAStages * kAStageBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
@@ -255,18 +255,23 @@ __global__ void __launch_bounds__(kAThreads, 1)
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 12) {
     if (lane == 0) {
-      // ------------------------------------------------ MMA issuer
-      uint32_t stage = 0, phase = 0;            // k ring, shared by both sweeps
-      uint32_t sfree_ph[2] = {0, 0};            // completed phases of s1free per buffer
-      uint32_t pv_ph[2] = {0, 0};               // completed phases of pvdone per buffer
+      // ------------------------------------------------ MMA issuers of the scores: this lane
+      // takes the blocks of one parity (warp 1 the even ones, warp 12 the odd ones) in both
+      // sweeps, i.e. always the same score buffer.  The k ring is shared: block number `seq` of
+      // the CTA's whole run sits in stage seq & 1, whose full barrier completes its phase
+      // (seq >> 1) & 1 for it.
+      const uint32_t par = warp == 1 ? 0u : 1u;
+      uint32_t sfree_ph = 0;                    // completed phases of s1free[par]
+      uint32_t pv_ph = 0;                       // completed phases of pvdone[par]
       uint32_t q_ph = 0, m_ph = 0, ofree_ph = 0;
+      uint32_t seq0 = 0;                        // k-ring sequence number of the item's first block
       bool ok = true;
-      // scores of block j from the operands in `st`: the two small cross terms first (bf16, 16
+      // scores of a block from the operands in `st`: the two small cross terms first (bf16, 16
       // dims per instruction), then the large term (tf32, 8 dims per instruction)
-      auto issue_scores = [&](uint32_t st, uint32_t buf) {
-        const uint32_t d = tmem_base + kColS + buf * kBkv;
+      auto issue_scores = [&](uint32_t st) {
+        const uint32_t d = tmem_base + kColS + par * kBkv;
 #pragma unroll
         for (int ks = 0; ks < kHd / 16; ks++) {
           const uint32_t off = (uint32_t)((ks >> 2) * 8192);
@@ -286,33 +291,31 @@ __global__ void __launch_bounds__(kAThreads, 1)
         ok = mbar_wait(bar_qready, q_ph, abort_flag, g.status, 0x900 | 1);
         q_ph ^= 1u;
         if (!ok) break;
-        tc_fence_after();
         // the previous item's O has been read out: sweep 1 borrows its columns
         ok = mbar_wait(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
         ofree_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
         // ---- sweep 1: bf16 scores for the row maxima (8 mantissa bits are ample for an offset),
-        // 128 keys and 16 dims per MMA, alternating
-        // between the score columns (384..511) and the idle O columns (256..383)
-        for (int j = 0; j < nblk1; j++) {
-          const uint32_t buf = (uint32_t)(j & 1);
-          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x900 | 2);
+        // 128 keys and 16 dims per MMA; the even blocks go to the score columns (384..511), the
+        // odd ones to the idle O columns (256..383)
+        for (int j = (int)par; j < nblk1; j += 2) {
+          const uint32_t seq = seq0 + (uint32_t)j, stage = seq & 1u;
+          ok = mbar_wait(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 2);
           if (!ok) break;
-          ok = mbar_wait(bar_s1free + 8 * buf, sfree_ph[buf] ^ 1u, abort_flag, g.status, 0x900 | 3);
+          ok = mbar_wait(bar_s1free + 8 * par, sfree_ph ^ 1u, abort_flag, g.status, 0x900 | 3);
           if (!ok) break;
-          sfree_ph[buf] ^= 1u;
+          sfree_ph ^= 1u;
           tc_fence_after();
           const uint32_t st = base + stage * kKStageBytes;
-          const uint32_t d = tmem_base + (buf ? kColO : kColS);
+          const uint32_t d = tmem_base + (par ? kColO : kColS);
 #pragma unroll
           for (int ks = 0; ks < kHd / 16; ks++) {
             const uint64_t kd = make_smem_desc(st + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
             umma_bf16_ts(d, tmem_base + kColQhiB + ks * 8, kd, kIdescPV, (uint32_t)(ks != 0));
           }
           umma_commit(bar_empty + 8 * stage);
-          umma_commit(bar_sfull + 8 * buf);
-          if (++stage == kAStages) { stage = 0; phase ^= 1u; }
+          umma_commit(bar_sfull + 8 * par);
         }
         if (!ok) break;
         // the softmax groups have read every score of sweep 1 and published the maxima
@@ -320,42 +323,32 @@ __global__ void __launch_bounds__(kAThreads, 1)
         m_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
-        // ---- sweep 2: accurate scores, P*V; the scores of block j+1 are issued before the
-        // weights of block j are waited for, so the softmax groups and the MMAs overlap.  A k
-        // stage is released when its scores are done, a v^T stage when its P*V is done.
-        ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x900 | 6);
-        if (!ok) break;
-        tc_fence_after();
-        issue_scores(base + stage * kKStageBytes, 0);
-        umma_commit(bar_empty + 8 * stage);
-        umma_commit(bar_sfull + 0);
-        if (++stage == kAStages) { stage = 0; phase ^= 1u; }
-        for (int j = 0; j < nblk; j++) {
-          const uint32_t buf = (uint32_t)(j & 1);
-          if (j + 1 < nblk) {
-            const uint32_t nbuf = buf ^ 1u;
-            ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x900 | 7);
+        // ---- sweep 2: accurate scores of this lane's blocks.  The buffer is free again when the
+        // P*V of the block two back has consumed its weights; a k stage is released as soon as
+        // the scores that read it are done.
+        bool any = false;
+        for (int j = (int)par; j < nblk; j += 2) {
+          const uint32_t seq = seq0 + (uint32_t)(nblk1 + j), stage = seq & 1u;
+          ok = mbar_wait(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 7);
+          if (!ok) break;
+          if (any) {
+            ok = mbar_wait(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 8);
             if (!ok) break;
-            if (j + 1 >= 2) {  // the weights that last lived in this buffer have been consumed
-              ok = mbar_wait(bar_pvdone + 8 * nbuf, pv_ph[nbuf], abort_flag, g.status, 0x900 | 8);
-              if (!ok) break;
-              pv_ph[nbuf] ^= 1u;
-            }
-            tc_fence_after();
-            issue_scores(base + stage * kKStageBytes, nbuf);
-            umma_commit(bar_empty + 8 * stage);
-            umma_commit(bar_sfull + 8 * nbuf);
-            if (++stage == kAStages) { stage = 0; phase ^= 1u; }
+            pv_ph ^= 1u;
           }
+          tc_fence_after();
+          issue_scores(base + stage * kKStageBytes);
+          umma_commit(bar_empty + 8 * stage);
+          umma_commit(bar_sfull + 8 * par);
+          any = true;
         }
         if (!ok) break;
-        // drain the pvdone phases of the last two blocks so the parities stay in step
-        for (int t = (nblk >= 2 ? nblk - 2 : 0); ok && t < nblk; t++) {
-          const uint32_t buf = (uint32_t)(t & 1);
-          ok = mbar_wait(bar_pvdone + 8 * buf, pv_ph[buf], abort_flag, g.status, 0x900 | 10);
-          pv_ph[buf] ^= 1u;
+        if (any) {  // the completion of this lane's last block, so that the parity stays in step
+          ok = mbar_wait(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 10);
+          pv_ph ^= 1u;
+          if (!ok) break;
         }
-        if (!ok) break;
+        seq0 += (uint32_t)(nblk1 + nblk);
       }
     }
   } else if (warp == 11) {
