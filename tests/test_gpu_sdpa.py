@@ -42,6 +42,8 @@ def test_matches_reference_fixture(sdq, golden_dir):
     (1024, 512, 24),      # the text cross-attention of a 1024-token tile: all 24 heads
     (2048, 2048, 4),
     (700, 4100, 3),       # many key blocks per row, ragged at both ends
+    (1300, 200, 32),      # 352 work items: several per CTA, an odd number of 128-key blocks
+    (260, 129, 5),        # three key blocks: the two score-issuing lanes get 2 and 1
 ])
 def test_against_float64(sdq, Lq, Lk, heads):
     rng = np.random.default_rng(Lq + Lk + heads)
