@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch", "libcompare", "block", "fp32"])
     ap.add_argument("--blocks", type=int, default=30, help="branch workload: number of DiT blocks")
     ap.add_argument("--heads", type=int, default=24, help="fp32 workload: attention heads of 128")
+    ap.add_argument("--with-attention", action="store_true",
+                    help="block workload: also run the block's self- and cross-attention (sdq_sdpa) in the fused pattern")
     ap.add_argument("--pack-file-blocks", type=int, default=0,
                     help="branch workload: also write this many blocks as a .sdcpp file and time the load")
     ap.add_argument("--verify-blocks", type=int, default=1, help="branch workload: blocks whose packed bytes are compared with the CPU packer")
@@ -831,16 +833,25 @@ def run_block(args):
         lin_bias("ffn.2", hid, M, y)
         xx.addcmul_(y, e[5])
 
+    heads = D // 128
+    qs, ks, vs = (qkv[:, :D].contiguous(), qkv[:, D:2 * D].contiguous(), qkv[:, 2 * D:].contiguous()) \
+        if args.with_attention else (None, None, None)
+    kv2 = torch.empty(T, D, device=dev) if args.with_attention else None
+
     def fused(xx):
         eps = C.c_float(1e-6)
         s._ck(lib.sdq_layernorm_mod_quantize(p(xx), M, D, p(e[0]), p(e[1]), eps, p(aq), p(a_s), None, 0, sp))
         pre("self_attn.qkv", aq, a_s, M, qkv)
+        if args.with_attention:      # self-attention over the M tokens (q/k RMSNorm and RoPE: the caller's)
+            s._ck(lib.sdq_sdpa(p(qs), p(ks), p(vs), M, M, D, heads, p(att), 0, sp))
         s._ck(lib.sdq_qgemm_residual(W["self_attn.o"][2], p(att), M, p(xx), p(e[2]), p(xx), p(W["self_attn.o"][3]), 0, sp))
         s._ck(lib.sdq_layernorm_mod_quantize(p(xx), M, D, p(ln3_b), p(ln3_w), eps, p(aq), p(a_s), None, S.LN_AFFINE, sp))
         pre("cross_attn.q", aq, a_s, M, y)
         s._ck(lib.sdq_quantize_activations(p(ctx), T, D, p(aqt), p(a_st), sp))
         pre("cross_attn.k", aqt, a_st, T, kv)
-        pre("cross_attn.v", aqt, a_st, T, kv)
+        pre("cross_attn.v", aqt, a_st, T, kv2 if args.with_attention else kv)
+        if args.with_attention:      # cross-attention on the 512 text tokens
+            s._ck(lib.sdq_sdpa(p(y), p(kv), p(kv2), M, T, D, heads, p(att), 0, sp))
         s._ck(lib.sdq_qgemm_residual(W["cross_attn.o"][2], p(att), M, p(xx), None, p(xx), p(W["cross_attn.o"][3]), 0, sp))
         s._ck(lib.sdq_ffn_block(W["ffn.0"][2], p(W["ffn.0"][3]), W["ffn.2"][2], p(W["ffn.2"][3]), p(xx), M,
                                 p(e[3]), p(e[4]), p(e[5]), eps, 0, sp))
@@ -859,11 +870,13 @@ def run_block(args):
         s.sync(sp)
         return e0.elapsed_time(e1) / args.steps, (s.launches() - n0) // args.steps
     # the two in-place patterns agree within the GELU bound on the same input
-    xa, xb = x.clone(), x.clone()
-    unfused(xa)
-    fused(xb)
-    torch.cuda.synchronize()
-    agree = float((xa - xb).abs().max() / xa.abs().max())
+    agree = None
+    if not args.with_attention:    # (with attention the fused pattern computes more than the unfused one)
+        xa, xb = x.clone(), x.clone()
+        unfused(xa)
+        fused(xb)
+        torch.cuda.synchronize()
+        agree = float((xa - xb).abs().max() / xa.abs().max())
     ops = sum(2.0 * (M if rows is None else rows) * N * K for (_, K, N, rows) in BLOCK_LINEARS)
     xw = x.clone()
     t_bare, l_bare = timed(bare)
@@ -880,6 +893,7 @@ def run_block(args):
                       "patterns_ms": {"bare_linears": t_bare, "unfused_with_elementwise_passes": t_unf,
                                       "fused_entry_points": t_fus},
                       "launches_per_block": {"bare_linears": l_bare, "unfused_own_kernels": l_unf, "fused": l_fus},
+                      "fused_pattern_includes_attention": bool(args.with_attention),
                       "fused_vs_unfused_max_rel_diff": agree}))
     return 0
 
