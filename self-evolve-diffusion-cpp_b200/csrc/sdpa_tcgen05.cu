@@ -288,11 +288,11 @@ __global__ void __launch_bounds__(kAThreads, 1)
         }
       };
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-        ok = mbar_wait(bar_qready, q_ph, abort_flag, g.status, 0x900 | 1);
+        ok = mbar_wait_spin(bar_qready, q_ph, abort_flag, g.status, 0x900 | 1);
         q_ph ^= 1u;
         if (!ok) break;
         // the previous item's O has been read out: sweep 1 borrows its columns
-        ok = mbar_wait(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
+        ok = mbar_wait_spin(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
         ofree_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
@@ -301,9 +301,9 @@ __global__ void __launch_bounds__(kAThreads, 1)
         // odd ones to the idle O columns (256..383)
         for (int j = (int)par; j < nblk1; j += 2) {
           const uint32_t seq = seq0 + (uint32_t)j, stage = seq & 1u;
-          ok = mbar_wait(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 2);
+          ok = mbar_wait_spin(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 2);
           if (!ok) break;
-          ok = mbar_wait(bar_s1free + 8 * par, sfree_ph ^ 1u, abort_flag, g.status, 0x900 | 3);
+          ok = mbar_wait_spin(bar_s1free + 8 * par, sfree_ph ^ 1u, abort_flag, g.status, 0x900 | 3);
           if (!ok) break;
           sfree_ph ^= 1u;
           tc_fence_after();
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
         }
         if (!ok) break;
         // the softmax groups have read every score of sweep 1 and published the maxima
-        ok = mbar_wait(bar_mready, m_ph, abort_flag, g.status, 0x900 | 4);
+        ok = mbar_wait_spin(bar_mready, m_ph, abort_flag, g.status, 0x900 | 4);
         m_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
@@ -329,10 +329,10 @@ __global__ void __launch_bounds__(kAThreads, 1)
         bool any = false;
         for (int j = (int)par; j < nblk; j += 2) {
           const uint32_t seq = seq0 + (uint32_t)(nblk1 + j), stage = seq & 1u;
-          ok = mbar_wait(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 7);
+          ok = mbar_wait_spin(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 7);
           if (!ok) break;
           if (any) {
-            ok = mbar_wait(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 8);
+            ok = mbar_wait_spin(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 8);
             if (!ok) break;
             pv_ph ^= 1u;
           }
@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
         }
         if (!ok) break;
         if (any) {  // the completion of this lane's last block, so that the parity stays in step
-          ok = mbar_wait(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 10);
+          ok = mbar_wait_spin(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 10);
           pv_ph ^= 1u;
           if (!ok) break;
         }
@@ -362,10 +362,10 @@ __global__ void __launch_bounds__(kAThreads, 1)
         // on this item's first pready)
         for (int j = 0; j < nblk; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
-          ok = mbar_wait(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
+          ok = mbar_wait_spin(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
           if (!ok) break;
           pready_ph[buf] ^= 1u;
-          ok = mbar_wait(bar_vfull + 8 * vstage, vphase, abort_flag, g.status, 0x900 | 11);
+          ok = mbar_wait_spin(bar_vfull + 8 * vstage, vphase, abort_flag, g.status, 0x900 | 11);
           if (!ok) break;
           tc_fence_after();
           const uint32_t vt = base + kAStages * kKStageBytes + vstage * kVTile;
@@ -489,25 +489,29 @@ __global__ void __launch_bounds__(kAThreads, 1)
           tmem_ld_32x32(s_col + buf * kBkv, r);
           tmem_ld_wait();
           const int64_t key0 = (int64_t)j * kBkv + grp * 32;
-          // this group's 32 columns become: 16 columns of bf16 pairs p_hi, then 16 of p_lo
+          const int valid = (int)min((int64_t)32, g.Lk - key0);  // < 32 only in the last block
+          // this group's 32 columns become: 16 columns of bf16 pairs p_hi, then 16 of p_lo.
+          // Two weights at a time: one cvt packs the pair of high parts, whose fp32 values are
+          // the two halves of that word shifted up; the low parts are what is left, packed by a
+          // second cvt.  The row sum adds the weights themselves (they differ from hi + lo by
+          // 2^-17 at most).
           uint32_t w[32];
 #pragma unroll
           for (int t = 0; t < 32; t += 2) {
-            float p[2] = {0.0f, 0.0f}, hi[2], lo[2];
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-              if (key0 + t + u < g.Lk) {
-                const float e = __fmul_rn(__fsub_rn(__uint_as_float(r[t + u]), m), g.scale_log2e);
-                asm("ex2.approx.f32 %0, %1;" : "=f"(p[u]) : "f"(e));
-              }
-              hi[u] = __bfloat162float(__float2bfloat16_rn(p[u]));
-              lo[u] = __bfloat162float(__float2bfloat16_rn(__fsub_rn(p[u], hi[u])));
-              l += __fadd_rn(hi[u], lo[u]);
-            }
-            const __nv_bfloat162 ph = __floats2bfloat162_rn(hi[0], hi[1]);  // lower key in the low half
-            const __nv_bfloat162 pl = __floats2bfloat162_rn(lo[0], lo[1]);
-            w[t >> 1] = *reinterpret_cast<const uint32_t*>(&ph);
-            w[16 + (t >> 1)] = *reinterpret_cast<const uint32_t*>(&pl);
+            float p0 = 0.0f, p1 = 0.0f;
+            const float e0 = __fmul_rn(__fsub_rn(__uint_as_float(r[t]), m), g.scale_log2e);
+            const float e1 = __fmul_rn(__fsub_rn(__uint_as_float(r[t + 1]), m), g.scale_log2e);
+            asm("ex2.approx.f32 %0, %1;" : "=f"(p0) : "f"(e0));
+            asm("ex2.approx.f32 %0, %1;" : "=f"(p1) : "f"(e1));
+            if (t >= valid) p0 = 0.0f;
+            if (t + 1 >= valid) p1 = 0.0f;
+            l += __fadd_rn(p0, p1);
+            uint32_t hi2, lo2;
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi2) : "f"(p1), "f"(p0));  // first source -> upper half
+            const float h0 = __uint_as_float(hi2 << 16), h1 = __uint_as_float(hi2 & 0xffff0000u);
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo2) : "f"(__fsub_rn(p1, h1)), "f"(__fsub_rn(p0, h0)));
+            w[t >> 1] = hi2;
+            w[16 + (t >> 1)] = lo2;
           }
           tmem_st_32x32(s_col + buf * kBkv, w);
         }

@@ -71,6 +71,35 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same bounded wait, polling without the hardware suspend: for a single lane whose wake-up
+// latency sits on the critical path (an MMA issuer between dependent batches of instructions).
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 1023u) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        __threadfence_system();
+        return false;
+      }
+    }
+  }
+}
+
 // Programmatic dependent launch, consumer side: returns once every kernel this grid depends
 // on in its stream has completed and its writes are visible.  Everything before it (barrier
 // set-up, tensor-memory allocation, descriptor prefetch) may overlap the producer kernel.
