@@ -965,7 +965,7 @@ def run_fp32(args):
     print(json.dumps({"metric": "fp32_attention_throughput", "value": att_flop / (t_att * 1e-3) / 1e12,
                       "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
                       "ms_per_step": t_att, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                      "dtype": "tf32x3 scores, bf16x3 P*V, f32 accumulate", "data": "synthetic",
+                      "dtype": "fp16x3 scores and P*V (two-term splits), f32 accumulate", "data": "synthetic",
                       "config": {"workload": "dit_attention_and_fp32_matmul", "tokens": L, "heads": H,
                                  "l2": "q, k, v %d MB each" % (L * Cc * 4 // 1000000)},
                       "gpu_launches": att_launches * args.steps,

@@ -3,43 +3,53 @@
 // fp32, no mask, scale 1/sqrt(head_dim)), for head_dim 128.
 //
 // Precision.  The reference is fp32 throughout and its outputs are compared at 1e-3 of the
-// largest value, which a plain tf32 (10-bit mantissa) score cannot hold in the tails: an error of
+// largest value, which a single 11-bit rounding of q and k cannot hold in the tails: an error of
 // 2^-11 in q or k moves a score by ~1e-3 and exp() turns that into the same relative error of the
-// weight.  So the scores are computed with three products per fp32 product (q = hi + lo,
-// k = hi + lo with hi = tf32(x); hi*hi + lo*hi + hi*lo): the large term as tf32 MMAs, the two
-// small cross terms (2^-11 of the product, so 8 mantissa bits are plenty) as bf16 MMAs, which
-// take 16 instead of 8 elements of the head dimension per instruction.  The softmax weights and v are each split into two bf16
-// numbers (16 mantissa bits together) and P*V is three bf16 MMAs (hi*hi + hi*lo + lo*hi): twice
-// the rate of tf32 per MMA, the same shared-memory and tensor-memory footprint as one tf32 plane,
-// and an error of ~1e-5 instead of the 3..6e-4 a single tf32 rounding of P and V leaves.  The row
-// sums add the split weights, so numerator and denominator agree.
+// weight.  So every operand is split into two fp16 numbers, x * 2^sh = hi + lo with hi = fp16(.)
+// and lo = fp16(. - hi) (22 mantissa bits together), and every product is three fp16 MMAs
+// (hi*hi + lo*hi + hi*lo, fp32 accumulation), for the scores and for P*V alike.  fp16 carries the
+// same 11 bits as tf32 but takes 16 instead of 8 elements of the contraction per instruction and
+// half the shared and tensor memory, which is what lets a key block be 128 keys wide.  The
+// powers of two 2^sh bring each operand's largest magnitude to [2^14, 2^15), so nothing overflows
+// and elements down to 2^-29 of the largest keep all their bits: one shift per query row (found by
+// the thread that owns the row), one for the whole of k and one for v (an absmax pass before the
+// split), a constant 2^10 for the softmax weights.  They are undone exactly: the row's and k's in
+// the factor the scores are multiplied by anyway, v's in the final 1 / row sum; the weights' cancels.
+// The row sums add the weights themselves, so numerator and denominator agree.
 //
-// Softmax without rescaling.  A first sweep over the keys finds each row's maximum from plain
-// bf16 scores (any value near the true maximum serves as the offset, as long as numerator and
-// denominator use the same one); a second sweep recomputes the scores accurately, exponentiates
-// and accumulates P*V in tensor memory for the whole key range.  No accumulator is ever rescaled.
+// Softmax without rescaling.  A first sweep over the keys finds each row's maximum from the
+// hi*hi scores alone (any value near the true maximum serves as the offset, as long as numerator
+// and denominator use the same one); a second sweep recomputes the scores accurately,
+// exponentiates and accumulates P*V in tensor memory for the whole key range.  No accumulator is
+// ever rescaled.  The offset must be within a few log2 units of the true maximum for the fp16
+// weights to keep their bits: where it is not (a weight reaches 2^15.8, or a row sum stays below
+// 2^3 -- scores in the tens of thousands, where the hi*hi scores of the first sweep are off by
+// that much), the row is marked and recomputed afterwards in plain fp32 on the CUDA cores by the
+// kernel that also serves the other head sizes.  So is a row whose scores can be so large
+// (head_dim * max|q_row| * max|k| / sqrt(head_dim) above 2^19 log2 units) that the dropped lo*lo
+// terms, 2^-22 of the products, would reach the weights.  A NaN row sum marks its row too.
 //
-// One CTA per (128 query rows, head), persistent over these work items; 320 threads:
-//   warp 10 lane 0: TMA producer of v^T (its own two-stage ring, released by the P*V MMAs, so
-//                   the k ring -- released as soon as a block's scores are done -- runs ahead).
-//   warp 0 lane 0 : TMA producer of k.  128 keys of bf16(k) per stage in sweep 1; per 64-key block
-//                   k_hi, the bf16 planes of k and of v^T in sweep 2; 128-byte-swizzled boxes,
-//                   two-stage ring.
+// One CTA per (128 query rows, head), persistent over these work items; 416 threads:
+//   warp 0 lane 0 : TMA producer of k: 128 keys per stage, the hi plane in sweep 1, hi and lo in
+//                   sweep 2; 128-byte-swizzled boxes of 128 keys x 64 dims, two-stage ring,
+//                   released as soon as a block's scores are done.
+//   warp 10 lane 0: TMA producer of v^T (hi and lo planes, 64 keys per stage, its own two-stage
+//                   ring released by the P*V MMAs).
 //   warp 1 lane 0 : MMA issuer of the scores of the even key blocks.  S = Q K^T with Q as the
 //   warp 12 lane 0: ... and of the odd key blocks.  A operand in TENSOR MEMORY, K from shared memory.
 //   warp 11 lane 0: MMA issuer of O += P V, with P in tensor memory (written in place over S by
 //                   the softmax warps) and V^T from shared memory.  Issuing a small MMA costs the
 //                   issuing lane about as long as the tensor pipe needs for it, so the
 //                   instruction streams come from three lanes.
-//   warps 2..5    : softmax group A (one thread per query row): the first 32 keys of every block.
-//   warps 6..9    : softmax group B: the other 32 keys.  Both groups finish the tile together:
+//   warps 2..5    : softmax group A (one thread per query row): the first 64 keys of every block.
+//   warps 6..9    : softmax group B: the other 64 keys.  Both groups finish the tile together:
 //                   O / row sum -> staged boxes -> bulk tensor stores.
-// Tensor memory (512 columns): Q_hi (tf32) 0..127, bf16(Q_lo) 128..191, bf16(Q_hi) 192..255,
-// O 256..383, S/P buffers 384..447 and 448..511.  Every mbarrier wait is bounded like the GEMM kernels'.
+// Tensor memory (512 columns, two fp16 per column for the A operands): Q_hi 0..63, Q_lo 64..127,
+// O 128..255, S/P buffers 256..383 and 384..511.  Every mbarrier wait is bounded like the GEMM
+// kernels'.
 #include "tc_common.cuh"
-#include "tf32_split.cuh"
 
-#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace sdq {
 namespace {
@@ -47,40 +57,55 @@ using namespace tc;
 
 constexpr int kHd = 128;            // head_dim this kernel is built for
 constexpr int kBq = 128;            // query rows per work item
-constexpr int kBkv = 64;            // keys per block
-constexpr int kKTile = kBkv * kHd * 4;          // 32 KiB: one tf32 plane of a key block
-constexpr int kVTile = kHd * kBkv * 4;          // 32 KiB: v^T of a key block
-constexpr int kKStageBytes = 2 * kKTile;   // k_hi (tf32) + bf16(k_hi) + bf16(k_lo); sweep 1: 128 keys of k_hi
+constexpr int kBkv = 128;           // keys per block
+constexpr int kVKeys = 64;          // keys per stage of the v^T ring
+constexpr int kKPlane = kBkv * kHd * 2;         // 32 KiB: one fp16 plane of a key block
+constexpr int kKStageBytes = 2 * kKPlane;       // k hi + lo
+constexpr int kVPlane = kHd * kVKeys * 2;       // 16 KiB: one fp16 plane of 64 keys of v^T
+constexpr int kVStageBytes = 2 * kVPlane;       // v^T hi + lo
 constexpr int kAStages = 2;                // per ring
-constexpr int kAStageBytes = kKStageBytes + kVTile;  // both rings, one stage each
+constexpr int kARingBytes = kAStages * (kKStageBytes + kVStageBytes);
 constexpr int kAThreads = kNumThreads + 96;  // + three warps: v^T producer, P*V issuer, second score issuer
 constexpr int kABookBytes = 2304;    // row maxima and sums of both groups (2 KiB) + barriers
 constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte boundary
-constexpr int kASmemBytes = kAStages * kAStageBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
-constexpr uint32_t kColQhi = 0, kColQloB = 128, kColQhiB = 192, kColO = 256, kColS = 384;
-constexpr int kKbTile = kBkv * kHd * 2;         // 16 KiB: one bf16 plane of a key block
-constexpr uint32_t kIdescS = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kBkv >> 3) << 17) |
+constexpr int kASmemBytes = kARingBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
+constexpr uint32_t kColQhi = 0, kColQlo = 64, kColO = 128, kColS = 256;
+constexpr float kPShift = 10.0f;     // the softmax weights are carried as p * 2^10 (<= 2^10 up to
+                                     // the error of the first sweep's maxima; clamped below 2^16)
+constexpr uint32_t kPHalfTop = 0x7b00;  // fp16 bits of 2^15.8: a weight this large means the first
+                                        // sweep's maximum was ~6 log2 units too low
+constexpr float kRowSumFloor = 8.0f;    // a row sum below 2^3 means it was ~7 too high
+constexpr float kScoreBound = 524288.0f;  // 2^19 log2 units: above this bound on sum |q_d k_d| the
+                                          // dropped lo*lo terms (2^-22 of it) would show in the weights
+constexpr int kOperandTop = 14;      // operands are scaled so that their largest magnitude is in [2^14, 2^15)
+// kind::f16 with fp16 inputs (format 0), fp32 accumulator, M = 128, N = 128: the scores (N = keys)
+// and P*V (N = head dims)
+constexpr uint32_t kIdescH = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(128 >> 3) << 17) |
                              ((uint32_t)(kBq >> 4) << 24);
-// cross terms of the scores: kind::f16 with bf16 inputs (format 1), N = 64
-constexpr uint32_t kIdescSb = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBkv >> 3) << 17) |
-                              ((uint32_t)(kBq >> 4) << 24);
-// P*V and the scores of sweep 1: kind::f16 with bf16 inputs (format 1), fp32 accumulator, N = 128
-constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kHd >> 3) << 17) |
-                              ((uint32_t)(kBq >> 4) << 24);
 
-// D[tmem] (+)= A[tmem] * B[smem]^T, tf32: the A operand (row i in lane i, K along the columns)
-// is read from tensor memory.
-__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
+// The power of two that brings a magnitude with these fp32 bits to [2^14, 2^15), as an exponent;
+// 0 for zero, subnormal, infinite or NaN magnitudes, and limited so that 2^sh is a normal float.
+__host__ __device__ __forceinline__ int operand_shift(uint32_t absbits) {
+  const int e = (int)(absbits >> 23) & 0xff;
+  if (e == 0 || e == 255) return 0;
+  const int sh = kOperandTop - (e - 127);
+  return sh < -100 ? -100 : (sh > 100 ? 100 : sh);
 }
-// The same with bf16 operands (two K elements per 32-bit column of the A operand).
-__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+__device__ __forceinline__ float pow2f(int sh) {  // |sh| <= 126
+  return __uint_as_float((uint32_t)(127 + sh) << 23);
+}
+// x -> the fp16 pair (hi, lo) of two scaled values, lower index in the low half
+__device__ __forceinline__ void split_f16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  const __half2 h = __floats2half2_rn(x0, x1);
+  const float2 f = __half22float2(h);
+  const __half2 l = __floats2half2_rn(__fsub_rn(x0, f.x), __fsub_rn(x1, f.y));
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]^T, kind::f16: the A operand (row i in lane i, two K elements per
+// 32-bit column, the lower index in the low half) is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -108,6 +133,8 @@ __device__ __forceinline__ void tmem_st_wait() {
 struct SdpaArgs {
   const float* q;   // [Lq, C]
   float* out;       // [Lq, C]
+  const uint32_t* absmax;  // fp32 bits of max |k| and max |v|
+  uint8_t* redo;           // [Lq, heads], zero on entry: 1 = recompute this row in plain fp32
   int64_t Lq, Lk, C;
   int heads;
   float scale_log2e;  // (1 / sqrt(head_dim)) * log2(e)
@@ -115,10 +142,8 @@ struct SdpaArgs {
 };
 
 __global__ void __launch_bounds__(kAThreads, 1)
-    sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hib128,
-                   const __grid_constant__ CUtensorMap tmap_k_hi,
-                   const __grid_constant__ CUtensorMap tmap_k_hib,
-                   const __grid_constant__ CUtensorMap tmap_k_lob,
+    sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi,
+                   const __grid_constant__ CUtensorMap tmap_k_lo,
                    const __grid_constant__ CUtensorMap tmap_vt_hi,
                    const __grid_constant__ CUtensorMap tmap_vt_lo,
                    const __grid_constant__ CUtensorMap tmap_out, SdpaArgs g) {
@@ -126,8 +151,9 @@ __global__ void __launch_bounds__(kAThreads, 1)
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t smem_staging = base + kAStages * kAStageBytes;
-  uint8_t* book = smem + kAStages * kAStageBytes + 8 * 4096;
+  const uint32_t smem_v = base + kAStages * kKStageBytes;   // the v^T ring follows the k ring
+  const uint32_t smem_staging = base + kARingBytes;
+  uint8_t* book = smem + kARingBytes + 8 * 4096;
   // row maxima and row sums of the two softmax groups, then the barriers
   float* x_max = reinterpret_cast<float*>(book);          // [2][128]
   float* x_sum = reinterpret_cast<float*>(book + 1024);   // [2][128]
@@ -136,17 +162,16 @@ __global__ void __launch_bounds__(kAThreads, 1)
   const uint32_t bar_full = bar0;               // [2]  k ring: TMA bytes landed
   const uint32_t bar_empty = bar0 + 16;         // [2]  k ring: stage read by its last MMA
   const uint32_t bar_sfull = bar0 + 32;         // [2]  scores of a block complete
-  const uint32_t bar_s1free = bar0 + 48;        // [2]  sweep 1: scores read by the softmax group
+  const uint32_t bar_s1free = bar0 + 48;        // [2]  sweep 1: scores read by the softmax groups
   const uint32_t bar_pready = bar0 + 64;        // [2]  sweep 2: weights written over the scores
   const uint32_t bar_pvdone = bar0 + 80;        // [2]  sweep 2: P*V of a block complete
   const uint32_t bar_qready = bar0 + 96;        // Q planes in tensor memory
   const uint32_t bar_mready = bar0 + 104;       // both groups published their row maxima
   const uint32_t bar_lready = bar0 + 112;       // both groups published their row sums
   const uint32_t bar_ofull = bar0 + 120;        // every MMA of the work item complete
-  const uint32_t bar_ofree = bar0 + 128;        // O read out: the next item may overwrite it
-  const uint32_t bar_vfull = bar0 + 136;        // [2]  v^T ring
-  const uint32_t bar_vempty = bar0 + 152;       // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  const uint32_t bar_vfull = bar0 + 128;        // [2]  v^T ring
+  const uint32_t bar_vempty = bar0 + 144;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (base - raw > (uint32_t)kAAlignSlack) {
@@ -158,7 +183,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqt = (int)((g.Lq + kBq - 1) / kBq);
   const int nblk = (int)((g.Lk + kBkv - 1) / kBkv);
-  const int nblk1 = (int)((g.Lk + 2 * kBkv - 1) / (2 * kBkv));  // sweep 1 walks 128 keys at a time
+  // the last block's second half of v^T is skipped when no key falls into it
+  const int last_halves = g.Lk - (int64_t)(nblk - 1) * kBkv > kVKeys ? 2 : 1;
   const int num_items = nqt * g.heads;
 
   if (threadIdx.x == 0) {
@@ -176,14 +202,11 @@ __global__ void __launch_bounds__(kAThreads, 1)
     mbar_init(bar_mready, 8);
     mbar_init(bar_lready, 8);
     mbar_init(bar_ofull, 1);
-    mbar_init(bar_ofree, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    prefetch_tmap(&tmap_k_hib128);
     prefetch_tmap(&tmap_k_hi);
-    prefetch_tmap(&tmap_k_hib);
-    prefetch_tmap(&tmap_k_lob);
+    prefetch_tmap(&tmap_k_lo);
     prefetch_tmap(&tmap_vt_hi);
     prefetch_tmap(&tmap_vt_lo);
     prefetch_tmap(&tmap_out);
@@ -199,58 +222,47 @@ __global__ void __launch_bounds__(kAThreads, 1)
 
   if (warp == 0) {
     if (lane == 0) {
-      // ------------------------------------------------ TMA producer of k
+      // ------------------------------------------------ TMA producer of k: per plane two boxes of
+      // 128 keys x 64 dims
       const uint64_t keep = policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int h = item / nqt;
-        // sweep 1: bf16(k_hi) only, 128 keys per stage (two boxes of 128 keys x 64 dims)
-        for (int j = 0; j < nblk1; j++) {
-          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 1);
-          if (!ok) break;
-          const uint32_t full = bar_full + 8 * stage;
-          const uint32_t st = base + stage * kKStageBytes;
-          mbar_expect_tx(full, 2 * kKbTile);
-          for (int i = 0; i < 2; i++)
-            tma_load_2d_hint(st + i * 16384, &tmap_k_hib128, full, h * kHd + 64 * i, j * 2 * kBkv, keep);
-          if (++stage == kAStages) { stage = 0; phase ^= 1u; }
-        }
-        // sweep 2: k_hi (boxes of 64 keys x 32 dims), bf16(k_hi) and bf16(k_lo) (boxes of 64 keys
-        // x 64 dims)
-        for (int j = 0; ok && j < nblk; j++) {
-          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 2);
-          if (!ok) break;
-          const uint32_t full = bar_full + 8 * stage;
-          const uint32_t st = base + stage * kKStageBytes;
-          mbar_expect_tx(full, kKStageBytes);
-          for (int i = 0; i < 4; i++)
-            tma_load_2d_hint(st + i * 8192, &tmap_k_hi, full, h * kHd + 32 * i, j * kBkv, keep);
-          for (int i = 0; i < 2; i++) {
-            tma_load_2d_hint(st + kKTile + i * 8192, &tmap_k_hib, full, h * kHd + 64 * i, j * kBkv, keep);
-            tma_load_2d_hint(st + kKTile + kKbTile + i * 8192, &tmap_k_lob, full, h * kHd + 64 * i, j * kBkv, keep);
+        for (int sweep = 0; ok && sweep < 2; sweep++) {
+          for (int j = 0; j < nblk; j++) {
+            ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | (1 + sweep));
+            if (!ok) break;
+            const uint32_t full = bar_full + 8 * stage;
+            const uint32_t st = base + stage * kKStageBytes;
+            mbar_expect_tx(full, sweep ? kKStageBytes : kKPlane);
+            for (int i = 0; i < 2; i++) {
+              tma_load_2d_hint(st + i * 16384, &tmap_k_hi, full, h * kHd + 64 * i, j * kBkv, keep);
+              if (sweep) tma_load_2d_hint(st + kKPlane + i * 16384, &tmap_k_lo, full, h * kHd + 64 * i, j * kBkv, keep);
+            }
+            if (++stage == kAStages) { stage = 0; phase ^= 1u; }
           }
-          if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 10) {
     if (lane == 0) {
       // ------------------------------------------------ TMA producer of v^T (sweep 2 only):
-      // the two bf16 planes, one box of 128 dims x 64 keys each
+      // the two fp16 planes, one box of 128 dims x 64 keys each per stage
       const uint64_t keep = policy_evict_last();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int h = item / nqt;
-        for (int j = 0; j < nblk; j++) {
+        const int nhalf = 2 * (nblk - 1) + last_halves;
+        for (int j = 0; j < nhalf; j++) {
           ok = mbar_wait(bar_vempty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | 3);
           if (!ok) break;
           const uint32_t full = bar_vfull + 8 * stage;
-          const uint32_t st = base + kAStages * kKStageBytes + stage * kVTile;
-          mbar_expect_tx(full, kVTile);
-          tma_load_2d_hint(st, &tmap_vt_hi, full, j * kBkv, h * kHd, keep);
-          tma_load_2d_hint(st + 16384, &tmap_vt_lo, full, j * kBkv, h * kHd, keep);
+          const uint32_t st = smem_v + stage * kVStageBytes;
+          mbar_expect_tx(full, kVStageBytes);
+          tma_load_2d_hint(st, &tmap_vt_hi, full, j * kVKeys, h * kHd, keep);
+          tma_load_2d_hint(st + kVPlane, &tmap_vt_lo, full, j * kVKeys, h * kHd, keep);
           if (++stage == kAStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -263,43 +275,21 @@ __global__ void __launch_bounds__(kAThreads, 1)
       // the CTA's whole run sits in stage seq & 1, whose full barrier completes its phase
       // (seq >> 1) & 1 for it.
       const uint32_t par = warp == 1 ? 0u : 1u;
+      const uint32_t d = tmem_base + kColS + par * kBkv;
       uint32_t sfree_ph = 0;                    // completed phases of s1free[par]
       uint32_t pv_ph = 0;                       // completed phases of pvdone[par]
-      uint32_t q_ph = 0, m_ph = 0, ofree_ph = 0;
+      uint32_t q_ph = 0, m_ph = 0;
       uint32_t seq0 = 0;                        // k-ring sequence number of the item's first block
       bool ok = true;
-      // scores of a block from the operands in `st`: the two small cross terms first (bf16, 16
-      // dims per instruction), then the large term (tf32, 8 dims per instruction)
-      auto issue_scores = [&](uint32_t st) {
-        const uint32_t d = tmem_base + kColS + par * kBkv;
-#pragma unroll
-        for (int ks = 0; ks < kHd / 16; ks++) {
-          const uint32_t off = (uint32_t)((ks >> 2) * 8192);
-          const uint64_t adv = (uint64_t)((ks & 3) * 2);
-          const uint64_t k_hib = make_smem_desc(st + kKTile + off) + adv;
-          const uint64_t k_lob = make_smem_desc(st + kKTile + kKbTile + off) + adv;
-          umma_bf16_ts(d, tmem_base + kColQloB + ks * 8, k_hib, kIdescSb, (uint32_t)(ks != 0));
-          umma_bf16_ts(d, tmem_base + kColQhiB + ks * 8, k_lob, kIdescSb, 1u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < kHd / 8; ks++) {
-          const uint64_t k_hi = make_smem_desc(st + (uint32_t)((ks >> 2) * 8192)) + (uint64_t)((ks & 3) * 2);
-          umma_tf32_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescS, 1u);
-        }
-      };
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         ok = mbar_wait_spin(bar_qready, q_ph, abort_flag, g.status, 0x900 | 1);
         q_ph ^= 1u;
         if (!ok) break;
-        // the previous item's O has been read out: sweep 1 borrows its columns
-        ok = mbar_wait_spin(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
-        ofree_ph ^= 1u;
-        if (!ok) break;
         tc_fence_after();
-        // ---- sweep 1: bf16 scores for the row maxima (8 mantissa bits are ample for an offset),
-        // 128 keys and 16 dims per MMA; the even blocks go to the score columns (384..511), the
-        // odd ones to the idle O columns (256..383)
-        for (int j = (int)par; j < nblk1; j += 2) {
+        // ---- sweep 1: hi*hi scores for the row maxima (11 mantissa bits are ample for an
+        // offset), 128 keys and 16 dims per MMA.  (The buffer's last use, the previous item's
+        // weights, was consumed before this lane left that item.)
+        for (int j = (int)par; j < nblk; j += 2) {
           const uint32_t seq = seq0 + (uint32_t)j, stage = seq & 1u;
           ok = mbar_wait_spin(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 2);
           if (!ok) break;
@@ -308,11 +298,10 @@ __global__ void __launch_bounds__(kAThreads, 1)
           sfree_ph ^= 1u;
           tc_fence_after();
           const uint32_t st = base + stage * kKStageBytes;
-          const uint32_t d = tmem_base + (par ? kColO : kColS);
 #pragma unroll
           for (int ks = 0; ks < kHd / 16; ks++) {
-            const uint64_t kd = make_smem_desc(st + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
-            umma_bf16_ts(d, tmem_base + kColQhiB + ks * 8, kd, kIdescPV, (uint32_t)(ks != 0));
+            const uint64_t k_hi = make_smem_desc(st + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
+            umma_f16_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescH, (uint32_t)(ks != 0));
           }
           umma_commit(bar_empty + 8 * stage);
           umma_commit(bar_sfull + 8 * par);
@@ -323,12 +312,13 @@ __global__ void __launch_bounds__(kAThreads, 1)
         m_ph ^= 1u;
         if (!ok) break;
         tc_fence_after();
-        // ---- sweep 2: accurate scores of this lane's blocks.  The buffer is free again when the
-        // P*V of the block two back has consumed its weights; a k stage is released as soon as
-        // the scores that read it are done.
+        // ---- sweep 2: accurate scores of this lane's blocks, three MMAs per 16 dims (the two
+        // small cross terms first).  The buffer is free again when the P*V of the block two back
+        // has consumed its weights; a k stage is released as soon as the scores that read it
+        // are done.
         bool any = false;
         for (int j = (int)par; j < nblk; j += 2) {
-          const uint32_t seq = seq0 + (uint32_t)(nblk1 + j), stage = seq & 1u;
+          const uint32_t seq = seq0 + (uint32_t)(nblk + j), stage = seq & 1u;
           ok = mbar_wait_spin(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 7);
           if (!ok) break;
           if (any) {
@@ -337,7 +327,17 @@ __global__ void __launch_bounds__(kAThreads, 1)
             pv_ph ^= 1u;
           }
           tc_fence_after();
-          issue_scores(base + stage * kKStageBytes);
+          const uint32_t st = base + stage * kKStageBytes;
+#pragma unroll
+          for (int ks = 0; ks < kHd / 16; ks++) {
+            const uint32_t off = (uint32_t)((ks >> 2) * 16384);
+            const uint64_t adv = (uint64_t)((ks & 3) * 2);
+            const uint64_t k_hi = make_smem_desc(st + off) + adv;
+            const uint64_t k_lo = make_smem_desc(st + kKPlane + off) + adv;
+            umma_f16_ts(d, tmem_base + kColQlo + ks * 8, k_hi, kIdescH, (uint32_t)(ks != 0));
+            umma_f16_ts(d, tmem_base + kColQhi + ks * 8, k_lo, kIdescH, 1u);
+            umma_f16_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescH, 1u);
+          }
           umma_commit(bar_empty + 8 * stage);
           umma_commit(bar_sfull + 8 * par);
           any = true;
@@ -348,7 +348,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
           pv_ph ^= 1u;
           if (!ok) break;
         }
-        seq0 += (uint32_t)(nblk1 + nblk);
+        seq0 += (uint32_t)(2 * nblk);
       }
     }
   } else if (warp == 11) {
@@ -358,32 +358,36 @@ __global__ void __launch_bounds__(kAThreads, 1)
       uint32_t pready_ph[2] = {0, 0};
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-        // (O is free: every softmax warp released the previous item's O before it could arrive
+        // (O is free: every softmax warp read the previous item's O out before it could arrive
         // on this item's first pready)
-        for (int j = 0; j < nblk; j++) {
+        for (int j = 0; ok && j < nblk; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
           ok = mbar_wait_spin(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
           if (!ok) break;
           pready_ph[buf] ^= 1u;
-          ok = mbar_wait_spin(bar_vfull + 8 * vstage, vphase, abort_flag, g.status, 0x900 | 11);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t vt = base + kAStages * kKStageBytes + vstage * kVTile;
           const uint32_t pcol = tmem_base + kColS + buf * kBkv;
+          const int halves = j == nblk - 1 ? last_halves : 2;
+          for (int hf = 0; hf < halves; hf++) {
+            ok = mbar_wait_spin(bar_vfull + 8 * vstage, vphase, abort_flag, g.status, 0x900 | 11);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t vt = smem_v + vstage * kVStageBytes;
 #pragma unroll
-          for (int ks = 0; ks < kBkv / 16; ks++) {
-            // 16 keys per kind::f16 instruction = 32 bytes of a v^T row: +2 in the address field.
-            // The weights of keys 16ks.. sit in 8 columns: hi at (ks>>1)*32 + (ks&1)*8, lo 16 further.
-            const uint64_t v_hi = make_smem_desc(vt) + (uint64_t)(ks * 2);
-            const uint64_t v_lo = make_smem_desc(vt + 16384) + (uint64_t)(ks * 2);
-            const uint32_t p_hi = pcol + (uint32_t)((ks >> 1) * 32 + (ks & 1) * 8);
-            umma_bf16_ts(tmem_base + kColO, p_hi + 16, v_hi, kIdescPV, (uint32_t)((j | ks) != 0));
-            umma_bf16_ts(tmem_base + kColO, p_hi, v_lo, kIdescPV, 1u);
-            umma_bf16_ts(tmem_base + kColO, p_hi, v_hi, kIdescPV, 1u);
+            for (int ks = 0; ks < kVKeys / 16; ks++) {
+              // 16 keys per instruction = 32 bytes of a v^T row: +2 in the address field.  The
+              // weights of the block's keys 32c + 16i .. sit in 8 columns: hi at 32c + 8i, lo 16 further.
+              const uint64_t v_hi = make_smem_desc(vt) + (uint64_t)(ks * 2);
+              const uint64_t v_lo = make_smem_desc(vt + kVPlane) + (uint64_t)(ks * 2);
+              const uint32_t p_hi = pcol + (uint32_t)((hf * 2 + (ks >> 1)) * 32 + (ks & 1) * 8);
+              umma_f16_ts(tmem_base + kColO, p_hi + 16, v_hi, kIdescH, (uint32_t)((j | hf | ks) != 0));
+              umma_f16_ts(tmem_base + kColO, p_hi, v_lo, kIdescH, 1u);
+              umma_f16_ts(tmem_base + kColO, p_hi, v_hi, kIdescH, 1u);
+            }
+            umma_commit(bar_vempty + 8 * vstage);
+            if (++vstage == kAStages) { vstage = 0; vphase ^= 1u; }
           }
-          umma_commit(bar_vempty + 8 * vstage);
+          if (!ok) break;
           umma_commit(bar_pvdone + 8 * buf);
-          if (++vstage == kAStages) { vstage = 0; vphase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(bar_ofull);  // every P*V of the item (and so every MMA before them) is complete
@@ -392,12 +396,13 @@ __global__ void __launch_bounds__(kAThreads, 1)
   } else {
     // -------------------------------------------------- softmax groups + epilogue (8 warps)
     const int quarter = warp & 3;
-    const int grp = (warp - 2) >> 2;        // 0: keys 0..31 of every block, 1: keys 32..63
+    const int grp = (warp - 2) >> 2;        // 0: keys 0..63 of every block, 1: keys 64..127
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
     const uint64_t stream_policy = policy_evict_first();
-    const uint32_t s_col = tmem_base + kColS + (uint32_t)grp * 32 + lane_base;  // + buffer * kBkv
+    const uint32_t s_col = tmem_base + kColS + (uint32_t)grp * 64 + lane_base;  // + buffer * kBkv
+    const int sh_k = operand_shift(g.absmax[0]), sh_v = operand_shift(g.absmax[1]);
     uint32_t sfull_ph[2] = {0, 0};
     uint32_t m_ph = 0, l_ph = 0, ofull_ph = 0;
     bool ok = true;
@@ -405,68 +410,72 @@ __global__ void __launch_bounds__(kAThreads, 1)
       const int h = item / nqt, qt = item - h * nqt;
       const int64_t q0 = (int64_t)qt * kBq;
       const int64_t row = q0 + row_in_tile;
+      const float* qrow = g.q + row * g.C + (int64_t)h * kHd;
+      // the power of two for this thread's query row
+      int sh_q = 0;
+      uint32_t mx = 0;
+      if (row < g.Lq) {
+#pragma unroll 4
+        for (int j = 0; j < kHd; j += 4) {
+          const float4 v = *reinterpret_cast<const float4*>(qrow + j);
+          mx = max(max(mx, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)),
+                   max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
+        }
+        sh_q = operand_shift(mx);
+      }
       if (grp == 0) {
-        // this thread's query row -> tensor memory (zeros past Lq): the tf32 plane q_hi, and
-        // bf16(q - q_hi) and bf16(q_hi) for the cross terms, two elements per column
-        const float* qrow = g.q + row * g.C + (int64_t)h * kHd;
+        // this thread's query row -> tensor memory (zeros past Lq): fp16 hi and lo of
+        // q * 2^sh_q, two elements per column
+        const float qs = pow2f(sh_q);
 #pragma unroll 1
         for (int c = 0; c < kHd / 64; c++) {
-          uint32_t lob[32], hib[32];
-#pragma unroll 1
-          for (int half_c = 0; half_c < 2; half_c++) {
-            uint32_t hi[32];
+          uint32_t hi[32], lo[32];
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (row < g.Lq) v = *reinterpret_cast<const float4*>(qrow + c * 64 + half_c * 32 + j);
-              const float xs[4] = {v.x, v.y, v.z, v.w};
-              float a[4], b[4];
-#pragma unroll
-              for (int t = 0; t < 4; t++) {
-                split_tf32(xs[t], a[t], b[t]);
-                hi[j + t] = __float_as_uint(a[t]);
-              }
-#pragma unroll
-              for (int t = 0; t < 4; t += 2) {
-                const __nv_bfloat162 pl = __floats2bfloat162_rn(b[t], b[t + 1]);  // lower dim in the low half
-                const __nv_bfloat162 ph = __floats2bfloat162_rn(a[t], a[t + 1]);
-                lob[half_c * 16 + ((j + t) >> 1)] = *reinterpret_cast<const uint32_t*>(&pl);
-                hib[half_c * 16 + ((j + t) >> 1)] = *reinterpret_cast<const uint32_t*>(&ph);
-              }
-            }
-            tmem_st_32x32(tmem_base + kColQhi + c * 64 + half_c * 32 + lane_base, hi);
+          for (int j = 0; j < 64; j += 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < g.Lq) v = *reinterpret_cast<const float4*>(qrow + c * 64 + j);
+            split_f16x2(__fmul_rn(v.x, qs), __fmul_rn(v.y, qs), hi[j >> 1], lo[j >> 1]);
+            split_f16x2(__fmul_rn(v.z, qs), __fmul_rn(v.w, qs), hi[(j >> 1) + 1], lo[(j >> 1) + 1]);
           }
-          tmem_st_32x32(tmem_base + kColQloB + c * 32 + lane_base, lob);
-          tmem_st_32x32(tmem_base + kColQhiB + c * 32 + lane_base, hib);
+          tmem_st_32x32(tmem_base + kColQhi + c * 32 + lane_base, hi);
+          tmem_st_32x32(tmem_base + kColQlo + c * 32 + lane_base, lo);
         }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_qready);
       }
-      // ---- sweep 1: the row maximum over this group's blocks (raw dot products)
+      // scores arrive as (q 2^sh_q) . (k 2^sh_k): the factor that turns them into log2 units
+      // (each factor a normal float; the product may round to zero or infinity only where the
+      // reference's own scores leave the fp32 range)
+      const float sc = __fmul_rn(__fmul_rn(g.scale_log2e, pow2f(-sh_q)), pow2f(-sh_k));
+      // ---- sweep 1: the row maximum over this group's half of every block (raw dot products)
       float m = -INFINITY;
-      for (int j = 0; j < nblk1; j++) {
+      for (int j = 0; j < nblk; j++) {
         const uint32_t buf = (uint32_t)(j & 1);
         ok = mbar_wait_warp(bar_sfull + 8 * buf, sfull_ph[buf], abort_flag, g.status, 0xa00 | 1);
         sfull_ph[buf] ^= 1u;
         if (!ok) break;
         tc_fence_after();
-        // this group's 64 of the block's 128 keys
-        const uint32_t x_col = tmem_base + (buf ? kColO : kColS) + (uint32_t)grp * 64 + lane_base;
+        const uint32_t x_col = s_col + buf * kBkv;
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(x_col, r0);
         tmem_ld_32x32(x_col + 32, r1);
         tmem_ld_wait();
-        const int64_t key0 = (int64_t)j * 2 * kBkv + grp * 64;
-#pragma unroll
-        for (int t = 0; t < 32; t++) {
-          if (key0 + t < g.Lk) m = fmaxf(m, __uint_as_float(r0[t]));
-          if (key0 + 32 + t < g.Lk) m = fmaxf(m, __uint_as_float(r1[t]));
-        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_s1free + 8 * buf);
+        const int64_t key0 = (int64_t)j * kBkv + grp * 64;
+        if (key0 + 64 <= g.Lk) {
+#pragma unroll
+          for (int t = 0; t < 32; t++) m = fmaxf(m, fmaxf(__uint_as_float(r0[t]), __uint_as_float(r1[t])));
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; t++) {
+            if (key0 + t < g.Lk) m = fmaxf(m, __uint_as_float(r0[t]));
+            if (key0 + 32 + t < g.Lk) m = fmaxf(m, __uint_as_float(r1[t]));
+          }
+        }
       }
       if (!ok) break;
       x_max[grp * kBq + row_in_tile] = m;
@@ -476,44 +485,48 @@ __global__ void __launch_bounds__(kAThreads, 1)
       m_ph ^= 1u;
       if (!ok) break;
       m = fmaxf(x_max[row_in_tile], x_max[kBq + row_in_tile]);
-      // ---- sweep 2: weights p = exp((s - m) * scale), rounded to tf32, written over the scores
+      // ---- sweep 2: weights p = 2^10 exp2((s - m) * sc) as fp16 pairs, written over the scores
+      const float e_off = __fsub_rn(kPShift, __fmul_rn(m, sc));
       float l = 0.0f;
+      uint32_t hmax = 0;   // largest fp16 bit patterns of the weights' hi parts (two halves)
       for (int j = 0; j < nblk; j++) {
         const uint32_t buf = (uint32_t)(j & 1);
         ok = mbar_wait_warp(bar_sfull + 8 * buf, sfull_ph[buf], abort_flag, g.status, 0xa00 | 3);
         sfull_ph[buf] ^= 1u;
         if (!ok) break;
         tc_fence_after();
-        {
-          uint32_t r[32];
-          tmem_ld_32x32(s_col + buf * kBkv, r);
-          tmem_ld_wait();
-          const int64_t key0 = (int64_t)j * kBkv + grp * 32;
-          const int valid = (int)min((int64_t)32, g.Lk - key0);  // < 32 only in the last block
-          // this group's 32 columns become: 16 columns of bf16 pairs p_hi, then 16 of p_lo.
-          // Two weights at a time: one cvt packs the pair of high parts, whose fp32 values are
-          // the two halves of that word shifted up; the low parts are what is left, packed by a
-          // second cvt.  The row sum adds the weights themselves (they differ from hi + lo by
-          // 2^-17 at most).
-          uint32_t w[32];
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(s_col + buf * kBkv, r0);
+        tmem_ld_32x32(s_col + buf * kBkv + 32, r1);
+        tmem_ld_wait();
+        const int64_t key0 = (int64_t)j * kBkv + grp * 64;
+        const int valid = (int)min((int64_t)64, g.Lk - key0);  // < 64 only in the last block
+        // each 32 columns become: 16 columns of fp16 pairs p_hi, then 16 of p_lo.  The row sum
+        // adds the weights themselves (they differ from hi + lo by 2^-22 at most).
+        auto weights = [&](const uint32_t (&r)[32], int first, uint32_t (&w)[32]) {
 #pragma unroll
           for (int t = 0; t < 32; t += 2) {
-            float p0 = 0.0f, p1 = 0.0f;
-            const float e0 = __fmul_rn(__fsub_rn(__uint_as_float(r[t]), m), g.scale_log2e);
-            const float e1 = __fmul_rn(__fsub_rn(__uint_as_float(r[t + 1]), m), g.scale_log2e);
+            float p0, p1;
+            const float e0 = fminf(__fmaf_rn(__uint_as_float(r[t]), sc, e_off), 15.98f);
+            const float e1 = fminf(__fmaf_rn(__uint_as_float(r[t + 1]), sc, e_off), 15.98f);
             asm("ex2.approx.f32 %0, %1;" : "=f"(p0) : "f"(e0));
             asm("ex2.approx.f32 %0, %1;" : "=f"(p1) : "f"(e1));
-            if (t >= valid) p0 = 0.0f;
-            if (t + 1 >= valid) p1 = 0.0f;
+            if (first + t >= valid) p0 = 0.0f;
+            if (first + t + 1 >= valid) p1 = 0.0f;
             l += __fadd_rn(p0, p1);
             uint32_t hi2, lo2;
-            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi2) : "f"(p1), "f"(p0));  // first source -> upper half
-            const float h0 = __uint_as_float(hi2 << 16), h1 = __uint_as_float(hi2 & 0xffff0000u);
-            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo2) : "f"(__fsub_rn(p1, h1)), "f"(__fsub_rn(p0, h0)));
+            split_f16x2(p0, p1, hi2, lo2);
+            hmax = __vmaxu2(hmax, hi2);
             w[t >> 1] = hi2;
             w[16 + (t >> 1)] = lo2;
           }
+        };
+        {
+          uint32_t w[32];
+          weights(r0, 0, w);
           tmem_st_32x32(s_col + buf * kBkv, w);
+          weights(r1, 32, w);
+          tmem_st_32x32(s_col + buf * kBkv + 32, w);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -528,7 +541,14 @@ __global__ void __launch_bounds__(kAThreads, 1)
       l_ph ^= 1u;
       if (!ok) break;
       l = x_sum[row_in_tile] + x_sum[kBq + row_in_tile];
-      const float inv = __fdiv_rn(1.0f, l);
+      // head_dim * max|q_row| * max|k| bounds sum |q_d k_d|, here in log2 units of the weights
+      const float bound = __fmul_rn(__fmul_rn(__uint_as_float(mx), __uint_as_float(g.absmax[0])),
+                                    (float)kHd * g.scale_log2e);
+      if (row < g.Lq && (max(hmax & 0xffffu, hmax >> 16) >= kPHalfTop || !(l >= kRowSumFloor) ||
+                         !(bound <= kScoreBound)))
+        g.redo[row * g.heads + h] = 1;   // offset too far from the row's maximum, or scores too large
+      // O holds sum p 2^10 (v 2^sh_v): divide by the row sum of p 2^10 and take v's power back out
+      const float inv = __fmul_rn(__fdiv_rn(1.0f, l), pow2f(-sh_v));
       // ---- epilogue: O / l, this group's two 32-column chunks
       ok = mbar_wait_warp(bar_ofull, ofull_ph, abort_flag, g.status, 0xa00 | 5);
       ofull_ph ^= 1u;
@@ -553,9 +573,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
           bulk_commit();
         }
       }
+      // (the reads of O are complete: the next item's first pready arrival tells the P*V issuer)
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ofree);
     }
   }
 
@@ -574,27 +593,50 @@ __global__ void __launch_bounds__(kAThreads, 1)
   }
 }
 
-// k -> the tf32 plane k_hi and, for the cross terms, bf16(k_hi) and bf16(k - k_hi).
-__global__ void __launch_bounds__(256) split_planes_kernel(const float* __restrict__ x, int64_t n,
-                                                           float* __restrict__ hi,
-                                                           __nv_bfloat16* __restrict__ hib,
-                                                           __nv_bfloat16* __restrict__ lob) {
+// Largest magnitudes of k and of v (as fp32 bit patterns, which order like the magnitudes) into
+// out[0] and out[1]; out starts at zero.
+__global__ void __launch_bounds__(256) absmax_pair_kernel(const float* __restrict__ k,
+                                                          const float* __restrict__ v, int64_t n,
+                                                          uint32_t* __restrict__ out) {
+  uint32_t mk = 0, mv = 0;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
-    float a, b;
-    split_tf32(x[i], a, b);
-    hi[i] = a;
-    hib[i] = __float2bfloat16_rn(a);
-    lob[i] = __float2bfloat16_rn(b);
+    mk = max(mk, __float_as_uint(fabsf(k[i])));
+    mv = max(mv, __float_as_uint(fabsf(v[i])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mk = max(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+    mv = max(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicMax(out, mk);
+    atomicMax(out + 1, mv);
   }
 }
 
-// v [Lk, C] -> two bf16 planes of v^T, each [C, ld] (ld >= Lk, a multiple of 8; the padding is
-// zero): hi = bf16(v), lo = bf16(v - hi).
-__global__ void __launch_bounds__(256) transpose_split_bf16_kernel(const float* __restrict__ v, int64_t Lk,
-                                                                   int64_t C, int64_t ld,
-                                                                   __nv_bfloat16* __restrict__ vt_hi,
-                                                                   __nv_bfloat16* __restrict__ vt_lo) {
+// k -> fp16 hi and lo planes of k * 2^sh (sh from the absmax pass).
+__global__ void __launch_bounds__(256) split_planes_kernel(const float* __restrict__ x, int64_t n,
+                                                           const uint32_t* __restrict__ absmax,
+                                                           __half* __restrict__ hi,
+                                                           __half* __restrict__ lo) {
+  const float sc = pow2f(operand_shift(absmax[0]));
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const float xs = __fmul_rn(x[i], sc);
+    const __half h = __float2half_rn(xs);
+    hi[i] = h;
+    lo[i] = __float2half_rn(__fsub_rn(xs, __half2float(h)));
+  }
+}
+
+// v [Lk, C] -> two fp16 planes of (v * 2^sh)^T, each [C, ld] (ld >= Lk, a multiple of 8; the
+// padding is zero): hi = fp16(.), lo = fp16(. - hi).
+__global__ void __launch_bounds__(256) transpose_split_f16_kernel(const float* __restrict__ v, int64_t Lk,
+                                                                  int64_t C, int64_t ld,
+                                                                  const uint32_t* __restrict__ absmax,
+                                                                  __half* __restrict__ vt_hi,
+                                                                  __half* __restrict__ vt_lo) {
   __shared__ float tile[32][33];
+  const float sc = pow2f(operand_shift(absmax[1]));
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t k0 = (int64_t)blockIdx.y * 32, c0 = (int64_t)blockIdx.x * 32;
   for (int r = ty; r < 32; r += 8)
@@ -602,26 +644,28 @@ __global__ void __launch_bounds__(256) transpose_split_bf16_kernel(const float* 
   __syncthreads();
   for (int r = ty; r < 32; r += 8) {
     if (c0 + r < C && k0 + tx < ld) {
-      const float x = tile[tx][r];
-      const __nv_bfloat16 h = __float2bfloat16_rn(x);
-      const float rest = isfinite(x) ? __fsub_rn(x, __bfloat162float(h)) : 0.0f;
+      const float x = __fmul_rn(tile[tx][r], sc);
+      const __half h = __float2half_rn(x);
+      const float rest = isfinite(x) ? __fsub_rn(x, __half2float(h)) : 0.0f;
       vt_hi[(c0 + r) * ld + k0 + tx] = h;
-      vt_lo[(c0 + r) * ld + k0 + tx] = __float2bfloat16_rn(rest);
+      vt_lo[(c0 + r) * ld + k0 + tx] = __float2half_rn(rest);
     }
   }
 }
 
 // Any head_dim / alignment: one warp per (query row, head), exact fp32 on the CUDA cores, three
-// passes over the keys (maximum, sum, weighted values).
+// passes over the keys (maximum, sum, weighted values).  With `only`, just the marked rows.
 __global__ void __launch_bounds__(256) sdpa_simt_kernel(const float* __restrict__ q,
                                                         const float* __restrict__ k,
                                                         const float* __restrict__ v, int64_t Lq,
                                                         int64_t Lk, int64_t C, int heads,
-                                                        float scale, float* __restrict__ out) {
+                                                        float scale, float* __restrict__ out,
+                                                        const uint8_t* __restrict__ only) {
   const int lane = threadIdx.x & 31;
   const int64_t hd = C / heads;
   const int64_t warps = (int64_t)gridDim.x * 8;
   for (int64_t it = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); it < Lq * heads; it += warps) {
+    if (only && !only[it]) continue;   // (marks are indexed like `it`: row * heads + head)
     const int64_t i = it / heads, h = it - i * heads;
     const float* qi = q + i * C + h * hd;
     auto score = [&](int64_t t) {
@@ -648,13 +692,13 @@ __global__ void __launch_bounds__(256) sdpa_simt_kernel(const float* __restrict_
   }
 }
 
-// v^T plane [C, ld] bf16, box = 128 rows x 64 keys (128 bytes), 128-byte swizzle.
+// v^T plane [C, ld] fp16, box = 128 rows x 64 keys (128 bytes), 128-byte swizzle.
 bool make_tmap_vt(CUtensorMap* map, const void* ptr, int64_t C, int64_t Lk, int64_t ld, std::string* why) {
   cuuint64_t dims[2] = {(cuuint64_t)Lk, (cuuint64_t)C};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kBkv, (cuuint32_t)kHd};
+  cuuint32_t box[2] = {(cuuint32_t)kVKeys, (cuuint32_t)kHd};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -664,33 +708,17 @@ bool make_tmap_vt(CUtensorMap* map, const void* ptr, int64_t C, int64_t Lk, int6
   return true;
 }
 
-// bf16 plane of k [Lk, C], box = box_keys keys x 64 dims (128 bytes), 128-byte swizzle.
-bool make_tmap_kb(CUtensorMap* map, const void* ptr, int64_t Lk, int64_t C, int box_keys, std::string* why) {
+// fp16 plane of k [Lk, C], box = 128 keys x 64 dims (128 bytes), 128-byte swizzle.
+bool make_tmap_k(CUtensorMap* map, const void* ptr, int64_t Lk, int64_t C, std::string* why) {
   cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)Lk};
   cuuint64_t strides[1] = {(cuuint64_t)C * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_keys};
+  cuuint32_t box[2] = {64, (cuuint32_t)kBkv};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    if (why) *why = "cuTensorMapEncodeTiled(bf16 k plane) failed with CUresult " + std::to_string((int)r);
-    return false;
-  }
-  return true;
-}
-
-bool make_tmap_2d_f32(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t pitch_elems,
-                      int box_rows, std::string* why) {
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * 4};
-  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides,
-                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    if (why) *why = "cuTensorMapEncodeTiled(attention operand) failed with CUresult " + std::to_string((int)r);
+    if (why) *why = "cuTensorMapEncodeTiled(fp16 k plane) failed with CUresult " + std::to_string((int)r);
     return false;
   }
   return true;
@@ -708,9 +736,10 @@ int sdpa_setup(std::string* why) {
   return SDQ_OK;
 }
 
-size_t sdpa_scratch_bytes(int64_t Lk, int64_t C) {
+size_t sdpa_scratch_bytes(int64_t Lq, int64_t Lk, int64_t C, int heads) {
   const int64_t ld = (Lk + 7) / 8 * 8;
-  return (size_t)(Lk * C) * 4 + (size_t)(2 * Lk * C + 2 * C * ld) * 2;  // k_hi fp32; k and v^T hi, lo bf16
+  // the two maxima; k and v^T hi, lo fp16; one mark per (query row, head)
+  return 16 + (size_t)(2 * Lk * C + 2 * C * ld) * 2 + (size_t)(Lq * heads);
 }
 
 cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk,
@@ -728,38 +757,48 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
     int64_t blocks = (Lq * heads + 7) / 8;
     if (blocks > (int64_t)sm_count * 8) blocks = (int64_t)sm_count * 8;
     count_launch();
-    sdpa_simt_kernel<<<(unsigned)blocks, 256, 0, s>>>(q, k, v, Lq, Lk, C, heads, scale, out);
+    sdpa_simt_kernel<<<(unsigned)blocks, 256, 0, s>>>(q, k, v, Lq, Lk, C, heads, scale, out, nullptr);
     return cudaGetLastError();
   }
   const int64_t ld = (Lk + 7) / 8 * 8;
-  float* k_hi = scratch;
-  __nv_bfloat16* k_hib = reinterpret_cast<__nv_bfloat16*>(scratch + Lk * C);
-  __nv_bfloat16* k_lob = k_hib + Lk * C;
-  __nv_bfloat16* vt_hi = k_lob + Lk * C;
-  __nv_bfloat16* vt_lo = vt_hi + C * ld;
+  uint32_t* absmax = reinterpret_cast<uint32_t*>(scratch);
+  __half* k_hi = reinterpret_cast<__half*>(scratch + 4);
+  __half* k_lo = k_hi + Lk * C;
+  __half* vt_hi = k_lo + Lk * C;
+  __half* vt_lo = vt_hi + C * ld;
+  uint8_t* redo = reinterpret_cast<uint8_t*>(vt_lo + C * ld);
+  cudaError_t e = cudaMemsetAsync(absmax, 0, 16, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(redo, 0, (size_t)(Lq * heads), s);
+  if (e != cudaSuccess) return e;
   int64_t blocks = (Lk * C + 255) / 256;
   if (blocks > (int64_t)sm_count * 16) blocks = (int64_t)sm_count * 16;
-  count_launch(2);
-  split_planes_kernel<<<(unsigned)blocks, 256, 0, s>>>(k, Lk * C, k_hi, k_hib, k_lob);
+  count_launch(3);
+  absmax_pair_kernel<<<(unsigned)blocks, 256, 0, s>>>(k, v, Lk * C, absmax);
+  split_planes_kernel<<<(unsigned)blocks, 256, 0, s>>>(k, Lk * C, absmax, k_hi, k_lo);
   dim3 tgrid((unsigned)((C + 31) / 32), (unsigned)((ld + 31) / 32));
-  transpose_split_bf16_kernel<<<tgrid, 256, 0, s>>>(v, Lk, C, ld, vt_hi, vt_lo);
-  cudaError_t e = cudaGetLastError();
+  transpose_split_f16_kernel<<<tgrid, 256, 0, s>>>(v, Lk, C, ld, absmax, vt_hi, vt_lo);
+  e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  CUtensorMap t_khi128, t_khi, t_khib, t_klob, t_vt_hi, t_vt_lo, t_out;
-  if (!make_tmap_kb(&t_khi128, k_hib, Lk, C, 2 * kBkv, why) ||
-      !make_tmap_2d_f32(&t_khi, k_hi, Lk, C, C, kBkv, why) || !make_tmap_kb(&t_khib, k_hib, Lk, C, kBkv, why) ||
-      !make_tmap_kb(&t_klob, k_lob, Lk, C, kBkv, why) ||
+  CUtensorMap t_khi, t_klo, t_vt_hi, t_vt_lo, t_out;
+  if (!make_tmap_k(&t_khi, k_hi, Lk, C, why) || !make_tmap_k(&t_klo, k_lo, Lk, C, why) ||
       !make_tmap_vt(&t_vt_hi, vt_hi, C, Lk, ld, why) || !make_tmap_vt(&t_vt_lo, vt_lo, C, Lk, ld, why) ||
       !make_out_tmap(&t_out, out, Lq, C, why))
     return cudaErrorInvalidValue;
   SdpaArgs g;
-  g.q = q; g.out = out; g.Lq = Lq; g.Lk = Lk; g.C = C; g.heads = heads;
+  g.q = q; g.out = out; g.absmax = absmax; g.redo = redo; g.Lq = Lq; g.Lk = Lk; g.C = C; g.heads = heads;
   g.scale_log2e = scale * 1.4426950408889634f;
   g.status = status;
   const int64_t items = ((Lq + kBq - 1) / kBq) * heads;
   count_launch();
   sdpa_tc_kernel<<<(unsigned)(items < sm_count ? items : sm_count), kAThreads, kASmemBytes, s>>>(
-      t_khi128, t_khi, t_khib, t_klob, t_vt_hi, t_vt_lo, t_out, g);
+      t_khi, t_klo, t_vt_hi, t_vt_lo, t_out, g);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  // rows whose offset was too far off (none on ordinary data): exact fp32 on the CUDA cores
+  int64_t rblocks = (Lq * heads + 7) / 8;
+  if (rblocks > (int64_t)sm_count * 8) rblocks = (int64_t)sm_count * 8;
+  count_launch();
+  sdpa_simt_kernel<<<(unsigned)rblocks, 256, 0, s>>>(q, k, v, Lq, Lk, C, heads, scale, out, redo);
   return cudaGetLastError();
 }
 

@@ -39,7 +39,7 @@ struct Workspace {
   int32_t* acc = nullptr; size_t acc_bytes = 0;   // split-K partial sums
   float2* ln_stats = nullptr; size_t ln_stats_bytes = 0;  // per-row mean and 1/sqrt(var+eps)
   float* f_split = nullptr; size_t f_split_bytes = 0;     // tf32 planes of the fp32 activations
-  float* attn = nullptr; size_t attn_bytes = 0;           // attention: tf32 planes of k, v^T
+  float* attn = nullptr; size_t attn_bytes = 0;           // attention: fp16 planes of k, v^T
 };
 
 struct Context {
@@ -639,7 +639,7 @@ int sdq_sdpa(const float* q_dev, const float* k_dev, const float* v_dev, int64_t
     std::lock_guard<std::mutex> lk(g_ctx->mu);
     ws = &g_ctx->ws[s];
   }
-  if (int rc = grow(&ws->attn, &ws->attn_bytes, sdpa_scratch_bytes(Lk, C) + 16)) return rc;
+  if (int rc = grow(&ws->attn, &ws->attn_bytes, sdpa_scratch_bytes(Lq, Lk, C, heads) + 16)) return rc;
   std::string why;
   cudaError_t e = launch_sdpa(q_dev, k_dev, v_dev, Lq, Lk, C, heads, out_dev, ws->attn, g_ctx->status, flags,
                               g_ctx->sm_count, s, &why);

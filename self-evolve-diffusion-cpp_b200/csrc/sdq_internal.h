@@ -97,7 +97,7 @@ cudaError_t launch_fmatmul(const float* a, int64_t M, int64_t K, const float* w_
 
 // ---- exact-softmax attention (blk::sdpa) on tcgen05: sdpa_tcgen05.cu ----
 int sdpa_setup(std::string* why);
-size_t sdpa_scratch_bytes(int64_t Lk, int64_t C);  // tf32 planes of k and the transposed v
+size_t sdpa_scratch_bytes(int64_t Lq, int64_t Lk, int64_t C, int heads);  // fp16 planes of k and v^T, per-row redo marks
 // out[Lq,C] = softmax(q k^T / sqrt(C/heads)) v per head; q [Lq,C], k and v [Lk,C], all device fp32.
 cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t Lq, int64_t Lk,
                         int64_t C, int heads, float* out, float* scratch, int* status,

@@ -1,9 +1,9 @@
 """GPU: exact-softmax attention (blk::sdpa) against the reference's outputs and the restatement.
 
 The reference gates attention like its other fp32 kernels: max-abs error <= 1e-3 of the largest
-output.  The tensor-core path computes the scores with three tf32 products per fp32 product and
-P*V with three bf16 products on two-term splits of the weights and of v; measured errors are
-~1e-5 at a few thousand keys and 1.3e-4 at 27280 keys (the tensor core's accumulator truncates,
+output.  The tensor-core path splits every operand (times a power of two) into two fp16 numbers
+and computes the scores and P*V with three fp16 products per fp32 product; measured errors are
+~1e-5 at a few thousand keys and ~1e-4 at 27280 keys (the tensor core's accumulator truncates,
 so the error grows with the length of the key range accumulated in it).
 """
 import os
@@ -72,6 +72,37 @@ def test_peaked_and_shifted_scores(sdq):
     want = attention64(q, k, v, heads)
     assert np.isfinite(got).all()
     assert max_rel_err(got, want) < TOL
+
+
+@pytest.mark.parametrize("sq,sk,sv", [
+    (1e4, 1e-4, 1e6),       # magnitudes far outside fp16 on every operand
+    (1e-6, 1e6, 1e-9),
+    (3e-12, 2e-13, 1.0),    # scores ~ 0: uniform weights
+    (30.0, 30.0, 1.0),      # scores ~ 1e4: the first sweep's maxima are off by whole log2 units
+    (300.0, 300.0, 1e20),   # scores ~ 1e6: one key takes each row; rows recomputed in plain fp32
+])
+def test_operand_magnitudes(sdq, sq, sk, sv):
+    """The fp16 planes carry q, k and v times powers of two chosen from the data (per query row,
+    per k, per v), so the magnitudes of the inputs do not matter; rows of very different size
+    sit in one tile.  Where the scores are so large that the first sweep's offset is useless the
+    marked rows come from the fp32 CUDA-core kernel."""
+    rng = np.random.default_rng(5)
+    heads, Lq, Lk = 2, 257, 391
+    C = heads * 128
+    q = (rng.standard_normal((Lq, C)) * sq).astype(np.float32)
+    q[::3] *= 1e-3
+    q[5] = 0.0                                            # a row of zeros: uniform weights
+    k = (rng.standard_normal((Lk, C)) * sk).astype(np.float32)
+    k[::7] *= 1e-4
+    v = (rng.standard_normal((Lk, C)) * sv).astype(np.float32)
+    got = sdq.sdpa_np(q, k, v, heads)
+    want = attention64(q, k, v, heads)
+    assert np.isfinite(got).all()
+    # scores in the thousands show the 22 bits the split operands carry (fp32 dot products have
+    # 24): ~1e-4 at scores ~1e3; beyond ~1e4 the rows are recomputed in plain fp32, whose own
+    # distance from float64 is then the yardstick
+    fp32_err = max_rel_err(sdq.sdpa_np(q, k, v, heads, force_simt=True), want)
+    assert max_rel_err(got, want) < max(3e-4 if sq * sk > 100 else 1e-4, 2 * fp32_err)
 
 
 def test_other_head_sizes_take_the_cuda_core_kernel(sdq):
