@@ -71,7 +71,7 @@ constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte
 constexpr int kASmemBytes = kARingBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
 constexpr uint32_t kColQhi = 0, kColQlo = 64, kColO = 128, kColS = 256;
 constexpr float kPShift = 10.0f;     // the softmax weights are carried as p * 2^10 (<= 2^10 up to
-                                     // the error of the first sweep's maxima; clamped below 2^16)
+                                     // the error of the first sweep's maxima)
 constexpr uint32_t kPHalfTop = 0x7b00;  // fp16 bits of 2^15.8: a weight this large means the first
                                         // sweep's maximum was ~6 log2 units too low
 constexpr float kRowSumFloor = 8.0f;    // a row sum below 2^3 means it was ~7 too high
@@ -502,17 +502,21 @@ __global__ void __launch_bounds__(kAThreads, 1)
         const int64_t key0 = (int64_t)j * kBkv + grp * 64;
         const int valid = (int)min((int64_t)64, g.Lk - key0);  // < 64 only in the last block
         // each 32 columns become: 16 columns of fp16 pairs p_hi, then 16 of p_lo.  The row sum
-        // adds the weights themselves (they differ from hi + lo by 2^-22 at most).
-        auto weights = [&](const uint32_t (&r)[32], int first, uint32_t (&w)[32]) {
+        // adds the weights themselves (they differ from hi + lo by 2^-22 at most).  A weight
+        // beyond fp16's range (offset far too low) becomes an infinity that spoils only its own
+        // row of O, and that row is marked for the fp32 pass by the test on hmax below.
+        auto weights = [&](const uint32_t (&r)[32], int first, bool masked, uint32_t (&w)[32]) {
 #pragma unroll
           for (int t = 0; t < 32; t += 2) {
             float p0, p1;
-            const float e0 = fminf(__fmaf_rn(__uint_as_float(r[t]), sc, e_off), 15.98f);
-            const float e1 = fminf(__fmaf_rn(__uint_as_float(r[t + 1]), sc, e_off), 15.98f);
+            const float e0 = __fmaf_rn(__uint_as_float(r[t]), sc, e_off);
+            const float e1 = __fmaf_rn(__uint_as_float(r[t + 1]), sc, e_off);
             asm("ex2.approx.f32 %0, %1;" : "=f"(p0) : "f"(e0));
             asm("ex2.approx.f32 %0, %1;" : "=f"(p1) : "f"(e1));
-            if (first + t >= valid) p0 = 0.0f;
-            if (first + t + 1 >= valid) p1 = 0.0f;
+            if (masked) {
+              if (first + t >= valid) p0 = 0.0f;
+              if (first + t + 1 >= valid) p1 = 0.0f;
+            }
             l += __fadd_rn(p0, p1);
             uint32_t hi2, lo2;
             split_f16x2(p0, p1, hi2, lo2);
@@ -523,10 +527,17 @@ __global__ void __launch_bounds__(kAThreads, 1)
         };
         {
           uint32_t w[32];
-          weights(r0, 0, w);
-          tmem_st_32x32(s_col + buf * kBkv, w);
-          weights(r1, 32, w);
-          tmem_st_32x32(s_col + buf * kBkv + 32, w);
+          if (valid >= 64) {
+            weights(r0, 0, false, w);
+            tmem_st_32x32(s_col + buf * kBkv, w);
+            weights(r1, 32, false, w);
+            tmem_st_32x32(s_col + buf * kBkv + 32, w);
+          } else {
+            weights(r0, 0, true, w);
+            tmem_st_32x32(s_col + buf * kBkv, w);
+            weights(r1, 32, true, w);
+            tmem_st_32x32(s_col + buf * kBkv + 32, w);
+          }
         }
         tmem_st_wait();
         tc_fence_before();
