@@ -30,10 +30,12 @@
 // terms, 2^-22 of the products, would reach the weights.  A NaN row sum marks its row too.
 //
 // One CTA per (128 query rows, head), persistent over these work items; 416 threads:
-//   warp 0 lane 0 : TMA producer of k: 128 keys per stage, the hi plane in sweep 1, hi and lo in
-//                   sweep 2; 128-byte-swizzled boxes of 128 keys x 64 dims, two-stage ring,
-//                   released as soon as a block's scores are done.
-//   warp 10 lane 0: TMA producer of v^T (hi and lo planes, 64 keys per stage, its own two-stage
+//   warp 0 lane 0 : TMA producer of k: a ring of four 32 KiB slots, one plane of 128 keys each
+//                   (128-byte-swizzled boxes of 128 keys x 64 dims): the hi plane per block in
+//                   sweep 1, hi and lo in sweep 2; released as soon as a block's scores are done.
+//                   A load takes ~1500 cycles from release to landed, three times what the MMAs
+//                   of a block of sweep 1 take: hence four slots.
+//   warp 10 lane 0: TMA producer of v^T (hi and lo planes, 64 keys per stage, its own three-stage
 //                   ring released by the P*V MMAs).
 //   warp 1 lane 0 : MMA issuer of the scores of the even key blocks.  S = Q K^T with Q as the
 //   warp 12 lane 0: ... and of the odd key blocks.  A operand in TENSOR MEMORY, K from shared memory.
@@ -43,9 +45,10 @@
 //                   instruction streams come from three lanes.
 //   warps 2..5    : softmax group A (one thread per query row): the first 64 keys of every block.
 //   warps 6..9    : softmax group B: the other 64 keys.  Both groups finish the tile together:
-//                   O / row sum -> staged boxes -> bulk tensor stores.
+//                   O / row sum, each thread storing its row's 128-byte pieces.
 // Tensor memory (512 columns, two fp16 per column for the A operands): Q_hi 0..63, Q_lo 64..127,
-// O 128..255, S/P buffers 256..383 and 384..511.  Every mbarrier wait is bounded like the GEMM
+// O 128..255, S/P buffers 256..383 and 384..511; sweep 1 rotates its scores over the two S
+// buffers and the O columns, so that the read-out of one block hides behind the MMAs of two.  Every mbarrier wait is bounded like the GEMM
 // kernels'.
 #include "tc_common.cuh"
 
@@ -60,15 +63,15 @@ constexpr int kBq = 128;            // query rows per work item
 constexpr int kBkv = 128;           // keys per block
 constexpr int kVKeys = 64;          // keys per stage of the v^T ring
 constexpr int kKPlane = kBkv * kHd * 2;         // 32 KiB: one fp16 plane of a key block
-constexpr int kKStageBytes = 2 * kKPlane;       // k hi + lo
 constexpr int kVPlane = kHd * kVKeys * 2;       // 16 KiB: one fp16 plane of 64 keys of v^T
 constexpr int kVStageBytes = 2 * kVPlane;       // v^T hi + lo
-constexpr int kAStages = 2;                // per ring
-constexpr int kARingBytes = kAStages * (kKStageBytes + kVStageBytes);
+constexpr int kKSlots = 4;                 // k ring: slots of one plane (sweep 1 takes one per key block, sweep 2 two)
+constexpr int kVStages = 3;                // v^T ring
+constexpr int kARingBytes = kKSlots * kKPlane + kVStages * kVStageBytes;   // 224 KiB
 constexpr int kAThreads = kNumThreads + 96;  // + three warps: v^T producer, P*V issuer, second score issuer
 constexpr int kABookBytes = 2304;    // row maxima and sums of both groups (2 KiB) + barriers
 constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte boundary
-constexpr int kASmemBytes = kARingBytes + 8 * 4096 + kABookBytes + kAAlignSlack;  // 227 KiB
+constexpr int kASmemBytes = kARingBytes + kABookBytes + kAAlignSlack;  // 227 KiB
 constexpr uint32_t kColQhi = 0, kColQlo = 64, kColO = 128, kColS = 256;
 constexpr float kPShift = 10.0f;     // the softmax weights are carried as p * 2^10 (<= 2^10 up to
                                      // the error of the first sweep's maxima)
@@ -145,34 +148,35 @@ __global__ void __launch_bounds__(kAThreads, 1)
     sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmap_k_hi,
                    const __grid_constant__ CUtensorMap tmap_k_lo,
                    const __grid_constant__ CUtensorMap tmap_vt_hi,
-                   const __grid_constant__ CUtensorMap tmap_vt_lo,
-                   const __grid_constant__ CUtensorMap tmap_out, SdpaArgs g) {
+                   const __grid_constant__ CUtensorMap tmap_vt_lo, SdpaArgs g) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t smem_v = base + kAStages * kKStageBytes;   // the v^T ring follows the k ring
-  const uint32_t smem_staging = base + kARingBytes;
-  uint8_t* book = smem + kARingBytes + 8 * 4096;
+  const uint32_t smem_v = base + kKSlots * kKPlane;   // the v^T ring follows the k ring
+  uint8_t* book = smem + kARingBytes;
   // row maxima and row sums of the two softmax groups, then the barriers
   float* x_max = reinterpret_cast<float*>(book);          // [2][128]
   float* x_sum = reinterpret_cast<float*>(book + 1024);   // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(book + 2048);
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t bar_full = bar0;               // [2]  k ring: TMA bytes landed
-  const uint32_t bar_empty = bar0 + 16;         // [2]  k ring: stage read by its last MMA
-  const uint32_t bar_sfull = bar0 + 32;         // [2]  scores of a block complete
-  const uint32_t bar_s1free = bar0 + 48;        // [2]  sweep 1: scores read by the softmax groups
-  const uint32_t bar_pready = bar0 + 64;        // [2]  sweep 2: weights written over the scores
-  const uint32_t bar_pvdone = bar0 + 80;        // [2]  sweep 2: P*V of a block complete
-  const uint32_t bar_qready = bar0 + 96;        // Q planes in tensor memory
-  const uint32_t bar_mready = bar0 + 104;       // both groups published their row maxima
-  const uint32_t bar_lready = bar0 + 112;       // both groups published their row sums
-  const uint32_t bar_ofull = bar0 + 120;        // every MMA of the work item complete
-  const uint32_t bar_vfull = bar0 + 128;        // [2]  v^T ring
-  const uint32_t bar_vempty = bar0 + 144;       // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  const uint32_t bar_kfull = bar0;              // [4]  k ring: TMA bytes landed
+  const uint32_t bar_kempty = bar0 + 32;        // [4]  k ring: slot read by its last MMA
+  const uint32_t bar_sfull = bar0 + 64;         // [2]  sweep 2: scores of a block complete
+  const uint32_t bar_s1full = bar0 + 80;        // [3]  sweep 1: scores of a block complete
+  const uint32_t bar_s1free = bar0 + 104;       // [3]  sweep 1: scores read by the softmax groups
+  const uint32_t bar_pready = bar0 + 128;       // [2]  sweep 2: weights written over the scores
+  const uint32_t bar_pvdone = bar0 + 144;       // [2]  sweep 2: P*V of a block complete
+  const uint32_t bar_qready = bar0 + 160;       // Q planes in tensor memory
+  const uint32_t bar_mready = bar0 + 168;       // both groups published their row maxima
+  const uint32_t bar_lready = bar0 + 176;       // both groups published their row sums
+  const uint32_t bar_ofull = bar0 + 184;        // every MMA of the work item complete
+  const uint32_t bar_ofree = bar0 + 192;        // O read out: the next item's first sweep may use its columns
+  const uint32_t bar_vfull = bar0 + 200;        // [3]  v^T ring
+  const uint32_t bar_vempty = bar0 + 224;       // [3]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 31);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert(2048 + 31 * 8 + 8 <= kABookBytes, "book too small");
 
   if (base - raw > (uint32_t)kAAlignSlack) {
     // the dynamic shared memory starts further from a 1024-byte boundary than the launch
@@ -188,20 +192,26 @@ __global__ void __launch_bounds__(kAThreads, 1)
   const int num_items = nqt * g.heads;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; i++) {
-      mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, 1);
-      mbar_init(bar_sfull + 8 * i, 1);
+    for (int i = 0; i < kKSlots; i++) {
+      mbar_init(bar_kfull + 8 * i, 1);
+      mbar_init(bar_kempty + 8 * i, 1);
+    }
+    for (int i = 0; i < 3; i++) {
+      mbar_init(bar_s1full + 8 * i, 1);
       mbar_init(bar_s1free + 8 * i, 8);
-      mbar_init(bar_pready + 8 * i, 8);
-      mbar_init(bar_pvdone + 8 * i, 1);
       mbar_init(bar_vfull + 8 * i, 1);
       mbar_init(bar_vempty + 8 * i, 1);
+    }
+    for (int i = 0; i < 2; i++) {
+      mbar_init(bar_sfull + 8 * i, 1);
+      mbar_init(bar_pready + 8 * i, 8);
+      mbar_init(bar_pvdone + 8 * i, 1);
     }
     mbar_init(bar_qready, 4);
     mbar_init(bar_mready, 8);
     mbar_init(bar_lready, 8);
     mbar_init(bar_ofull, 1);
+    mbar_init(bar_ofree, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -209,7 +219,6 @@ __global__ void __launch_bounds__(kAThreads, 1)
     prefetch_tmap(&tmap_k_lo);
     prefetch_tmap(&tmap_vt_hi);
     prefetch_tmap(&tmap_vt_lo);
-    prefetch_tmap(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), 512);
@@ -222,26 +231,25 @@ __global__ void __launch_bounds__(kAThreads, 1)
 
   if (warp == 0) {
     if (lane == 0) {
-      // ------------------------------------------------ TMA producer of k: per plane two boxes of
-      // 128 keys x 64 dims
+      // ------------------------------------------------ TMA producer of k: a ring of four
+      // slots of one plane (two boxes of 128 keys x 64 dims); a block of sweep 1 takes one slot
+      // (hi), a block of sweep 2 two (hi, then lo)
       const uint64_t keep = policy_evict_last();
-      uint32_t stage = 0, phase = 0;
+      uint32_t slot = 0, phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int h = item / nqt;
-        for (int sweep = 0; ok && sweep < 2; sweep++) {
-          for (int j = 0; j < nblk; j++) {
-            ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x800 | (1 + sweep));
-            if (!ok) break;
-            const uint32_t full = bar_full + 8 * stage;
-            const uint32_t st = base + stage * kKStageBytes;
-            mbar_expect_tx(full, sweep ? kKStageBytes : kKPlane);
-            for (int i = 0; i < 2; i++) {
-              tma_load_2d_hint(st + i * 16384, &tmap_k_hi, full, h * kHd + 64 * i, j * kBkv, keep);
-              if (sweep) tma_load_2d_hint(st + kKPlane + i * 16384, &tmap_k_lo, full, h * kHd + 64 * i, j * kBkv, keep);
-            }
-            if (++stage == kAStages) { stage = 0; phase ^= 1u; }
-          }
+        for (int n = 0; n < 3 * nblk; n++) {
+          const int j = n < nblk ? n : (n - nblk) >> 1;
+          const bool lo = n >= nblk && ((n - nblk) & 1);
+          ok = mbar_wait(bar_kempty + 8 * slot, phase ^ 1u, abort_flag, g.status, 0x800 | (n < nblk ? 1 : 2));
+          if (!ok) break;
+          const uint32_t full = bar_kfull + 8 * slot;
+          const uint32_t st = base + slot * kKPlane;
+          mbar_expect_tx(full, kKPlane);
+          for (int i = 0; i < 2; i++)
+            tma_load_2d_hint(st + i * 16384, lo ? &tmap_k_lo : &tmap_k_hi, full, h * kHd + 64 * i, j * kBkv, keep);
+          if (++slot == kKSlots) { slot = 0; phase ^= 1u; }
         }
       }
     }
@@ -263,7 +271,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
           mbar_expect_tx(full, kVStageBytes);
           tma_load_2d_hint(st, &tmap_vt_hi, full, j * kVKeys, h * kHd, keep);
           tma_load_2d_hint(st + kVPlane, &tmap_vt_lo, full, j * kVKeys, h * kHd, keep);
-          if (++stage == kAStages) { stage = 0; phase ^= 1u; }
+          if (++stage == kVStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -271,42 +279,49 @@ __global__ void __launch_bounds__(kAThreads, 1)
     if (lane == 0) {
       // ------------------------------------------------ MMA issuers of the scores: this lane
       // takes the blocks of one parity (warp 1 the even ones, warp 12 the odd ones) in both
-      // sweeps, i.e. always the same score buffer.  The k ring is shared: block number `seq` of
-      // the CTA's whole run sits in stage seq & 1, whose full barrier completes its phase
-      // (seq >> 1) & 1 for it.
+      // sweeps.  The k ring is shared: slot number `seq` of the CTA's whole run is ring slot
+      // seq & 3, whose full barrier completes its phase (seq >> 2) & 1 for it.
       const uint32_t par = warp == 1 ? 0u : 1u;
-      const uint32_t d = tmem_base + kColS + par * kBkv;
-      uint32_t sfree_ph = 0;                    // completed phases of s1free[par]
+      const uint32_t d2 = tmem_base + kColS + par * kBkv;   // sweep 2: always the same buffer
+      uint32_t s1_uses[3] = {0, 0, 0};          // sweep 1: uses of each score buffer before this item
       uint32_t pv_ph = 0;                       // completed phases of pvdone[par]
-      uint32_t q_ph = 0, m_ph = 0;
-      uint32_t seq0 = 0;                        // k-ring sequence number of the item's first block
+      uint32_t q_ph = 0, m_ph = 0, ofree_ph = 0;
+      uint32_t seq0 = 0;                        // k-ring sequence number of the item's first slot
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         ok = mbar_wait_spin(bar_qready, q_ph, abort_flag, g.status, 0x900 | 1);
         q_ph ^= 1u;
         if (!ok) break;
+        // the previous item's O has been read out (and so every MMA of that item is complete):
+        // sweep 1 borrows its columns
+        ok = mbar_wait_spin(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
+        ofree_ph ^= 1u;
+        if (!ok) break;
         tc_fence_after();
         // ---- sweep 1: hi*hi scores for the row maxima (11 mantissa bits are ample for an
-        // offset), 128 keys and 16 dims per MMA.  (The buffer's last use, the previous item's
-        // weights, was consumed before this lane left that item.)
+        // offset), 128 keys and 16 dims per MMA, rotating over three buffers: the two score
+        // buffers and the idle O columns
         for (int j = (int)par; j < nblk; j += 2) {
-          const uint32_t seq = seq0 + (uint32_t)j, stage = seq & 1u;
-          ok = mbar_wait_spin(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 2);
+          const uint32_t seq = seq0 + (uint32_t)j, slot = seq & 3u;
+          const uint32_t b3 = (uint32_t)j % 3u, use = s1_uses[b3] + (uint32_t)j / 3u;
+          ok = mbar_wait_spin(bar_kfull + 8 * slot, (seq >> 2) & 1u, abort_flag, g.status, 0x900 | 2);
           if (!ok) break;
-          ok = mbar_wait_spin(bar_s1free + 8 * par, sfree_ph ^ 1u, abort_flag, g.status, 0x900 | 3);
+          ok = mbar_wait_spin(bar_s1free + 8 * b3, (use & 1u) ^ 1u, abort_flag, g.status, 0x900 | 3);
           if (!ok) break;
-          sfree_ph ^= 1u;
           tc_fence_after();
-          const uint32_t st = base + stage * kKStageBytes;
+          const uint32_t st = base + slot * kKPlane;
+          const uint32_t d = tmem_base + (b3 == 2 ? kColO : kColS + b3 * kBkv);
 #pragma unroll
           for (int ks = 0; ks < kHd / 16; ks++) {
             const uint64_t k_hi = make_smem_desc(st + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
             umma_f16_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescH, (uint32_t)(ks != 0));
           }
-          umma_commit(bar_empty + 8 * stage);
-          umma_commit(bar_sfull + 8 * par);
+          umma_commit(bar_kempty + 8 * slot);
+          umma_commit(bar_s1full + 8 * b3);
         }
         if (!ok) break;
+#pragma unroll
+        for (int b = 0; b < 3; b++) s1_uses[b] += (uint32_t)(nblk > b ? (nblk - b + 2) / 3 : 0);
         // the softmax groups have read every score of sweep 1 and published the maxima
         ok = mbar_wait_spin(bar_mready, m_ph, abort_flag, g.status, 0x900 | 4);
         m_ph ^= 1u;
@@ -314,12 +329,15 @@ __global__ void __launch_bounds__(kAThreads, 1)
         tc_fence_after();
         // ---- sweep 2: accurate scores of this lane's blocks, three MMAs per 16 dims (the two
         // small cross terms first).  The buffer is free again when the P*V of the block two back
-        // has consumed its weights; a k stage is released as soon as the scores that read it
-        // are done.
+        // has consumed its weights; the k slots are released as soon as the scores that read
+        // them are done.
         bool any = false;
         for (int j = (int)par; j < nblk; j += 2) {
-          const uint32_t seq = seq0 + (uint32_t)(nblk + j), stage = seq & 1u;
-          ok = mbar_wait_spin(bar_full + 8 * stage, (seq >> 1) & 1u, abort_flag, g.status, 0x900 | 7);
+          const uint32_t seq = seq0 + (uint32_t)(nblk + 2 * j);
+          const uint32_t slot_hi = seq & 3u, slot_lo = (seq + 1) & 3u;
+          ok = mbar_wait_spin(bar_kfull + 8 * slot_hi, (seq >> 2) & 1u, abort_flag, g.status, 0x900 | 7);
+          if (!ok) break;
+          ok = mbar_wait_spin(bar_kfull + 8 * slot_lo, ((seq + 1) >> 2) & 1u, abort_flag, g.status, 0x900 | 6);
           if (!ok) break;
           if (any) {
             ok = mbar_wait_spin(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 8);
@@ -327,18 +345,19 @@ __global__ void __launch_bounds__(kAThreads, 1)
             pv_ph ^= 1u;
           }
           tc_fence_after();
-          const uint32_t st = base + stage * kKStageBytes;
+          const uint32_t st_hi = base + slot_hi * kKPlane, st_lo = base + slot_lo * kKPlane;
 #pragma unroll
           for (int ks = 0; ks < kHd / 16; ks++) {
             const uint32_t off = (uint32_t)((ks >> 2) * 16384);
             const uint64_t adv = (uint64_t)((ks & 3) * 2);
-            const uint64_t k_hi = make_smem_desc(st + off) + adv;
-            const uint64_t k_lo = make_smem_desc(st + kKPlane + off) + adv;
-            umma_f16_ts(d, tmem_base + kColQlo + ks * 8, k_hi, kIdescH, (uint32_t)(ks != 0));
-            umma_f16_ts(d, tmem_base + kColQhi + ks * 8, k_lo, kIdescH, 1u);
-            umma_f16_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescH, 1u);
+            const uint64_t k_hi = make_smem_desc(st_hi + off) + adv;
+            const uint64_t k_lo = make_smem_desc(st_lo + off) + adv;
+            umma_f16_ts(d2, tmem_base + kColQlo + ks * 8, k_hi, kIdescH, (uint32_t)(ks != 0));
+            umma_f16_ts(d2, tmem_base + kColQhi + ks * 8, k_lo, kIdescH, 1u);
+            umma_f16_ts(d2, tmem_base + kColQhi + ks * 8, k_hi, kIdescH, 1u);
           }
-          umma_commit(bar_empty + 8 * stage);
+          umma_commit(bar_kempty + 8 * slot_hi);
+          umma_commit(bar_kempty + 8 * slot_lo);
           umma_commit(bar_sfull + 8 * par);
           any = true;
         }
@@ -348,7 +367,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
           pv_ph ^= 1u;
           if (!ok) break;
         }
-        seq0 += (uint32_t)(2 * nblk);
+        seq0 += (uint32_t)(3 * nblk);
       }
     }
   } else if (warp == 11) {
@@ -358,8 +377,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
       uint32_t pready_ph[2] = {0, 0};
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-        // (O is free: every softmax warp read the previous item's O out before it could arrive
-        // on this item's first pready)
+        // (O is free: every softmax warp read the previous item's O out, and the first sweep that
+        // borrowed its columns was read, before any could arrive on this item's first pready)
         for (int j = 0; ok && j < nblk; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
           ok = mbar_wait_spin(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
@@ -384,7 +403,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
               umma_f16_ts(tmem_base + kColO, p_hi, v_hi, kIdescH, 1u);
             }
             umma_commit(bar_vempty + 8 * vstage);
-            if (++vstage == kAStages) { vstage = 0; vphase ^= 1u; }
+            if (++vstage == kVStages) { vstage = 0; vphase ^= 1u; }
           }
           if (!ok) break;
           umma_commit(bar_pvdone + 8 * buf);
@@ -399,11 +418,10 @@ __global__ void __launch_bounds__(kAThreads, 1)
     const int grp = (warp - 2) >> 2;        // 0: keys 0..63 of every block, 1: keys 64..127
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t box = smem_staging + (uint32_t)((warp - 2) * 4096);
-    const uint64_t stream_policy = policy_evict_first();
     const uint32_t s_col = tmem_base + kColS + (uint32_t)grp * 64 + lane_base;  // + buffer * kBkv
     const int sh_k = operand_shift(g.absmax[0]), sh_v = operand_shift(g.absmax[1]);
     uint32_t sfull_ph[2] = {0, 0};
+    uint32_t s1_uses[3] = {0, 0, 0};        // sweep 1: uses of each score buffer before this item
     uint32_t m_ph = 0, l_ph = 0, ofull_ph = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
@@ -452,19 +470,18 @@ __global__ void __launch_bounds__(kAThreads, 1)
       // ---- sweep 1: the row maximum over this group's half of every block (raw dot products)
       float m = -INFINITY;
       for (int j = 0; j < nblk; j++) {
-        const uint32_t buf = (uint32_t)(j & 1);
-        ok = mbar_wait_warp(bar_sfull + 8 * buf, sfull_ph[buf], abort_flag, g.status, 0xa00 | 1);
-        sfull_ph[buf] ^= 1u;
+        const uint32_t b3 = (uint32_t)j % 3u, use = s1_uses[b3] + (uint32_t)j / 3u;
+        ok = mbar_wait_warp(bar_s1full + 8 * b3, use & 1u, abort_flag, g.status, 0xa00 | 1);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t x_col = s_col + buf * kBkv;
+        const uint32_t x_col = tmem_base + (b3 == 2 ? kColO : kColS + b3 * kBkv) + (uint32_t)grp * 64 + lane_base;
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(x_col, r0);
         tmem_ld_32x32(x_col + 32, r1);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_s1free + 8 * buf);
+        if (lane == 0) mbar_arrive(bar_s1free + 8 * b3);
         const int64_t key0 = (int64_t)j * kBkv + grp * 64;
         if (key0 + 64 <= g.Lk) {
 #pragma unroll
@@ -478,6 +495,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
         }
       }
       if (!ok) break;
+#pragma unroll
+      for (int b = 0; b < 3; b++) s1_uses[b] += (uint32_t)(nblk > b ? (nblk - b + 2) / 3 : 0);
       x_max[grp * kBq + row_in_tile] = m;
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_mready);
@@ -560,42 +579,37 @@ __global__ void __launch_bounds__(kAThreads, 1)
         g.redo[row * g.heads + h] = 1;   // offset too far from the row's maximum, or scores too large
       // O holds sum p 2^10 (v 2^sh_v): divide by the row sum of p 2^10 and take v's power back out
       const float inv = __fmul_rn(__fdiv_rn(1.0f, l), pow2f(-sh_v));
-      // ---- epilogue: O / l, this group's two 32-column chunks
+      // ---- epilogue: O / l, this group's two 32-column chunks, each thread its row's 128 bytes
       ok = mbar_wait_warp(bar_ofull, ofull_ph, abort_flag, g.status, 0xa00 | 5);
       ofull_ph ^= 1u;
       if (!ok) break;
       tc_fence_after();
+      float* orow = g.out + row * g.C + (int64_t)h * kHd;
 #pragma unroll 1
       for (int c = 2 * grp; c < 2 * grp + 2; c++) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + kColO + c * 32 + lane_base, r);
         tmem_ld_wait();
-        if (lane == 0) bulk_wait_read<0>();
-        __syncwarp();
+        if (row < g.Lq) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          st_shared_v4(box + (uint32_t)(lane * 128 + (((j >> 2) ^ (lane & 7)) << 4)),
-                       make_float4(__fmul_rn(__uint_as_float(r[j]), inv), __fmul_rn(__uint_as_float(r[j + 1]), inv),
-                                   __fmul_rn(__uint_as_float(r[j + 2]), inv), __fmul_rn(__uint_as_float(r[j + 3]), inv)));
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d_hint(&tmap_out, box, h * kHd + c * 32, (int)(q0 + quarter * 32), stream_policy);
-          bulk_commit();
+          for (int j = 0; j < 32; j += 4)
+            __stcs(reinterpret_cast<float4*>(orow + c * 32 + j),
+                   make_float4(__fmul_rn(__uint_as_float(r[j]), inv), __fmul_rn(__uint_as_float(r[j + 1]), inv),
+                               __fmul_rn(__uint_as_float(r[j + 2]), inv), __fmul_rn(__uint_as_float(r[j + 3]), inv)));
         }
       }
-      // (the reads of O are complete: the next item's first pready arrival tells the P*V issuer)
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ofree);
     }
   }
 
   // ---------------------------------------------------- common exit
-  if (warp >= 2 && lane == 0) bulk_wait_read<0>();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   if (*abort_flag) {
-    for (int i = 0; i < 1000; i++) __nanosleep(1000);  // let bulk copies in flight land (~1 ms)
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);  // let bulk loads in flight land (~1 ms)
     __syncthreads();
   }
   if (warp == 1) {
@@ -790,10 +804,9 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   transpose_split_f16_kernel<<<tgrid, 256, 0, s>>>(v, Lk, C, ld, absmax, vt_hi, vt_lo);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  CUtensorMap t_khi, t_klo, t_vt_hi, t_vt_lo, t_out;
+  CUtensorMap t_khi, t_klo, t_vt_hi, t_vt_lo;
   if (!make_tmap_k(&t_khi, k_hi, Lk, C, why) || !make_tmap_k(&t_klo, k_lo, Lk, C, why) ||
-      !make_tmap_vt(&t_vt_hi, vt_hi, C, Lk, ld, why) || !make_tmap_vt(&t_vt_lo, vt_lo, C, Lk, ld, why) ||
-      !make_out_tmap(&t_out, out, Lq, C, why))
+      !make_tmap_vt(&t_vt_hi, vt_hi, C, Lk, ld, why) || !make_tmap_vt(&t_vt_lo, vt_lo, C, Lk, ld, why))
     return cudaErrorInvalidValue;
   SdpaArgs g;
   g.q = q; g.out = out; g.absmax = absmax; g.redo = redo; g.Lq = Lq; g.Lk = Lk; g.C = C; g.heads = heads;
@@ -802,7 +815,7 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
   const int64_t items = ((Lq + kBq - 1) / kBq) * heads;
   count_launch();
   sdpa_tc_kernel<<<(unsigned)(items < sm_count ? items : sm_count), kAThreads, kASmemBytes, s>>>(
-      t_khi, t_klo, t_vt_hi, t_vt_lo, t_out, g);
+      t_khi, t_klo, t_vt_hi, t_vt_lo, g);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   // rows whose offset was too far off (none on ordinary data): exact fp32 on the CUDA cores
