@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--workload", default="ffn_pair_720p", choices=["ffn_pair_720p", "sweep", "branch", "libcompare", "block", "fp32"])
     ap.add_argument("--blocks", type=int, default=30, help="branch workload: number of DiT blocks")
     ap.add_argument("--heads", type=int, default=24, help="fp32 workload: attention heads of 128")
+    ap.add_argument("--qk-scale", type=float, default=1.0,
+                    help="fp32 workload: factor on the standard-normal q and k (larger = more peaked softmax)")
     ap.add_argument("--with-attention", action="store_true",
                     help="block workload: also run the block's self- and cross-attention (sdq_sdpa) in the fused pattern")
     ap.add_argument("--pack-file-blocks", type=int, default=0,
@@ -103,19 +105,21 @@ class ClockSampler:
         time.sleep(0.15)
         self.proc.terminate()
         inside = [r for (t, r) in self.rows if t0 - 0.05 <= t <= t1 + 0.15] or [r for _, r in self.rows[-3:]]
-        sm, mx, reasons = [], None, set()
+        sm, mx, reasons, watts = [], None, set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in inside:
             try:
                 sm.append(float(r[0]))
                 mx = float(r[1])
+                watts.append(float(r[2]))
             except (ValueError, IndexError):
                 continue
             for n, v in zip(names, r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm),
+                "power_w": float(np.median(watts)) if watts else None}
 
 
 # ------------------------------------------------------------------ reference arm (CPU)
@@ -834,15 +838,18 @@ def run_block(args):
         xx.addcmul_(y, e[5])
 
     heads = D // 128
-    qs, ks, vs = (qkv[:, :D].contiguous(), qkv[:, D:2 * D].contiguous(), qkv[:, 2 * D:].contiguous()) \
-        if args.with_attention else (None, None, None)
+    qs, ks, vs = [torch.empty(M, D, device=dev) for _ in range(3)] if args.with_attention else (None, None, None)
     kv2 = torch.empty(T, D, device=dev) if args.with_attention else None
 
     def fused(xx):
         eps = C.c_float(1e-6)
         s._ck(lib.sdq_layernorm_mod_quantize(p(xx), M, D, p(e[0]), p(e[1]), eps, p(aq), p(a_s), None, 0, sp))
         pre("self_attn.qkv", aq, a_s, M, qkv)
-        if args.with_attention:      # self-attention over the M tokens (q/k RMSNorm and RoPE: the caller's)
+        if args.with_attention:      # self-attention over the M tokens.  The three copies stand in for
+            # the caller's q/k RMSNorm and RoPE passes, which read the projections and write q, k, v
+            qs.copy_(qkv[:, :D])
+            ks.copy_(qkv[:, D:2 * D])
+            vs.copy_(qkv[:, 2 * D:])
             s._ck(lib.sdq_sdpa(p(qs), p(ks), p(vs), M, M, D, heads, p(att), 0, sp))
         s._ck(lib.sdq_qgemm_residual(W["self_attn.o"][2], p(att), M, p(xx), p(e[2]), p(xx), p(W["self_attn.o"][3]), 0, sp))
         s._ck(lib.sdq_layernorm_mod_quantize(p(xx), M, D, p(ln3_b), p(ln3_w), eps, p(aq), p(a_s), None, S.LN_AFFINE, sp))
@@ -925,21 +932,28 @@ def run_fp32(args):
     def p(t):
         return C.c_void_p(t.data_ptr())
 
-    def timed(fn):
+    def timed(fn, clocks=None):
         for _ in range(max(args.warmup, 1)):
             fn()
         torch.cuda.synchronize()
+        sampler = ClockSampler(0) if clocks is not None else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_wall0 = time.time()
         e0.record(stream)
         for _ in range(args.steps):
             fn()
         e1.record(stream)
         torch.cuda.synchronize()
+        if sampler:
+            clocks.update(sampler.stop(t_wall0, time.time()))
         return e0.elapsed_time(e1) / args.steps
     q, k, v = [torch.randn(L, Cc, device=dev, generator=g) for _ in range(3)]
+    q *= args.qk_scale
+    k *= args.qk_scale
     out = torch.empty(L, Cc, device=dev)
     n0 = s.launches()
-    t_att = timed(lambda: s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), 0, sp)))
+    att_clocks = {}
+    t_att = timed(lambda: s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), 0, sp)), att_clocks)
     att_launches = (s.launches() - n0) // (args.steps + max(args.warmup, 1))
     rows = min(L, 1024)                                   # float64 check: two heads, the first rows
     q64, k64, v64 = [x.view(L, H, 128).transpose(0, 1)[:2].double() for x in (q, k, v)]
@@ -968,10 +982,12 @@ def run_fp32(args):
                       "dtype": "fp16x3 scores and P*V (two-term splits), f32 accumulate", "data": "synthetic",
                       "config": {"workload": "dit_attention_and_fp32_matmul", "tokens": L, "heads": H,
                                  "l2": "q, k, v %d MB each" % (L * Cc * 4 // 1000000)},
-                      "gpu_launches": att_launches * args.steps,
+                      "gpu_launches": att_launches * args.steps, "clocks": att_clocks,
                       "attention": {"ms": t_att, "tflops": att_flop / (t_att * 1e-3) / 1e12,
                                     "max_err_over_max_abs_vs_float64": err_att, "torch_fp32_sdpa_ms": t_att_torch,
-                                    "frac_of_measured_bf16_peak": att_flop / (t_att * 1e-3) / 1e12 / bf16, "of": pk_kind},
+                                    "frac_of_measured_bf16_peak": att_flop / (t_att * 1e-3) / 1e12 / bf16, "of": pk_kind,
+                                    # 56 fp16 MMAs of 128x128x16 per 128 keys against 16 of plain fp16 attention
+                                    "issued_fp16_tflops": 3.5 * att_flop / (t_att * 1e-3) / 1e12},
                       "matmul": {"shape": [M, K, N], "ms": t_mm, "tflops": mm_flop / (t_mm * 1e-3) / 1e12,
                                  "max_err_over_max_abs_vs_float64": err_mm, "torch_fp32_matmul_ms": t_mm_torch}}))
     return 0

@@ -261,11 +261,15 @@ SDQ_API int sdq_fmatmul(sdq_weight_t w, const float* A, int64_t M, float* out,
  * out[Lq,C] = softmax(q k^T / sqrt(C/heads)) v for each of `heads` heads -- replaces blk::sdpa
  * (src/model/blocks.h:60-66, src/model/blocks.cpp:113-199; the reference never sets its causal
  * flag).  q is fp32 [Lq,C], k and v fp32 [Lk,C], all device memory; head h owns columns
- * [h*C/heads, (h+1)*C/heads).  For head_dim 128 (the DiT's) the scores are computed on the
- * tensor cores with three tf32 products per fp32 product, the softmax weights and v are rounded
- * to tf32 once, and the row maximum comes from a first sweep over the keys, so no accumulator is
- * rescaled; other head sizes take an fp32 CUDA-core kernel.  Held to the reference's 1e-3 bound
- * (max-abs error / max-abs output); exp and the summation order are not bit-reproducible. */
+ * [h*C/heads, (h+1)*C/heads).  For head_dim 128 (the DiT's) everything runs on the tensor
+ * cores: q, k, v and the softmax weights are each carried as two fp16 numbers times a power of
+ * two (22 mantissa bits; the powers are found from the data, so magnitudes do not matter), every
+ * product is three fp16 MMAs with fp32 accumulation, and the row maximum comes from a first
+ * sweep over the keys, so no accumulator is rescaled.  Rows whose scores are out of that
+ * scheme's range (|score| in the tens of thousands) are recomputed in plain fp32 by the CUDA-core
+ * kernel that also serves the other head sizes.  Held to the reference's 1e-3 bound (max-abs
+ * error / max-abs output; ~1e-5 measured at a few thousand keys, 1e-4 at 27280); exp and the
+ * summation order are not bit-identical to the CPU's, but two runs give the same bits. */
 SDQ_API int sdq_sdpa(const float* q_dev, const float* k_dev, const float* v_dev, int64_t Lq,
                      int64_t Lk, int64_t C, int heads, float* out_dev, uint32_t flags,
                      void* stream);
