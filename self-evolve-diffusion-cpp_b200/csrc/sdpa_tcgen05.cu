@@ -75,9 +75,10 @@ constexpr int kASmemBytes = kARingBytes + kABookBytes + kAAlignSlack;  // 227 Ki
 constexpr uint32_t kColQhi = 0, kColQlo = 64, kColO = 128, kColS = 256;
 constexpr float kPShift = 10.0f;     // the softmax weights are carried as p * 2^10 (<= 2^10 up to
                                      // the error of the first sweep's maxima)
-constexpr uint32_t kPHalfTop = 0x7b00;  // fp16 bits of 2^15.8: a weight this large means the first
-                                        // sweep's maximum was ~6 log2 units too low
-constexpr float kRowSumFloor = 8.0f;    // a row sum below 2^3 means it was ~7 too high
+constexpr uint32_t kPHalfTop = 0x7b00;  // fp16 bits of 2^15.8: no finite weight gets there
+constexpr float kRowSumFloor = 8.0f;    // (a row sum is at least 2^10 / 2^kRescaleStep unless something is not finite)
+constexpr float kRescaleStep = 4.0f;    // log2 units by which a block's maximum may exceed the running
+                                        // offset before the offset moves (weights stay below 2^14)
 constexpr float kScoreBound = 524288.0f;  // 2^19 log2 units: above this bound on sum |q_d k_d| the
                                           // dropped lo*lo terms (2^-22 of it) would show in the weights
 constexpr int kOperandTop = 14;      // operands are scaled so that their largest magnitude is in [2^14, 2^15)
@@ -162,21 +163,18 @@ __global__ void __launch_bounds__(kAThreads, 1)
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_kfull = bar0;              // [4]  k ring: TMA bytes landed
   const uint32_t bar_kempty = bar0 + 32;        // [4]  k ring: slot read by its last MMA
-  const uint32_t bar_sfull = bar0 + 64;         // [2]  sweep 2: scores of a block complete
-  const uint32_t bar_s1full = bar0 + 80;        // [3]  sweep 1: scores of a block complete
-  const uint32_t bar_s1free = bar0 + 104;       // [3]  sweep 1: scores read by the softmax groups
-  const uint32_t bar_pready = bar0 + 128;       // [2]  sweep 2: weights written over the scores
-  const uint32_t bar_pvdone = bar0 + 144;       // [2]  sweep 2: P*V of a block complete
-  const uint32_t bar_qready = bar0 + 160;       // Q planes in tensor memory
-  const uint32_t bar_mready = bar0 + 168;       // both groups published their row maxima
-  const uint32_t bar_lready = bar0 + 176;       // both groups published their row sums
-  const uint32_t bar_ofull = bar0 + 184;        // every MMA of the work item complete
-  const uint32_t bar_ofree = bar0 + 192;        // O read out: the next item's first sweep may use its columns
-  const uint32_t bar_vfull = bar0 + 200;        // [3]  v^T ring
-  const uint32_t bar_vempty = bar0 + 224;       // [3]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 31);
+  const uint32_t bar_sfull = bar0 + 64;         // [2]  scores of a block complete
+  const uint32_t bar_pready = bar0 + 80;        // [2]  weights written over the scores
+  const uint32_t bar_pvdone = bar0 + 96;        // [2]  P*V of a block complete
+  const uint32_t bar_qready = bar0 + 112;       // Q planes in tensor memory
+  const uint32_t bar_lready = bar0 + 120;       // both groups published their row sums
+  const uint32_t bar_ofull = bar0 + 128;        // every MMA of the work item complete
+  const uint32_t bar_vfull = bar0 + 136;        // [3]  v^T ring
+  const uint32_t bar_vempty = bar0 + 160;       // [3]
+  const uint32_t bar_pair = bar0 + 184;         // [4]  the two softmax warps that own the same 32 rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 27);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert(2048 + 31 * 8 + 8 <= kABookBytes, "book too small");
+  static_assert(2048 + 27 * 8 + 8 <= kABookBytes, "book too small");
 
   if (base - raw > (uint32_t)kAAlignSlack) {
     // the dynamic shared memory starts further from a 1024-byte boundary than the launch
@@ -196,9 +194,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
       mbar_init(bar_kfull + 8 * i, 1);
       mbar_init(bar_kempty + 8 * i, 1);
     }
-    for (int i = 0; i < 3; i++) {
-      mbar_init(bar_s1full + 8 * i, 1);
-      mbar_init(bar_s1free + 8 * i, 8);
+    for (int i = 0; i < kVStages; i++) {
       mbar_init(bar_vfull + 8 * i, 1);
       mbar_init(bar_vempty + 8 * i, 1);
     }
@@ -207,11 +203,10 @@ __global__ void __launch_bounds__(kAThreads, 1)
       mbar_init(bar_pready + 8 * i, 8);
       mbar_init(bar_pvdone + 8 * i, 1);
     }
+    for (int i = 0; i < 4; i++) mbar_init(bar_pair + 8 * i, 2);
     mbar_init(bar_qready, 4);
-    mbar_init(bar_mready, 8);
     mbar_init(bar_lready, 8);
     mbar_init(bar_ofull, 1);
-    mbar_init(bar_ofree, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -232,17 +227,16 @@ __global__ void __launch_bounds__(kAThreads, 1)
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------ TMA producer of k: a ring of four
-      // slots of one plane (two boxes of 128 keys x 64 dims); a block of sweep 1 takes one slot
-      // (hi), a block of sweep 2 two (hi, then lo)
+      // slots of one plane (two boxes of 128 keys x 64 dims); a key block takes two (hi, then lo)
       const uint64_t keep = policy_evict_last();
       uint32_t slot = 0, phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int h = item / nqt;
-        for (int n = 0; n < 3 * nblk; n++) {
-          const int j = n < nblk ? n : (n - nblk) >> 1;
-          const bool lo = n >= nblk && ((n - nblk) & 1);
-          ok = mbar_wait(bar_kempty + 8 * slot, phase ^ 1u, abort_flag, g.status, 0x800 | (n < nblk ? 1 : 2));
+        for (int n = 0; n < 2 * nblk; n++) {
+          const int j = n >> 1;
+          const bool lo = n & 1;
+          ok = mbar_wait(bar_kempty + 8 * slot, phase ^ 1u, abort_flag, g.status, 0x800 | 1);
           if (!ok) break;
           const uint32_t full = bar_kfull + 8 * slot;
           const uint32_t st = base + slot * kKPlane;
@@ -278,62 +272,28 @@ __global__ void __launch_bounds__(kAThreads, 1)
   } else if (warp == 1 || warp == 12) {
     if (lane == 0) {
       // ------------------------------------------------ MMA issuers of the scores: this lane
-      // takes the blocks of one parity (warp 1 the even ones, warp 12 the odd ones) in both
-      // sweeps.  The k ring is shared: slot number `seq` of the CTA's whole run is ring slot
-      // seq & 3, whose full barrier completes its phase (seq >> 2) & 1 for it.
+      // takes the blocks of one parity (warp 1 the even ones, warp 12 the odd ones), i.e. always
+      // the same score buffer.  The k ring is shared: slot number `seq` of the CTA's whole run
+      // is ring slot seq & 3, whose full barrier completes its phase (seq >> 2) & 1 for it.
       const uint32_t par = warp == 1 ? 0u : 1u;
-      const uint32_t d2 = tmem_base + kColS + par * kBkv;   // sweep 2: always the same buffer
-      uint32_t s1_uses[3] = {0, 0, 0};          // sweep 1: uses of each score buffer before this item
+      const uint32_t d2 = tmem_base + kColS + par * kBkv;
       uint32_t pv_ph = 0;                       // completed phases of pvdone[par]
-      uint32_t q_ph = 0, m_ph = 0, ofree_ph = 0;
+      uint32_t q_ph = 0;
       uint32_t seq0 = 0;                        // k-ring sequence number of the item's first slot
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        // Q of this item is in tensor memory (written after every MMA of the previous item had
+        // completed)
         ok = mbar_wait_spin(bar_qready, q_ph, abort_flag, g.status, 0x900 | 1);
         q_ph ^= 1u;
         if (!ok) break;
-        // the previous item's O has been read out (and so every MMA of that item is complete):
-        // sweep 1 borrows its columns
-        ok = mbar_wait_spin(bar_ofree, ofree_ph ^ 1u, abort_flag, g.status, 0x900 | 5);
-        ofree_ph ^= 1u;
-        if (!ok) break;
         tc_fence_after();
-        // ---- sweep 1: hi*hi scores for the row maxima (11 mantissa bits are ample for an
-        // offset), 128 keys and 16 dims per MMA, rotating over three buffers: the two score
-        // buffers and the idle O columns
-        for (int j = (int)par; j < nblk; j += 2) {
-          const uint32_t seq = seq0 + (uint32_t)j, slot = seq & 3u;
-          const uint32_t b3 = (uint32_t)j % 3u, use = s1_uses[b3] + (uint32_t)j / 3u;
-          ok = mbar_wait_spin(bar_kfull + 8 * slot, (seq >> 2) & 1u, abort_flag, g.status, 0x900 | 2);
-          if (!ok) break;
-          ok = mbar_wait_spin(bar_s1free + 8 * b3, (use & 1u) ^ 1u, abort_flag, g.status, 0x900 | 3);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t st = base + slot * kKPlane;
-          const uint32_t d = tmem_base + (b3 == 2 ? kColO : kColS + b3 * kBkv);
-#pragma unroll
-          for (int ks = 0; ks < kHd / 16; ks++) {
-            const uint64_t k_hi = make_smem_desc(st + (uint32_t)((ks >> 2) * 16384)) + (uint64_t)((ks & 3) * 2);
-            umma_f16_ts(d, tmem_base + kColQhi + ks * 8, k_hi, kIdescH, (uint32_t)(ks != 0));
-          }
-          umma_commit(bar_kempty + 8 * slot);
-          umma_commit(bar_s1full + 8 * b3);
-        }
-        if (!ok) break;
-#pragma unroll
-        for (int b = 0; b < 3; b++) s1_uses[b] += (uint32_t)(nblk > b ? (nblk - b + 2) / 3 : 0);
-        // the softmax groups have read every score of sweep 1 and published the maxima
-        ok = mbar_wait_spin(bar_mready, m_ph, abort_flag, g.status, 0x900 | 4);
-        m_ph ^= 1u;
-        if (!ok) break;
-        tc_fence_after();
-        // ---- sweep 2: accurate scores of this lane's blocks, three MMAs per 16 dims (the two
-        // small cross terms first).  The buffer is free again when the P*V of the block two back
-        // has consumed its weights; the k slots are released as soon as the scores that read
-        // them are done.
+        // scores of this lane's blocks, three MMAs per 16 dims (the two small cross terms
+        // first).  The buffer is free again when the P*V of the block two back has consumed its
+        // weights; the k slots are released as soon as the scores that read them are done.
         bool any = false;
         for (int j = (int)par; j < nblk; j += 2) {
-          const uint32_t seq = seq0 + (uint32_t)(nblk + 2 * j);
+          const uint32_t seq = seq0 + (uint32_t)(2 * j);
           const uint32_t slot_hi = seq & 3u, slot_lo = (seq + 1) & 3u;
           ok = mbar_wait_spin(bar_kfull + 8 * slot_hi, (seq >> 2) & 1u, abort_flag, g.status, 0x900 | 7);
           if (!ok) break;
@@ -367,7 +327,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
           pv_ph ^= 1u;
           if (!ok) break;
         }
-        seq0 += (uint32_t)(3 * nblk);
+        seq0 += (uint32_t)(2 * nblk);
       }
     }
   } else if (warp == 11) {
@@ -377,8 +337,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
       uint32_t pready_ph[2] = {0, 0};
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-        // (O is free: every softmax warp read the previous item's O out, and the first sweep that
-        // borrowed its columns was read, before any could arrive on this item's first pready)
+        // (O is free: every softmax warp read the previous item's O out before it could arrive
+        // on this item's first pready)
         for (int j = 0; ok && j < nblk; j++) {
           const uint32_t buf = (uint32_t)(j & 1);
           ok = mbar_wait_spin(bar_pready + 8 * buf, pready_ph[buf], abort_flag, g.status, 0x900 | 9);
@@ -421,9 +381,19 @@ __global__ void __launch_bounds__(kAThreads, 1)
     const uint32_t s_col = tmem_base + kColS + (uint32_t)grp * 64 + lane_base;  // + buffer * kBkv
     const int sh_k = operand_shift(g.absmax[0]), sh_v = operand_shift(g.absmax[1]);
     uint32_t sfull_ph[2] = {0, 0};
-    uint32_t s1_uses[3] = {0, 0, 0};        // sweep 1: uses of each score buffer before this item
-    uint32_t m_ph = 0, l_ph = 0, ofull_ph = 0;
+    uint32_t pv_uses[2] = {0, 0};           // P*V completions on each score buffer before this item
+    uint32_t l_ph = 0, ofull_ph = 0, pair_ph = 0;
     bool ok = true;
+    // Meeting point of this warp and the one of the other group that owns the same rows (an
+    // mbarrier like every other wait here, so that it is bounded): what either wrote to shared
+    // memory before it is visible to the other after it.
+    auto pair_sync = [&]() {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pair + 8 * quarter);
+      const bool r = mbar_wait_warp(bar_pair + 8 * quarter, pair_ph, abort_flag, g.status, 0xa00 | 7);
+      pair_ph ^= 1u;
+      return r;
+    };
     for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
       const int h = item / nqt, qt = item - h * nqt;
       const int64_t q0 = (int64_t)qt * kBq;
@@ -467,45 +437,12 @@ __global__ void __launch_bounds__(kAThreads, 1)
       // (each factor a normal float; the product may round to zero or infinity only where the
       // reference's own scores leave the fp32 range)
       const float sc = __fmul_rn(__fmul_rn(g.scale_log2e, pow2f(-sh_q)), pow2f(-sh_k));
-      // ---- sweep 1: the row maximum over this group's half of every block (raw dot products)
-      float m = -INFINITY;
-      for (int j = 0; j < nblk; j++) {
-        const uint32_t b3 = (uint32_t)j % 3u, use = s1_uses[b3] + (uint32_t)j / 3u;
-        ok = mbar_wait_warp(bar_s1full + 8 * b3, use & 1u, abort_flag, g.status, 0xa00 | 1);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t x_col = tmem_base + (b3 == 2 ? kColO : kColS + b3 * kBkv) + (uint32_t)grp * 64 + lane_base;
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(x_col, r0);
-        tmem_ld_32x32(x_col + 32, r1);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_s1free + 8 * b3);
-        const int64_t key0 = (int64_t)j * kBkv + grp * 64;
-        if (key0 + 64 <= g.Lk) {
-#pragma unroll
-          for (int t = 0; t < 32; t++) m = fmaxf(m, fmaxf(__uint_as_float(r0[t]), __uint_as_float(r1[t])));
-        } else {
-#pragma unroll
-          for (int t = 0; t < 32; t++) {
-            if (key0 + t < g.Lk) m = fmaxf(m, __uint_as_float(r0[t]));
-            if (key0 + 32 + t < g.Lk) m = fmaxf(m, __uint_as_float(r1[t]));
-          }
-        }
-      }
-      if (!ok) break;
-#pragma unroll
-      for (int b = 0; b < 3; b++) s1_uses[b] += (uint32_t)(nblk > b ? (nblk - b + 2) / 3 : 0);
-      x_max[grp * kBq + row_in_tile] = m;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_mready);
-      ok = mbar_wait_warp(bar_mready, m_ph, abort_flag, g.status, 0xa00 | 2);
-      m_ph ^= 1u;
-      if (!ok) break;
-      m = fmaxf(x_max[row_in_tile], x_max[kBq + row_in_tile]);
-      // ---- sweep 2: weights p = 2^10 exp2((s - m) * sc) as fp16 pairs, written over the scores
-      const float e_off = __fsub_rn(kPShift, __fmul_rn(m, sc));
+      // ---- one sweep over the keys with a running offset m_run per row (raw dot products):
+      // weights p = 2^10 exp2((s - m_run) * sc).  The offset only moves when a block's maximum
+      // exceeds it by more than kRescaleStep log2 units (the fp16 weights have room up to 2^15.8);
+      // then O and the row sum are scaled down once, after the P*V that is still accumulating
+      // into O has completed.  On ordinary data that happens in the first block or two of a row.
+      float m_run = -INFINITY, e_off = 0.0f;
       float l = 0.0f;
       uint32_t hmax = 0;   // largest fp16 bit patterns of the weights' hi parts (two halves)
       for (int j = 0; j < nblk; j++) {
@@ -520,6 +457,53 @@ __global__ void __launch_bounds__(kAThreads, 1)
         tmem_ld_wait();
         const int64_t key0 = (int64_t)j * kBkv + grp * 64;
         const int valid = (int)min((int64_t)64, g.Lk - key0);  // < 64 only in the last block
+        // the block's maximum over this group's keys, then over the row's other 64 keys (the
+        // thread of the other group that owns the same row), through shared memory
+        float bm = -INFINITY;
+        if (valid >= 64) {
+#pragma unroll
+          for (int t = 0; t < 32; t++) bm = fmaxf(bm, fmaxf(__uint_as_float(r0[t]), __uint_as_float(r1[t])));
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; t++) {
+            if (t < valid) bm = fmaxf(bm, __uint_as_float(r0[t]));
+            if (32 + t < valid) bm = fmaxf(bm, __uint_as_float(r1[t]));
+          }
+        }
+        float* xb = (j & 1) ? x_sum : x_max;          // alternating, so that one meeting per block is enough
+        xb[grp * kBq + row_in_tile] = bm;
+        ok = pair_sync();
+        if (!ok) break;
+        bm = fmaxf(bm, xb[(grp ^ 1) * kBq + row_in_tile]);
+        const bool grow = __fmul_rn(__fsub_rn(bm, m_run), sc) > kRescaleStep;   // (true in the first block)
+        if (__any_sync(0xffffffffu, grow)) {
+          float f = 1.0f;
+          if (grow) {
+            if (j > 0) asm("ex2.approx.f32 %0, %1;" : "=f"(f) : "f"(__fmul_rn(__fsub_rn(m_run, bm), sc)));
+            m_run = bm;
+            e_off = __fsub_rn(kPShift, __fmul_rn(m_run, sc));
+            l = __fmul_rn(l, f);
+          }
+          if (j > 0) {
+            // O holds the blocks so far: the last P*V must have completed before O is scaled
+            // (the next one waits for this block's weights).  The whole warp takes part in the
+            // tensor-memory traffic; rows whose offset did not move scale by one.
+            const uint32_t pb = (uint32_t)((j - 1) & 1);
+            ok = mbar_wait_warp(bar_pvdone + 8 * pb, (pv_uses[pb] + (uint32_t)((j - 1) >> 1)) & 1u, abort_flag,
+                                g.status, 0xa00 | 6);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 2 * grp; c < 2 * grp + 2; c++) {
+              uint32_t o[32];
+              tmem_ld_32x32(tmem_base + kColO + c * 32 + lane_base, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int t = 0; t < 32; t++) o[t] = __float_as_uint(__fmul_rn(__uint_as_float(o[t]), f));
+              tmem_st_32x32(tmem_base + kColO + c * 32 + lane_base, o);
+            }
+          }
+        }
         // each 32 columns become: 16 columns of fp16 pairs p_hi, then 16 of p_lo.  The row sum
         // adds the weights themselves (they differ from hi + lo by 2^-22 at most).  A weight
         // beyond fp16's range (offset far too low) becomes an infinity that spoils only its own
@@ -564,6 +548,10 @@ __global__ void __launch_bounds__(kAThreads, 1)
         if (lane == 0) mbar_arrive(bar_pready + 8 * buf);
       }
       if (!ok) break;
+      pv_uses[0] += (uint32_t)((nblk + 1) >> 1);
+      pv_uses[1] += (uint32_t)(nblk >> 1);
+      ok = pair_sync();   // the partner has read this thread's last block maximum out of x_sum
+      if (!ok) break;
       x_sum[grp * kBq + row_in_tile] = l;
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_lready);
@@ -598,9 +586,8 @@ __global__ void __launch_bounds__(kAThreads, 1)
                                __fmul_rn(__uint_as_float(r[j + 2]), inv), __fmul_rn(__uint_as_float(r[j + 3]), inv)));
         }
       }
+      // (the reads of O are complete: the next item's first pready arrival tells the P*V issuers)
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ofree);
     }
   }
 

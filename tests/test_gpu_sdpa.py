@@ -105,6 +105,25 @@ def test_operand_magnitudes(sdq, sq, sk, sv):
     assert max_rel_err(got, want) < max(3e-4 if sq * sk > 100 else 1e-4, 2 * fp32_err)
 
 
+def test_scores_growing_along_the_keys(sdq):
+    """Key magnitudes ramp up by 40x along the key axis, so every row's running maximum moves
+    many times (the accumulated output and row sum are rescaled each time), by different amounts
+    in different rows of one tile."""
+    rng = np.random.default_rng(33)
+    heads, Lq, Lk = 2, 300, 1700
+    C = heads * 128
+    q = (rng.standard_normal((Lq, C)) * np.linspace(0.3, 2.0, Lq)[:, None]).astype(np.float32)
+    k = (rng.standard_normal((Lk, C)) * np.linspace(0.1, 4.0, Lk)[:, None]).astype(np.float32)
+    v = rng.standard_normal((Lk, C)).astype(np.float32)
+    got = sdq.sdpa_np(q, k, v, heads)
+    want = attention64(q, k, v, heads)
+    assert np.isfinite(got).all()
+    assert max_rel_err(got, want) < 1e-4
+    # and the reverse order: the maximum is found at once, later blocks only add small weights
+    got = sdq.sdpa_np(q, k[::-1].copy(), v[::-1].copy(), heads)
+    assert max_rel_err(got, want) < 1e-4
+
+
 def test_other_head_sizes_take_the_cuda_core_kernel(sdq):
     rng = np.random.default_rng(2)
     for heads, hd, Lq, Lk in [(3, 64, 40, 77), (2, 96, 9, 130), (1, 20, 5, 3)]:
