@@ -264,8 +264,9 @@ SDQ_API int sdq_fmatmul(sdq_weight_t w, const float* A, int64_t M, float* out,
  * [h*C/heads, (h+1)*C/heads).  For head_dim 128 (the DiT's) everything runs on the tensor
  * cores: q, k, v and the softmax weights are each carried as two fp16 numbers times a power of
  * two (22 mantissa bits; the powers are found from the data, so magnitudes do not matter), every
- * product is three fp16 MMAs with fp32 accumulation, and the row maximum comes from a first
- * sweep over the keys, so no accumulator is rescaled.  Rows whose scores are out of that
+ * product is three fp16 MMAs with fp32 accumulation, in one sweep over the keys with a running
+ * offset per row (the accumulator is rescaled only when a row's maximum moves by more than 4
+ * log2 units, i.e. in its first blocks).  Rows whose scores are out of that
  * scheme's range (|score| in the tens of thousands) are recomputed in plain fp32 by the CUDA-core
  * kernel that also serves the other head sizes.  Held to the reference's 1e-3 bound (max-abs
  * error / max-abs output; ~1e-5 measured at a few thousand keys, 1e-4 at 27280); exp and the

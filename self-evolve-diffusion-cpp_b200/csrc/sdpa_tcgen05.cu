@@ -17,38 +17,38 @@
 // the factor the scores are multiplied by anyway, v's in the final 1 / row sum; the weights' cancels.
 // The row sums add the weights themselves, so numerator and denominator agree.
 //
-// Softmax without rescaling.  A first sweep over the keys finds each row's maximum from the
-// hi*hi scores alone (any value near the true maximum serves as the offset, as long as numerator
-// and denominator use the same one); a second sweep recomputes the scores accurately,
-// exponentiates and accumulates P*V in tensor memory for the whole key range.  No accumulator is
-// ever rescaled.  The offset must be within a few log2 units of the true maximum for the fp16
-// weights to keep their bits: where it is not (a weight reaches 2^15.8, or a row sum stays below
-// 2^3 -- scores in the tens of thousands, where the hi*hi scores of the first sweep are off by
-// that much), the row is marked and recomputed afterwards in plain fp32 on the CUDA cores by the
-// kernel that also serves the other head sizes.  So is a row whose scores can be so large
-// (head_dim * max|q_row| * max|k| / sqrt(head_dim) above 2^19 log2 units) that the dropped lo*lo
-// terms, 2^-22 of the products, would reach the weights.  A NaN row sum marks its row too.
+// One sweep over the keys.  Each row carries a running offset m (a raw dot product): weights are
+// p = 2^10 exp((s - m) scale), O accumulates P*V in tensor memory for the whole key range.  Any
+// value near the row's maximum serves as the offset, as long as numerator and denominator use
+// the same one, and the fp16 weights have room up to 2^15.8: so the offset only moves when a
+// block's maximum exceeds it by more than 4 log2 units, and only then O and the row sum are
+// scaled down (by the softmax threads, after the P*V that was accumulating into O has
+// completed) -- on ordinary data in the first block or two of a row, never afterwards.  The two
+// threads that share a row (one per 64 of a block's 128 keys) exchange their block maxima
+// through shared memory, so both always hold the same offset.  A row whose scores can be so
+// large (head_dim * max|q_row| * max|k| / sqrt(head_dim) above 2^19 log2 units) that the dropped
+// lo*lo terms, 2^-22 of the products, would reach the weights is marked and recomputed
+// afterwards in plain fp32 on the CUDA cores by the kernel that also serves the other head
+// sizes; so is a row whose sum is not finite or whose weights left fp16's range.
 //
 // One CTA per (128 query rows, head), persistent over these work items; 416 threads:
 //   warp 0 lane 0 : TMA producer of k: a ring of four 32 KiB slots, one plane of 128 keys each
-//                   (128-byte-swizzled boxes of 128 keys x 64 dims): the hi plane per block in
-//                   sweep 1, hi and lo in sweep 2; released as soon as a block's scores are done.
-//                   A load takes ~1500 cycles from release to landed, three times what the MMAs
-//                   of a block of sweep 1 take: hence four slots.
+//                   (128-byte-swizzled boxes of 128 keys x 64 dims), hi then lo per key block;
+//                   released as soon as a block's scores are done (a load takes ~1500 cycles
+//                   from release to landed).
 //   warp 10 lane 0: TMA producer of v^T (hi and lo planes, 64 keys per stage, its own three-stage
 //                   ring released by the P*V MMAs).
 //   warp 1 lane 0 : MMA issuer of the scores of the even key blocks.  S = Q K^T with Q as the
 //   warp 12 lane 0: ... and of the odd key blocks.  A operand in TENSOR MEMORY, K from shared memory.
 //   warp 11 lane 0: MMA issuer of O += P V, with P in tensor memory (written in place over S by
-//                   the softmax warps) and V^T from shared memory.  Issuing a small MMA costs the
-//                   issuing lane about as long as the tensor pipe needs for it, so the
-//                   instruction streams come from three lanes.
+//                   the softmax warps) and V^T from shared memory.  A lane gets one of these
+//                   MMAs out every ~90-125 cycles whatever its width, the tensor pipe needs 64
+//                   for a 128-wide one: the pipe is full when two lanes issue at the same time.
 //   warps 2..5    : softmax group A (one thread per query row): the first 64 keys of every block.
 //   warps 6..9    : softmax group B: the other 64 keys.  Both groups finish the tile together:
 //                   O / row sum, each thread storing its row's 128-byte pieces.
 // Tensor memory (512 columns, two fp16 per column for the A operands): Q_hi 0..63, Q_lo 64..127,
-// O 128..255, S/P buffers 256..383 and 384..511; sweep 1 rotates its scores over the two S
-// buffers and the O columns, so that the read-out of one block hides behind the MMAs of two.  Every mbarrier wait is bounded like the GEMM
+// O 128..255, S/P buffers 256..383 and 384..511.  Every mbarrier wait is bounded like the GEMM
 // kernels'.
 #include "tc_common.cuh"
 
