@@ -65,7 +65,7 @@ constexpr int kVKeys = 64;          // keys per stage of the v^T ring
 constexpr int kKPlane = kBkv * kHd * 2;         // 32 KiB: one fp16 plane of a key block
 constexpr int kVPlane = kHd * kVKeys * 2;       // 16 KiB: one fp16 plane of 64 keys of v^T
 constexpr int kVStageBytes = 2 * kVPlane;       // v^T hi + lo
-constexpr int kKSlots = 4;                 // k ring: slots of one plane (sweep 1 takes one per key block, sweep 2 two)
+constexpr int kKSlots = 4;                 // k ring: slots of one plane (a key block takes two: hi, lo)
 constexpr int kVStages = 3;                // v^T ring
 constexpr int kARingBytes = kKSlots * kKPlane + kVStages * kVStageBytes;   // 224 KiB
 constexpr int kAThreads = kNumThreads + 96;  // + three warps: v^T producer, P*V issuer, second score issuer
@@ -73,8 +73,8 @@ constexpr int kABookBytes = 2304;    // row maxima and sums of both groups (2 Ki
 constexpr int kAAlignSlack = 768;    // to bring the dynamic base to a 1024-byte boundary
 constexpr int kASmemBytes = kARingBytes + kABookBytes + kAAlignSlack;  // 227 KiB
 constexpr uint32_t kColQhi = 0, kColQlo = 64, kColO = 128, kColS = 256;
-constexpr float kPShift = 10.0f;     // the softmax weights are carried as p * 2^10 (<= 2^10 up to
-                                     // the error of the first sweep's maxima)
+constexpr float kPShift = 10.0f;     // the softmax weights are carried as p * 2^10 (p relative to the
+                                     // row's running offset: at most 2^kRescaleStep)
 constexpr uint32_t kPHalfTop = 0x7b00;  // fp16 bits of 2^15.8: no finite weight gets there
 constexpr float kRowSumFloor = 8.0f;    // (a row sum is at least 2^10 / 2^kRescaleStep unless something is not finite)
 constexpr float kRescaleStep = 4.0f;    // log2 units by which a block's maximum may exceed the running
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
     }
   } else if (warp == 10) {
     if (lane == 0) {
-      // ------------------------------------------------ TMA producer of v^T (sweep 2 only):
+      // ------------------------------------------------ TMA producer of v^T:
       // the two fp16 planes, one box of 128 dims x 64 keys each per stage
       const uint64_t keep = policy_evict_last();
       uint32_t stage = 0, phase = 0;

@@ -78,14 +78,14 @@ def test_peaked_and_shifted_scores(sdq):
     (1e4, 1e-4, 1e6),       # magnitudes far outside fp16 on every operand
     (1e-6, 1e6, 1e-9),
     (3e-12, 2e-13, 1.0),    # scores ~ 0: uniform weights
-    (30.0, 30.0, 1.0),      # scores ~ 1e4: the first sweep's maxima are off by whole log2 units
+    (30.0, 30.0, 1.0),      # scores ~ 1e4: the 22 bits of the split operands begin to show
     (300.0, 300.0, 1e20),   # scores ~ 1e6: one key takes each row; rows recomputed in plain fp32
 ])
 def test_operand_magnitudes(sdq, sq, sk, sv):
     """The fp16 planes carry q, k and v times powers of two chosen from the data (per query row,
     per k, per v), so the magnitudes of the inputs do not matter; rows of very different size
-    sit in one tile.  Where the scores are so large that the first sweep's offset is useless the
-    marked rows come from the fp32 CUDA-core kernel."""
+    sit in one tile.  Where the scores can be so large that the dropped lo*lo terms would show,
+    the rows are marked and come from the fp32 CUDA-core kernel."""
     rng = np.random.default_rng(5)
     heads, Lq, Lk = 2, 257, 391
     C = heads * 128
