@@ -60,6 +60,10 @@ typedef uint64_t sdq_weight_t;
 
 #define SDQ_LN_AFFINE 0x40u  /* sdq_layernorm_mod_quantize: `scale` and `shift` are the layernorm's
                                 own weight and bias, h = ln * weight + bias */
+#define SDQ_SDPA_V_FP16 0x80u /* sdq_sdpa: v enters P*V as one fp16 number per element (11 mantissa
+                               * bits, after its power-of-two scaling) instead of two: two MMAs per
+                               * product instead of three and half the v^T traffic; outputs move by
+                               * up to ~2.5e-4 of the largest (inside the reference's 1e-3 bound) */
 
 /* source element types of sdq_quantize_rows (the packer's SRC table,
  * tools/quantize/pack_sdcpp.py:26-35) */
@@ -269,7 +273,8 @@ SDQ_API int sdq_fmatmul(sdq_weight_t w, const float* A, int64_t M, float* out,
  * log2 units, i.e. in its first blocks).  Rows whose scores are out of that
  * scheme's range (|score| in the tens of thousands) are recomputed in plain fp32 by the CUDA-core
  * kernel that also serves the other head sizes.  Held to the reference's 1e-3 bound (max-abs
- * error / max-abs output; ~1e-5 measured at a few thousand keys, 1e-4 at 27280); exp and the
+ * error / max-abs output; ~1e-5 measured at a few thousand keys, 1e-4 at 27280; flags may carry
+ * SDQ_SDPA_V_FP16, SDQ_FORCE_SIMT, SDQ_SYNC); exp and the
  * summation order are not bit-identical to the CPU's, but two runs give the same bits. */
 SDQ_API int sdq_sdpa(const float* q_dev, const float* k_dev, const float* v_dev, int64_t Lq,
                      int64_t Lk, int64_t C, int heads, float* out_dev, uint32_t flags,

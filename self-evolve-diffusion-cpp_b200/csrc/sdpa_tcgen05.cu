@@ -141,6 +141,7 @@ struct SdpaArgs {
   uint8_t* redo;           // [Lq, heads], zero on entry: 1 = recompute this row in plain fp32
   int64_t Lq, Lk, C;
   int heads;
+  int v_lo;          // 1: P*V uses both planes of v^T (three MMAs per product), 0: the hi plane only (two)
   float scale_log2e;  // (1 / sqrt(head_dim)) * log2(e)
   int* status;
 };
@@ -262,9 +263,9 @@ __global__ void __launch_bounds__(kAThreads, 1)
           if (!ok) break;
           const uint32_t full = bar_vfull + 8 * stage;
           const uint32_t st = smem_v + stage * kVStageBytes;
-          mbar_expect_tx(full, kVStageBytes);
+          mbar_expect_tx(full, g.v_lo ? kVStageBytes : kVPlane);
           tma_load_2d_hint(st, &tmap_vt_hi, full, j * kVKeys, h * kHd, keep);
-          tma_load_2d_hint(st + kVPlane, &tmap_vt_lo, full, j * kVKeys, h * kHd, keep);
+          if (g.v_lo) tma_load_2d_hint(st + kVPlane, &tmap_vt_lo, full, j * kVKeys, h * kHd, keep);
           if (++stage == kVStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -359,7 +360,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
               const uint64_t v_lo = make_smem_desc(vt + kVPlane) + (uint64_t)(ks * 2);
               const uint32_t p_hi = pcol + (uint32_t)((hf * 2 + (ks >> 1)) * 32 + (ks & 1) * 8);
               umma_f16_ts(tmem_base + kColO, p_hi + 16, v_hi, kIdescH, (uint32_t)((j | hf | ks) != 0));
-              umma_f16_ts(tmem_base + kColO, p_hi, v_lo, kIdescH, 1u);
+              if (g.v_lo) umma_f16_ts(tmem_base + kColO, p_hi, v_lo, kIdescH, 1u);
               umma_f16_ts(tmem_base + kColO, p_hi, v_hi, kIdescH, 1u);
             }
             umma_commit(bar_vempty + 8 * vstage);
@@ -796,6 +797,7 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
       !make_tmap_vt(&t_vt_hi, vt_hi, C, Lk, ld, why) || !make_tmap_vt(&t_vt_lo, vt_lo, C, Lk, ld, why))
     return cudaErrorInvalidValue;
   SdpaArgs g;
+  g.v_lo = (flags & SDQ_SDPA_V_FP16) ? 0 : 1;
   g.q = q; g.out = out; g.absmax = absmax; g.redo = redo; g.Lq = Lq; g.Lk = Lk; g.C = C; g.heads = heads;
   g.scale_log2e = scale * 1.4426950408889634f;
   g.status = status;

@@ -124,6 +124,20 @@ def test_scores_growing_along_the_keys(sdq):
     assert max_rel_err(got, want) < 1e-4
 
 
+def test_v_as_one_fp16_number(sdq):
+    """SDQ_SDPA_V_FP16: two MMAs per P*V product; v rounded to 11 bits moves the outputs by a few
+    1e-4 at most, inside the reference's 1e-3 bound."""
+    rng = np.random.default_rng(12)
+    heads, Lq, Lk = 3, 500, 1111
+    q, k, v = [rng.standard_normal((n, heads * 128)).astype(np.float32) for n in (Lq, Lk, Lk)]
+    q *= 3.0                                              # peaked rows: little averaging of v's rounding
+    want = attention64(q, k, v, heads)
+    full = sdq.sdpa_np(q, k, v, heads)
+    fast = sdq.sdpa_np(q, k, v, heads, v_fp16=True)
+    assert max_rel_err(full, want) < 2e-5
+    assert 2e-5 < max_rel_err(fast, want) < 4e-4           # (the flag did something, and stayed in bounds)
+
+
 def test_other_head_sizes_take_the_cuda_core_kernel(sdq):
     rng = np.random.default_rng(2)
     for heads, hd, Lq, Lk in [(3, 64, 40, 77), (2, 96, 9, 130), (1, 20, 5, 3)]:
