@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
       mbar_init(bar_pvdone + 8 * i, 1);
     }
     for (int i = 0; i < 4; i++) mbar_init(bar_pair + 8 * i, 2);
-    mbar_init(bar_qready, 4);
+    mbar_init(bar_qready, 8);
     mbar_init(bar_lready, 8);
     mbar_init(bar_ofull, 1);
     *abort_flag = 0;
@@ -399,36 +399,49 @@ __global__ void __launch_bounds__(kAThreads, 1)
       const int h = item / nqt, qt = item - h * nqt;
       const int64_t q0 = (int64_t)qt * kBq;
       const int64_t row = q0 + row_in_tile;
-      const float* qrow = g.q + row * g.C + (int64_t)h * kHd;
-      // the power of two for this thread's query row
-      int sh_q = 0;
+      // This thread's half of its query row (this group's 64 dims) -> registers; the row's
+      // largest magnitude from both halves (the other one through shared memory) gives its
+      // power of two; then fp16 hi and lo of q * 2^sh_q -> tensor memory, two elements per
+      // column (zeros past Lq).
+      const float* qhalf = g.q + row * g.C + (int64_t)h * kHd + grp * 64;
+      float4 qv[16];
       uint32_t mx = 0;
-      if (row < g.Lq) {
-#pragma unroll 4
-        for (int j = 0; j < kHd; j += 4) {
-          const float4 v = *reinterpret_cast<const float4*>(qrow + j);
-          mx = max(max(mx, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)),
-                   max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
-        }
-        sh_q = operand_shift(mx);
-      }
-      if (grp == 0) {
-        // this thread's query row -> tensor memory (zeros past Lq): fp16 hi and lo of
-        // q * 2^sh_q, two elements per column
-        const float qs = pow2f(sh_q);
-#pragma unroll 1
-        for (int c = 0; c < kHd / 64; c++) {
-          uint32_t hi[32], lo[32];
 #pragma unroll
-          for (int j = 0; j < 64; j += 4) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (row < g.Lq) v = *reinterpret_cast<const float4*>(qrow + c * 64 + j);
-            split_f16x2(__fmul_rn(v.x, qs), __fmul_rn(v.y, qs), hi[j >> 1], lo[j >> 1]);
-            split_f16x2(__fmul_rn(v.z, qs), __fmul_rn(v.w, qs), hi[(j >> 1) + 1], lo[(j >> 1) + 1]);
+      for (int j = 0; j < 16; j++) {
+        qv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < g.Lq) qv[j] = *reinterpret_cast<const float4*>(qhalf + 4 * j);
+      }
+      {  // the next work item's rows on their way into L2 meanwhile
+        const int nxt = item + (int)gridDim.x;
+        if (nxt < num_items) {
+          const int h2 = nxt / nqt, qt2 = nxt - h2 * nqt;
+          const int64_t row2 = (int64_t)qt2 * kBq + row_in_tile;
+          if (row2 < g.Lq) {
+            const float* nq = g.q + row2 * g.C + (int64_t)h2 * kHd + grp * 64;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nq));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nq + 32));
           }
-          tmem_st_32x32(tmem_base + kColQhi + c * 32 + lane_base, hi);
-          tmem_st_32x32(tmem_base + kColQlo + c * 32 + lane_base, lo);
         }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        mx = max(max(mx, __float_as_uint(fabsf(qv[j].x))), max(__float_as_uint(fabsf(qv[j].y)),
+                 max(__float_as_uint(fabsf(qv[j].z)), __float_as_uint(fabsf(qv[j].w)))));
+      x_max[grp * kBq + row_in_tile] = __uint_as_float(mx);
+      ok = pair_sync();
+      if (!ok) break;
+      mx = max(mx, __float_as_uint(x_max[(grp ^ 1) * kBq + row_in_tile]));
+      const int sh_q = row < g.Lq ? operand_shift(mx) : 0;
+      {
+        const float qs = pow2f(sh_q);
+        uint32_t hi[32], lo[32];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          split_f16x2(__fmul_rn(qv[j].x, qs), __fmul_rn(qv[j].y, qs), hi[2 * j], lo[2 * j]);
+          split_f16x2(__fmul_rn(qv[j].z, qs), __fmul_rn(qv[j].w, qs), hi[2 * j + 1], lo[2 * j + 1]);
+        }
+        tmem_st_32x32(tmem_base + kColQhi + grp * 32 + lane_base, hi);
+        tmem_st_32x32(tmem_base + kColQlo + grp * 32 + lane_base, lo);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
