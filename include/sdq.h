@@ -129,6 +129,8 @@ SDQ_API int sdq_weight_wrap_device(const int8_t* q_dev, const float* scale_dev, 
 /* Finds the weight uploaded from host address `q_host` (the key the reference's
  * caller has in hand: blk::Linear::w.data, src/model/ovi_dit.cpp:66-70). */
 SDQ_API int sdq_weight_lookup(const void* q_host, sdq_weight_t* out);
+/* Extents and device addresses of a weight; for an fp32 weight (sdq_fweight_upload) q_dev and
+ * scale_dev are reported as NULL.  Any out pointer may be NULL. */
 SDQ_API int sdq_weight_info(sdq_weight_t w, int64_t* N, int64_t* K, const int8_t** q_dev,
                     const float** scale_dev);
 SDQ_API int sdq_weight_release(sdq_weight_t w);
@@ -144,7 +146,13 @@ SDQ_API int sdq_weight_release(sdq_weight_t w);
  * activation between the two FFN linears (src/model/ovi_dit.cpp:132-142,
  * 214-222).  A and out are device memory unless SDQ_A_HOST / SDQ_OUT_HOST.
  * M == 0 is a no-op (src/core/qgemm.cpp:76); a weight always has N >= 1 and K >= 1.
- * Like the reference (src/core/qgemm.cpp:21), the int32 sums cannot overflow for K <= 133152. */
+ * Like the reference (src/core/qgemm.cpp:21), the int32 sums cannot overflow for K <= 133152.
+ * Alignment: fp32 pointers need only their natural 4 bytes.  The fast epilogue (bulk tensor
+ * stores, scales / bias / gate read four at a time) is taken when out, the weight's scales,
+ * bias, gate and residual are 16-byte aligned and N % 4 == 0; anything else -- a bias that is a
+ * slice of a larger vector at an odd offset, say -- runs the per-element epilogue of the 1-CTA
+ * kernel, same bits, slower.  This holds for every entry point that takes these pointers
+ * except sdq_qgemm_colsplit, which has only the fast form and rejects such pointers. */
 SDQ_API int sdq_qgemm(sdq_weight_t w, const float* A, int64_t M, float* out, const float* bias,
               uint32_t flags, void* stream);
 
@@ -295,7 +303,11 @@ SDQ_API int sdq_sdpa(const float* q_dev, const float* k_dev, const float* v_dev,
  * stream, or events).  A, out and bias are device memory (SDQ_A_HOST /
  * SDQ_OUT_HOST are rejected: staging would need an allocation).  The first call
  * on each device does a one-time host-side set-up; make it before any stream
- * capture begins. */
+ * capture begins.  A bounded wait that gives up inside the GEMM kernel leaves a
+ * code in the array; only a call made with SDQ_SYNC reads it (after waiting for
+ * the stream) and returns SDQ_ERR_DEVICE_TIMEOUT -- for its own kernels or for
+ * those of earlier calls -- so a caller that never passes SDQ_SYNC is never
+ * told.  The pointers w_scale_dev and bias_dev may have any 4-byte alignment. */
 #define SDQ_STATIC_MAX_ROWS 32768
 #define SDQ_STATIC_MAX_AQ_BYTES 33554432
 SDQ_API int sdq_qgemm_static_scratch(const int8_t* wq_dev, const float* w_scale_dev, int64_t N,

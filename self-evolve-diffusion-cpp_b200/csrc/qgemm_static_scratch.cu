@@ -16,14 +16,21 @@
 //   * all calls on a device share the one array.  Two calls whose kernels can
 //     overlap on the GPU (different streams, no ordering between them) race on
 //     it; calls on one stream, or otherwise ordered, are fine;
-//   * the array keeps what the last call left.  The only part that must start at
-//     zero -- the status word the GEMM kernel reports a timed-out wait in -- is
-//     cleared on the stream at the start of every call; the rest is overwritten
-//     before it is read.
+//   * the array keeps what the last call left.  The activations and scales are
+//     overwritten before they are read, so nothing needs clearing between calls.
+//     The one word that must be zero for a kernel to record a timed-out wait in it
+//     -- the status word -- is zero when the library is loaded and is set back to
+//     zero by the host only after a time-out has been reported: a call made
+//     with SDQ_SYNC waits for the stream, reads the word and, if a kernel of this or
+//     of an earlier call gave up, returns SDQ_ERR_DEVICE_TIMEOUT and clears it.  A
+//     caller that never passes SDQ_SYNC never learns of a time-out (the word just
+//     stays set); nothing is lost in between, because calls without SDQ_SYNC do not
+//     touch it.
 //
 // The first call on each device performs a one-time set-up on the host (device
 // address of the array, kernel attributes, driver entry point).  Make that first
 // call outside any stream capture.
+#include <cstdio>
 #include <mutex>
 
 #include "sdq_internal.h"
@@ -95,7 +102,6 @@ extern "C" int sdq_qgemm_static_scratch(const int8_t* wq_dev, const float* w_sca
   float* a_scale = reinterpret_cast<float*>(d->base + kStatusBytes);
   int8_t* aq = reinterpret_cast<int8_t*>(d->base + kStatusBytes + kScaleBytes);
 
-  SDQ_CUDA(cudaMemsetAsync(status, 0, sizeof(int), s));  // the one part that must start at zero
   SDQ_CUDA(sdq::launch_act_quant(A_dev, M, K, aq, a_scale, d->sm_count, s));
   sdq::GemmArgs g;
   g.aq = aq; g.a_scale = a_scale; g.bq = wq_dev; g.b_scale = w_scale_dev; g.bias = bias_dev;
@@ -113,7 +119,13 @@ extern "C" int sdq_qgemm_static_scratch(const int8_t* wq_dev, const float* w_sca
     SDQ_CUDA(cudaStreamSynchronize(s));
     int st = 0;
     SDQ_CUDA(cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (st != 0) return fail(SDQ_ERR_DEVICE_TIMEOUT, "sdq_qgemm_static_scratch: a bounded wait inside the GEMM kernel gave up");
+    if (st != 0) {
+      SDQ_CUDA(cudaMemset(status, 0, sizeof(int)));  // reported: the next time-out can be recorded
+      char buf[160];
+      snprintf(buf, sizeof buf,
+               "sdq_qgemm_static_scratch: a bounded wait inside the GEMM kernel of this or an earlier call gave up (code 0x%x)", st);
+      return fail(SDQ_ERR_DEVICE_TIMEOUT, buf);
+    }
   }
   return SDQ_OK;
 }

@@ -324,7 +324,8 @@ cudaError_t launch_t(const GemmArgs& g, int sm_count, cudaStream_t s, std::strin
   // (a debugging aid) and odd N keep the per-thread store path.
   const int use_tma_store = (g.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0) &&
                             g.acc_dump == nullptr && g.k_splits <= 1 &&
-                            (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0;
+                            (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0 &&
+                            epilogue_vectors_aligned(g);
   if (g.k_splits > 1) {
     if (!make_out_tmap(&tout, g.splitk_acc, g.M, g.N, why, CU_TENSOR_MAP_DATA_TYPE_INT32))
       return cudaErrorInvalidValue;

@@ -17,6 +17,15 @@
 // No TMA multicast is used.  Every wait is bounded as in the 1-CTA kernel, and the two
 // CTAs leave through a cluster barrier so that neither frees shared or tensor memory
 // the other may still signal.
+//
+// Last, partial wave.  With T tiles on C CTA pairs, the first floor(T/C) rounds give every
+// pair a whole tile.  The remaining T mod C tiles would keep only some pairs busy for a
+// whole tile time, so (when a scratch accumulator is supplied and it pays) their k-blocks are
+// shared out instead: the tail's (T mod C) * KB k-block units are cut into C equal contiguous
+// ranges, a pair runs its range (at most two segments, each a k-range of one tile) and adds the
+// raw int32 partial sums into the scratch with bulk tensor reductions -- integer addition,
+// exact in any order -- and tail_finalize_kernel then turns the sums of those tiles into
+// fp32 outputs and clears the scratch for the next launch.
 #include <cstdio>
 #include <cstdlib>
 
@@ -97,6 +106,51 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       : "memory");
 }
 
+// The work of one CTA pair: `rounds` whole tiles (tile = round * C + cluster), then the
+// segments of its share of the tail.  Every role walks the same list.
+struct Work {
+  int tile;      // index into the tile order
+  int kb0, kb1;  // k-block range
+  int partial;   // 1: a tail segment, partial sums go to the scratch accumulator
+};
+struct WorkList {
+  int rounds, first_tail, num_tiles, num_clusters, cluster_id, kblocks;
+  int u0, u1;  // this pair's range of tail units (tile-major, k-block-minor)
+  __device__ WorkList(int tiles, int clusters, int cluster, int kb, bool share_tail)
+      : num_tiles(tiles), num_clusters(clusters), cluster_id(cluster), kblocks(kb) {
+    rounds = share_tail ? tiles / clusters : (tiles + clusters - 1) / clusters;
+    first_tail = rounds * clusters;
+    const int64_t units = share_tail ? (int64_t)(tiles - first_tail) * kb : 0;
+    u0 = (int)(units * cluster / clusters);
+    u1 = (int)(units * (cluster + 1) / clusters);
+  }
+  __device__ bool get(int idx, Work& w) const {
+    if (idx < rounds) {
+      w.tile = idx * num_clusters + cluster_id;
+      w.kb0 = 0; w.kb1 = kblocks; w.partial = 0;
+      return w.tile < num_tiles;
+    }
+    if (u1 <= u0) return false;
+    const int t = u0 / kblocks;  // first tail tile this pair touches
+    const int seg = idx - rounds;
+    if (seg == 0) {
+      w.tile = first_tail + t;
+      w.kb0 = u0 - t * kblocks;
+      w.kb1 = min(kblocks, w.kb0 + (u1 - u0));
+      w.partial = 1;
+      return true;
+    }
+    if (seg == 1 && u1 > (t + 1) * kblocks) {
+      w.tile = first_tail + t + 1;
+      w.kb0 = 0;
+      w.kb1 = u1 - (t + 1) * kblocks;
+      w.partial = 1;
+      return true;
+    }
+    return false;
+  }
+};
+
 // Output tensor maps: one in the ordinary case; in the column-split multi-GPU form one per
 // destination buffer (this GPU's and each peer's), all describing [M, out_ld] fp32.
 struct OutMaps {
@@ -109,7 +163,8 @@ template <int kStages2, int kBoxes, bool kResidual>
 __global__ void __launch_bounds__(kNumThreads, 1)
     qgemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
-                     const __grid_constant__ OutMaps outs, int num_outs, GemmArgs g) {
+                     const __grid_constant__ OutMaps outs, int num_outs,
+                     const __grid_constant__ CUtensorMap tmap_tail, GemmArgs g) {
   constexpr int kStagingBytes2 = 8 * 4096 * kBoxes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -135,6 +190,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const int num_n_blocks = (int)((g.N + kBlockN2 - 1) / kBlockN2);
   const int num_k_blocks = (int)((g.K + BLOCK_K - 1) / BLOCK_K);
   const int num_tiles = num_m_pairs * num_n_blocks;
+  const int group_pairs = g.group_pairs > 0 ? g.group_pairs : kGroupM / 2;
+  const WorkList work(num_tiles, num_clusters, cluster_id, num_k_blocks, g.tail_acc != nullptr);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages2; s++) {
@@ -151,6 +208,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
     for (int i = 0; i < num_outs; i++) prefetch_tmap(&outs.m[i]);
+    if (g.tail_acc) prefetch_tmap(&tmap_tail);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols2);
@@ -166,23 +224,26 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       // ------------------------------------------------ TMA producer (both CTAs)
       grid_dependency_wait();  // aq is written by the quantize kernel launched just before
       const uint64_t keep_policy = policy_evict_last();
-      const uint64_t normal_policy = policy_evict_normal();
+      const uint64_t a_policy = g.a_policy == 1 ? policy_evict_first()
+                                : (g.a_policy == 2 ? keep_policy : policy_evict_normal());
+      const uint64_t b_policy = g.b_policy == 1 ? policy_evict_normal() : keep_policy;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+      Work w;
+      for (int idx = 0; ok && work.get(idx, w); idx++) {
         int m_pair, n_blk;
-        tile_coords_g(tile, num_m_pairs, num_n_blocks, kGroupM / 2, m_pair, n_blk);
+        tile_coords_g(w.tile, num_m_pairs, num_n_blocks, group_pairs, m_pair, n_blk);
         const int row0 = (m_pair * 2 + (int)rank) * BLOCK_M;
         const int wrow0 = n_blk * kBlockN2 + (int)rank * BLOCK_M;
-        for (int kb = 0; kb < num_k_blocks; kb++) {
+        for (int kb = w.kb0; kb < w.kb1; kb++) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x1100 | 1);
           if (!ok) break;
           const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
           if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes2);
           tma_load_2d_pair(smem_a + stage * kHalfBytes, &tmap_a, full_leader, kb * BLOCK_K, row0,
-                           normal_policy);
+                           a_policy);
           tma_load_2d_pair(smem_b + stage * kHalfBytes, &tmap_b, full_leader, kb * BLOCK_K, wrow0,
-                           keep_policy);
+                           b_policy);
           if (++stage == kStages2) { stage = 0; phase ^= 1u; }
         }
       }
@@ -192,12 +253,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       // ------------------------------------------------ MMA issuer (leader CTA only)
       uint32_t stage = 0, phase = 0, abuf = 0, aphase = 0;
       bool ok = true;
-      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+      Work w;
+      for (int idx = 0; ok && work.get(idx, w); idx++) {
         ok = mbar_wait(bar_tempty + 8 * abuf, aphase ^ 1u, abort_flag, g.status, 0x1200 | 1);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + abuf * kBlockN2;
-        for (int kb = 0; kb < num_k_blocks; kb++) {
+        for (int kb = w.kb0; kb < w.kb1; kb++) {
           ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x1200 | 2);
           if (!ok) break;
           tc_fence_after();
@@ -206,7 +268,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; k++)
             umma_i8_pair(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)),
-                         bdesc + (uint64_t)(k * (UMMA_K >> 4)), kIdesc2, (uint32_t)((kb | k) != 0));
+                         bdesc + (uint64_t)(k * (UMMA_K >> 4)), kIdesc2,
+                         (uint32_t)(((kb - w.kb0) | k) != 0));
           umma_commit_pair(bar_empty + 8 * stage);
           if (++stage == kStages2) { stage = 0; phase ^= 1u; }
         }
@@ -228,9 +291,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     grid_dependency_wait();  // a_scale comes from the quantize kernel
     uint32_t abuf = 0, aphase = 0;
     bool ok = true;
-    for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+    Work w;
+    for (int idx = 0; ok && work.get(idx, w); idx++) {
       int m_pair, n_blk;
-      tile_coords_g(tile, num_m_pairs, num_n_blocks, kGroupM / 2, m_pair, n_blk);
+      tile_coords_g(w.tile, num_m_pairs, num_n_blocks, group_pairs, m_pair, n_blk);
       ok = mbar_wait_warp(bar_tfull + 8 * abuf, aphase, abort_flag, g.status, 0x1300 | 1);
       if (!ok) break;
       tc_fence_after();
@@ -245,6 +309,27 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (nc >= g.N) break;
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + abuf * kBlockN2 + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+          if (w.partial) {
+            // a tail segment: the raw partial sums are added into the scratch accumulator
+            // (row = tail tile * 256 + row inside the tile, column = column inside the tile)
+            tmem_ld_wait();
+            const uint32_t box = box0 + box_sel * 4096;
+            if (kBoxes > 1) box_sel ^= 1u;
+            if (lane == 0) bulk_wait_read<kBoxes - 1>();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              st_shared_v4_b32(box + (uint32_t)(lane * 128 + (((j >> 2) ^ (lane & 7)) << 4)), r[j],
+                               r[j + 1], r[j + 2], r[j + 3]);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_2d(&tmap_tail, box, c * 32,
+                                (w.tile - work.first_tail) * (2 * BLOCK_M) + (int)rank * BLOCK_M + quarter * 32);
+              bulk_commit();
+            }
+            continue;
+          }
           float4 x[8];
           if (kResidual)  // in flight while the accumulators arrive from tensor memory
             chunk_load_residual(g.residual, row0, g.M, g.N, nc, lane, x);
@@ -305,6 +390,46 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   }
 }
 
+// Second step for the tiles of a shared last wave: fp32 outputs from the summed int32
+// partial sums, which are cleared on the way so that the scratch is all zero again.
+// grid = (tail tiles, 8); a thread takes 4 consecutive columns of one row at a time.
+template <bool kResidual>
+__global__ void __launch_bounds__(256) tail_finalize_kernel(GemmArgs g, int first_tail, int group_pairs) {
+  const int num_m_pairs = (int)((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M));
+  const int num_n_blocks = (int)((g.N + kBlockN2 - 1) / kBlockN2);
+  int m_pair, n_blk;
+  tile_coords_g(first_tail + (int)blockIdx.x, num_m_pairs, num_n_blocks, group_pairs, m_pair, n_blk);
+  const bool gelu = (g.flags & SDQ_GELU_TANH) != 0;
+  int4* acc = reinterpret_cast<int4*>(g.tail_acc + (size_t)blockIdx.x * (2 * BLOCK_M) * kBlockN2);
+  constexpr int kVecs = 2 * BLOCK_M * kBlockN2 / 4;  // 16384 groups of 4 columns per tile
+  for (int v = (int)blockIdx.y * 256 + (int)threadIdx.x; v < kVecs; v += (int)gridDim.y * 256) {
+    const int r = v / (kBlockN2 / 4), c4 = (v - r * (kBlockN2 / 4)) * 4;
+    const int64_t row = (int64_t)m_pair * (2 * BLOCK_M) + r, col = (int64_t)n_blk * kBlockN2 + c4;
+    if (row >= g.M || col >= g.N) continue;  // never written: still zero
+    const int4 a = acc[v];
+    acc[v] = make_int4(0, 0, 0, 0);
+    const float a_s = g.a_scale[row];
+    const float4 bs = __ldg(reinterpret_cast<const float4*>(g.b_scale + col));
+    float4 bb = make_float4(0.f, 0.f, 0.f, 0.f), gg = bb, xx = bb;
+    if (g.bias) bb = __ldg(reinterpret_cast<const float4*>(g.bias + col));
+    float* dst = g.out + row * g.N + col;
+    if (kResidual) {
+      xx = *reinterpret_cast<const float4*>(g.residual + row * g.N + col);
+      if (g.gate) gg = __ldg(reinterpret_cast<const float4*>(g.gate + col));
+    }
+    const int av[4] = {a.x, a.y, a.z, a.w};
+    const float sc[4] = {bs.x, bs.y, bs.z, bs.w}, bi[4] = {bb.x, bb.y, bb.z, bb.w};
+    const float gs[4] = {gg.x, gg.y, gg.z, gg.w}, xs[4] = {xx.x, xx.y, xx.z, xx.w};
+    float o[4];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      o[t] = epilogue_value(av[t], a_s, sc[t], g.bias ? &bi[t] : nullptr, gelu);
+      if (kResidual) o[t] = residual_value(o[t], xs[t], g.gate ? &gs[t] : nullptr);
+    }
+    *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------- host side
@@ -316,6 +441,37 @@ int tc2_config() {
   }();
   return cfg == 52 ? 52 : 61;
 }
+namespace {
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+// Tiles of the last, partial wave whose k-blocks are shared out, or 0 when every tile is
+// left to one pair.  Sharing saves (1 - tail/C) of a tile time (~0.4 us per 128-byte
+// k-block at the sustained int8 rate) and costs one more launch plus a pass over the
+// scratch (~0.2 us per tile).
+int plan_tail(const GemmArgs& g, int64_t tiles, int64_t clusters) {
+  static const int mode = env_int("SDQ_TC2_TAIL", 1);  // 0: never, 1: when it pays, 2: whenever possible
+  if (mode == 0 || g.out_copies > 0) return 0;
+  const int64_t tail = tiles % clusters;
+  if (tail == 0) return 0;
+  if (mode == 2) return (int)tail;
+  const double kblocks = (double)((g.K + BLOCK_K - 1) / BLOCK_K);
+  const double saved_us = (1.0 - (double)tail / (double)clusters) * kblocks * 0.40 - (4.0 + 0.2 * (double)tail);
+  return saved_us > 1.0 ? (int)tail : 0;
+}
+// Height of a band of the tile walk, in 256-row pairs.  A band's rows of aq are fetched from
+// HBM once and then served from L2 to every column block; the weight matrix is re-read once
+// per band, so taller bands mean fewer weight re-reads as long as the band still fits in L2
+// beside the weights in flight: the target is ~24 MB of aq per band.
+int plan_group(const GemmArgs& g) {
+  static const int forced = env_int("SDQ_TC2_GROUP", 0);
+  if (forced > 0) return forced;
+  const double band_bytes_per_pair = 2.0 * BLOCK_M * (double)g.K;
+  int pairs = (int)(24.0e6 / band_bytes_per_pair);
+  return pairs < 4 ? 4 : (pairs > 37 ? 37 : pairs);
+}
+}  // namespace
 
 int qgemm_tc2_setup(std::string* why) {
   cudaError_t a = cudaSuccess;
@@ -331,31 +487,49 @@ int qgemm_tc2_setup(std::string* why) {
   return SDQ_OK;
 }
 
-// The pair kernel stores only through bulk tensor stores (N % 4 == 0, 16-byte aligned
-// out, no accumulator dump) and pays off once every cluster has at least one tile.
-bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count) {
-  static const int forced = [] {
-    const char* v = getenv("SDQ_TC_VARIANT");  // "1": never, "2": whenever possible
-    return v ? atoi(v) : 0;
-  }();
-  if (g.acc_dump) return false;
-  if (g.residual && (g.out_copies > 0 || (reinterpret_cast<uintptr_t>(g.residual) & 15) != 0)) return false;
+// The pair kernel stores only through bulk tensor stores and its epilogue reads the scales,
+// bias and gate four floats at a time: N % 4 == 0, 16-byte aligned out / residual / b_scale /
+// bias / gate, no accumulator dump.
+const char* qgemm_tc2_unfit(const GemmArgs& g) {
+  auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (g.acc_dump) return "the accumulator dump needs the 1-CTA kernel";
+  if (misaligned(g.b_scale)) return "the weight scales are not 16-byte aligned";
+  if (g.bias && misaligned(g.bias)) return "the bias is not 16-byte aligned";
+  if (g.residual && g.gate && misaligned(g.gate)) return "the gate is not 16-byte aligned";
+  if (g.residual && misaligned(g.residual)) return "the residual is not 16-byte aligned";
   if (g.out_copies > 0) {
-    // every destination 16-byte aligned with a 16-byte row pitch and column offset
-    if (g.out_ld % 4 != 0 || g.out_col0 % 4 != 0) return false;
+    if (g.residual) return "the column-split form has no residual epilogue";
+    if (g.out_ld % 4 != 0 || g.out_col0 % 4 != 0) return "the row pitch or column offset of the destinations is not a multiple of 4";
     for (int i = 0; i < g.out_copies; i++)
-      if ((reinterpret_cast<uintptr_t>(g.out_all[i]) & 15) != 0) return false;
-    return true;  // the caller asked for the fused form; it has no other kernel
+      if (misaligned(g.out_all[i])) return "a destination is not 16-byte aligned";
+    return nullptr;
   }
+  if (g.N % 4 != 0) return "N is not a multiple of 4";
+  if (misaligned(g.out)) return "out is not 16-byte aligned";
+  return nullptr;
+}
+
+// Tiles of the last wave the launcher would share out if it is given a scratch accumulator
+// (GemmArgs::tail_acc) of at least that many tiles; 0: it needs none.
+int qgemm_tc2_tail_tiles(const GemmArgs& g, int sm_count) {
+  const int64_t tiles = ((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((g.N + kBlockN2 - 1) / kBlockN2);
+  return plan_tail(g, tiles, sm_count / 2);
+}
+
+// ... and it pays off once every cluster has at least one tile.
+bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count) {
+  static const int forced = env_int("SDQ_TC_VARIANT", 0);  // "1": never, "2": whenever possible
+  if (qgemm_tc2_unfit(g)) return false;
+  if (g.out_copies > 0) return true;  // the caller asked for the fused form; it has no other kernel
   if (forced == 1) return false;
-  if (g.N % 4 != 0 || (reinterpret_cast<uintptr_t>(g.out) & 15) != 0) return false;
   const int64_t tiles = ((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((g.N + kBlockN2 - 1) / kBlockN2);
   if (forced == 2) return true;
   return tiles >= sm_count / 2;
 }
 
-cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why) {
-  CUtensorMap ta, tb;
+cudaError_t launch_qgemm_tc2(const GemmArgs& g_in, int sm_count, cudaStream_t s, std::string* why) {
+  GemmArgs g = g_in;
+  CUtensorMap ta, tb, ttail;
   OutMaps outs;
   if (!make_tmap(&ta, g.aq, g.M, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;
   if (!make_tmap(&tb, g.bq, g.N, g.K, BLOCK_M, why)) return cudaErrorInvalidValue;  // 128-row halves
@@ -370,7 +544,21 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, st
   for (int i = num_outs; i < 8; i++) outs.m[i] = outs.m[0];
   const int64_t tiles = ((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((g.N + kBlockN2 - 1) / kBlockN2);
   int64_t clusters = sm_count / 2;
-  if (tiles < clusters) clusters = tiles;
+  int tail = plan_tail(g, tiles, clusters);
+  if (!g.tail_acc || tail > g.tail_cap_tiles) tail = 0;
+  if (tail > 0) {
+    // [tail tiles x 256 rows, 256 columns] int32, boxes of 32 x 32 like the output
+    if (!make_out_tmap(&ttail, g.tail_acc, (int64_t)tail * 2 * BLOCK_M, kBlockN2, why, CU_TENSOR_MAP_DATA_TYPE_INT32))
+      return cudaErrorInvalidValue;
+  } else {
+    g.tail_acc = nullptr;
+    ttail = ta;  // unused by the kernel
+    if (tiles < clusters) clusters = tiles;
+  }
+  g.group_pairs = plan_group(g);
+  static const int a_policy = env_int("SDQ_TC2_APOLICY", 0), b_policy = env_int("SDQ_TC2_BPOLICY", 0);
+  g.a_policy = a_policy;
+  g.b_policy = b_policy;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(clusters * 2));
   cfg.blockDim = dim3(kNumThreads);
@@ -387,12 +575,22 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, st
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   count_launch();
+  cudaError_t e;
   if (g.residual) {
-    if (deep) return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1, true>, ta, tb, outs, num_outs, g);
-    return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2, true>, ta, tb, outs, num_outs, g);
+    e = deep ? cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1, true>, ta, tb, outs, num_outs, ttail, g)
+             : cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2, true>, ta, tb, outs, num_outs, ttail, g);
+  } else {
+    e = deep ? cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1, false>, ta, tb, outs, num_outs, ttail, g)
+             : cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2, false>, ta, tb, outs, num_outs, ttail, g);
   }
-  if (deep) return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1, false>, ta, tb, outs, num_outs, g);
-  return cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2, false>, ta, tb, outs, num_outs, g);
+  if (e == cudaSuccess && tail > 0) {
+    const int first_tail = (int)(tiles - tail);
+    count_launch();
+    if (g.residual) tail_finalize_kernel<true><<<dim3((unsigned)tail, 8), 256, 0, s>>>(g, first_tail, g.group_pairs);
+    else tail_finalize_kernel<false><<<dim3((unsigned)tail, 8), 256, 0, s>>>(g, first_tail, g.group_pairs);
+    e = cudaGetLastError();
+  }
+  return e;
 }
 
 }  // namespace sdq

@@ -6,9 +6,11 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <stdexcept>
 #include <thread>
+#include <unordered_map>
 
 #include "core/tensor.h"
 #include "model/blocks.h"
@@ -20,6 +22,8 @@ namespace {
 
 size_t elem_size(DType d) { return d == DType::F32 ? 4 : d == DType::BF16 ? 2 : 1; }
 
+std::atomic<bool> g_device_ready{false};
+
 void ensure_device() {
   static std::once_flag once;
   static int rc = SDQ_OK;
@@ -28,11 +32,102 @@ void ensure_device() {
     const char* dev = std::getenv("SD_DEVICE");
     rc = sdq_init(dev ? std::atoi(dev) : 0);
     if (rc != SDQ_OK) msg = sdq_last_error();
+    else g_device_ready.store(true);
   });
   if (rc != SDQ_OK) throw std::runtime_error("sd (B200): " + msg);
 }
 
 [[noreturn]] void raise_last() { throw std::runtime_error(sdq_last_error()); }
+
+// Storage of owning tensors.  The caller of the reference's interface allocates a fresh
+// output for every linear (src/core/qgemm.cpp:75) and hands activations over as plain host
+// tensors; copies between pageable memory and the GPU run at a fraction of the PCIe rate and
+// block the host.  Once the device is in use, blocks of 256 KiB and more therefore come from
+// page-locked memory, and because page-locking costs far more than a copy, released blocks
+// are kept and handed out again (the forward pass asks for the same few sizes over and over).
+// SD_PINNED_POOL_MB bounds the idle blocks kept (default 8192; 0 switches the pool off).
+class PinnedPool {
+ public:
+  void* get(size_t bytes) {
+    if (!g_device_ready.load() || bytes < kMinBytes || cap() == 0) return nullptr;
+    const size_t want = (bytes + kGrain - 1) / kGrain * kGrain;
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      auto it = idle_.lower_bound(want);
+      if (it != idle_.end() && it->first <= want + want / 8) {
+        void* p = it->second;
+        live_[p] = it->first;
+        idle_bytes_ -= it->first;
+        idle_.erase(it);
+        return p;
+      }
+    }
+    void* p = nullptr;
+    if (sdq_malloc_host(&p, want) != SDQ_OK || !p) return nullptr;  // the caller falls back to malloc
+    std::lock_guard<std::mutex> lk(mu_);
+    live_[p] = want;
+    return p;
+  }
+  // true when p was a block of this pool (and has been taken back)
+  bool put(void* p) {
+    size_t size = 0;
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      auto it = live_.find(p);
+      if (it == live_.end()) return false;
+      size = it->second;
+      live_.erase(it);
+      if (idle_bytes_ + size <= cap()) {
+        idle_.emplace(size, p);
+        idle_bytes_ += size;
+        return true;
+      }
+    }
+    sdq_free_host(p);
+    return true;
+  }
+
+ private:
+  static constexpr size_t kMinBytes = size_t(256) << 10, kGrain = size_t(1) << 20;
+  static size_t cap() {
+    static const size_t c = [] {
+      const char* v = std::getenv("SD_PINNED_POOL_MB");
+      return (size_t)(v ? std::atoll(v) : 8192) << 20;
+    }();
+    return c;
+  }
+  std::mutex mu_;
+  std::unordered_map<void*, size_t> live_;
+  std::multimap<size_t, void*> idle_;
+  size_t idle_bytes_ = 0;
+};
+PinnedPool& pool() {
+  static PinnedPool* p = new PinnedPool;  // never destroyed: tensors may outlive static teardown
+  return *p;
+}
+
+void* tensor_alloc(size_t nbytes) {
+  if (void* p = pool().get(nbytes)) return p;
+  void* p = aligned_alloc(64, (nbytes + 63) / 64 * 64 + 64);
+  if (!p) throw std::bad_alloc();
+  return p;
+}
+void tensor_free(void* p) {
+  if (p && !pool().put(p)) std::free(p);
+}
+
+// An owning tensor whose bytes are NOT cleared: for results that are overwritten in full.
+Tensor uninitialized(std::vector<int64_t> shape, DType d) {
+  Tensor t;
+  int64_t n = 1;
+  for (int64_t x : shape) n *= x;
+  t.shape = std::move(shape);
+  t.dtype = d;
+  t.nbytes = (size_t)n * elem_size(d);
+  t.data = tensor_alloc(t.nbytes);
+  t.owning = true;
+  return t;
+}
 
 }  // namespace
 
@@ -41,17 +136,16 @@ Tensor::Tensor(std::vector<int64_t> s, DType d) : shape(std::move(s)), dtype(d) 
   int64_t n = 1;
   for (int64_t x : shape) n *= x;
   nbytes = (size_t)n * elem_size(dtype);
-  data = aligned_alloc(64, (nbytes + 63) / 64 * 64 + 64);
-  if (!data) throw std::bad_alloc();
+  data = tensor_alloc(nbytes);
   std::memset(data, 0, nbytes);
 }
 Tensor::~Tensor() {
-  if (owning && data) std::free(data);
+  if (owning && data) tensor_free(data);
 }
 Tensor::Tensor(Tensor&& o) noexcept { *this = std::move(o); }
 Tensor& Tensor::operator=(Tensor&& o) noexcept {
   if (this == &o) return *this;
-  if (owning && data) std::free(data);
+  if (owning && data) tensor_free(data);
   shape = std::move(o.shape);
   dtype = o.dtype;
   data = o.data;
@@ -94,12 +188,20 @@ void to_bf16(const Tensor& f32, Tensor& out) {
 // ---- the hot path (reference src/core/qgemm.cpp:73-142) ----
 void qgemm(const Tensor& A, const Tensor& Bq, const Tensor& bs, Tensor& out) {
   const int64_t M = A.rows(), K = A.cols(), N = Bq.rows();
-  out = Tensor({M, N}, DType::F32);
-  if (M == 0 || N == 0 || K == 0) return;
+  if (M == 0 || N == 0 || K == 0) {  // an empty problem gives a zero tensor (src/core/qgemm.cpp:75-76)
+    out = Tensor({M, N}, DType::F32);
+    return;
+  }
   ensure_device();
+  out = uninitialized({M, N}, DType::F32);  // every element is written by the copy back
   sdq_weight_t w = 0;
   bool temporary = false;
-  if (sdq_weight_lookup(Bq.data, &w) != SDQ_OK) {
+  // The device copy made at load time is the pack tensor viewed as [numel / last, last]; a
+  // caller's view of the same bytes with another shape (i8view2d, src/model/ovi_dit.cpp:42-50)
+  // must not run with the cached extents.
+  int64_t wn = 0, wk = 0;
+  if (sdq_weight_lookup(Bq.data, &w) != SDQ_OK || sdq_weight_info(w, &wn, &wk, nullptr, nullptr) != SDQ_OK ||
+      wn != N || wk != K) {
     if (sdq_weight_upload(Bq.ptr<int8_t>(), bs.ptr<float>(), N, K, &w) != SDQ_OK) raise_last();
     temporary = true;
   }
@@ -118,7 +220,7 @@ void matmul(const Tensor& A, const Tensor& B, Tensor& C, const float* bias) {
   if (A.dtype == DType::BF16) { to_f32(A, Af); a = &Af; }
   if (B.dtype == DType::BF16) { to_f32(B, Bf); b = &Bf; }
   const int64_t M = a->rows(), K = a->cols(), N = b->cols();
-  C = Tensor({M, N}, DType::F32);
+  C = (M == 0 || N == 0 || K == 0) ? Tensor({M, N}, DType::F32) : uninitialized({M, N}, DType::F32);
   if (M == 0 || N == 0) return;
   if (K == 0) {  // an empty sum: only the bias is left, as in the reference
     if (bias)
@@ -128,7 +230,11 @@ void matmul(const Tensor& A, const Tensor& B, Tensor& C, const float* bias) {
   ensure_device();
   sdq_weight_t w = 0;
   bool temporary = false;
-  if (b != &B || sdq_weight_lookup(B.data, &w) != SDQ_OK) {
+  int64_t wn = 0, wk = 0;
+  const int8_t* wq = nullptr;
+  // a resident copy only counts when it is an fp32 weight of exactly this shape
+  if (b != &B || sdq_weight_lookup(B.data, &w) != SDQ_OK ||
+      sdq_weight_info(w, &wn, &wk, &wq, nullptr) != SDQ_OK || wq != nullptr || wn != N || wk != K) {
     if (sdq_fweight_upload(b->ptr<float>(), K, N, SDQ_A_HOST, &w) != SDQ_OK) raise_last();
     temporary = true;
   }

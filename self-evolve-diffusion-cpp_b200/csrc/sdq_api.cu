@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <deque>
 #include <mutex>
 #include <thread>
 #include <unordered_map>
@@ -40,22 +41,43 @@ struct Workspace {
   float2* ln_stats = nullptr; size_t ln_stats_bytes = 0;  // per-row mean and 1/sqrt(var+eps)
   float* f_split = nullptr; size_t f_split_bytes = 0;     // tf32 planes of the fp32 activations
   float* attn = nullptr; size_t attn_bytes = 0;           // attention: fp16 planes of k, v^T
+  // partial int32 sums of the tiles whose K range is shared between CTA pairs (the last, partial
+  // wave of the 2-CTA GEMM); all zero between launches: the pass that reads them clears them
+  int32_t* tail_acc = nullptr; size_t tail_acc_bytes = 0; uint64_t tail_epoch = 0;
+  // the FFN pair's host-pointer pipeline of this stream: two copy streams, events, chunk buffers
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev_in[2] = {}, ev_a_free[2] = {}, ev_comp[2] = {}, ev_out_done[2] = {};
+  float* pa[2] = {}; size_t pa_bytes[2] = {};
+  float* py[2] = {}; size_t py_bytes[2] = {};
+  float* ph = nullptr; size_t ph_bytes = 0;
 };
+
+// Releases everything a stream's workspace holds (device memory, copy streams, events).
+void release_workspace(Workspace& w) {
+  cudaFree(w.aq); cudaFree(w.a_scale); cudaFree(w.a_stage); cudaFree(w.out_stage); cudaFree(w.acc);
+  cudaFree(w.ln_stats); cudaFree(w.f_split); cudaFree(w.attn); cudaFree(w.tail_acc);
+  for (int i = 0; i < 2; i++) {
+    cudaFree(w.pa[i]); cudaFree(w.py[i]);
+    if (w.ev_in[i]) {
+      cudaEventDestroy(w.ev_in[i]); cudaEventDestroy(w.ev_a_free[i]);
+      cudaEventDestroy(w.ev_comp[i]); cudaEventDestroy(w.ev_out_done[i]);
+    }
+  }
+  cudaFree(w.ph);
+  if (w.copy_in) cudaStreamDestroy(w.copy_in);
+  if (w.copy_out) cudaStreamDestroy(w.copy_out);
+  w = Workspace();
+}
 
 struct Context {
   int device = -1;
   int sm_count = 0;
   int* status = nullptr;  // device word written by a kernel whose bounded wait gave up
   std::mutex mu;
-  std::vector<Weight> weights;                       // handle = index + 1
+  std::deque<Weight> weights;                        // handle = index + 1 (a deque: no reallocation)
   std::unordered_map<const void*, sdq_weight_t> by_host;
-  std::unordered_map<cudaStream_t, Workspace> ws;
-  // the FFN pair's host-pointer pipeline: two copy streams, events, chunk buffers
-  cudaStream_t copy_in = nullptr, copy_out = nullptr;
-  cudaEvent_t ev_in[2] = {}, ev_a_free[2] = {}, ev_comp[2] = {}, ev_out_done[2] = {};
-  float* pa[2] = {}; size_t pa_bytes[2] = {};
-  float* py[2] = {}; size_t py_bytes[2] = {};
-  float* ph = nullptr; size_t ph_bytes = 0;
+  std::unordered_map<cudaStream_t, Workspace> ws;     // node-based: a Workspace never moves
+  std::atomic<uint64_t> tail_epoch{1};                // bumped when a kernel gave up mid-way
   // staged uploads of large weights
   std::mutex upload_mu;
   cudaStream_t up_stream = nullptr;
@@ -84,18 +106,37 @@ int need_ctx() {
   return SDQ_OK;
 }
 
-Weight* get_any_weight(sdq_weight_t h) {
+// Registry slot of a live handle; the caller holds g_ctx->mu.
+Weight* slot_locked(sdq_weight_t h) {
   if (!g_ctx || h == 0 || h > g_ctx->weights.size()) return nullptr;
   Weight* w = &g_ctx->weights[h - 1];
   return w->live ? w : nullptr;
 }
-Weight* get_weight(sdq_weight_t h) {  // an int8 weight
-  Weight* w = get_any_weight(h);
-  return (w && w->q) ? w : nullptr;
+// Compute calls work on a copy taken under the lock, so that uploads and releases running
+// on other host threads never move or rewrite what a call in progress reads.
+struct WeightRef {
+  Weight w;
+  bool ok = false;
+  const Weight* operator->() const { return &w; }
+  const Weight& operator*() const { return w; }
+  explicit operator bool() const { return ok; }
+};
+WeightRef get_any_weight(sdq_weight_t h) {
+  WeightRef r;
+  if (!g_ctx) return r;
+  std::lock_guard<std::mutex> lk(g_ctx->mu);
+  if (Weight* w = slot_locked(h)) { r.w = *w; r.ok = true; }
+  return r;
 }
-Weight* get_fweight(sdq_weight_t h) {  // an fp32 weight
-  Weight* w = get_any_weight(h);
-  return (w && w->f_hi) ? w : nullptr;
+WeightRef get_weight(sdq_weight_t h) {  // an int8 weight
+  WeightRef r = get_any_weight(h);
+  r.ok = r.ok && r.w.q != nullptr;
+  return r;
+}
+WeightRef get_fweight(sdq_weight_t h) {  // an fp32 weight
+  WeightRef r = get_any_weight(h);
+  r.ok = r.ok && r.w.f_hi != nullptr;
+  return r;
 }
 
 int check_status_word() {
@@ -103,6 +144,7 @@ int check_status_word() {
   SDQ_CUDA(cudaMemcpy(&st, g_ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
   if (st != 0) {
     cudaMemset(g_ctx->status, 0, sizeof(int));
+    g_ctx->tail_epoch.fetch_add(1);  // partial sums may be left in the scratch accumulators
     char buf[96];
     snprintf(buf, sizeof buf, "a bounded wait inside the GEMM kernel gave up (code 0x%x)", st);
     return fail(SDQ_ERR_DEVICE_TIMEOUT, buf);
@@ -120,6 +162,28 @@ int run_gemm(const Weight& w, const int8_t* aq, const float* a_scale, int64_t M,
   g.residual = residual; g.gate = residual ? gate : nullptr;
   if (!(flags & SDQ_FORCE_SIMT) && qgemm_tc_supported(g)) {
     std::string why;
+    if (qgemm_tc2_wanted(g, g_ctx->sm_count)) {
+      if (const int tail = qgemm_tc2_tail_tiles(g, g_ctx->sm_count)) {
+        // scratch for the partial sums of the shared last wave: zero when first made (and again
+        // after a kernel gave up mid-way); every launch that uses it leaves it zero
+        Workspace* ws;
+        {
+          std::lock_guard<std::mutex> lk(g_ctx->mu);
+          ws = &g_ctx->ws[s];
+        }
+        const size_t cap_tiles = (size_t)(g_ctx->sm_count / 2);
+        const size_t bytes = cap_tiles * 256 * 256 * sizeof(int32_t);
+        const uint64_t epoch = g_ctx->tail_epoch.load();
+        if (ws->tail_acc_bytes < bytes || ws->tail_epoch != epoch) {
+          if (int rc = grow(&ws->tail_acc, &ws->tail_acc_bytes, bytes)) return rc;
+          SDQ_CUDA(cudaMemsetAsync(ws->tail_acc, 0, ws->tail_acc_bytes, s));
+          ws->tail_epoch = epoch;
+        }
+        g.tail_acc = ws->tail_acc;
+        g.tail_cap_tiles = (int)cap_tiles;
+        (void)tail;
+      }
+    }
     const int splits = qgemm_tc_plan_splits(g, g_ctx->sm_count);
     if (splits > 1) {
       Workspace* ws;
@@ -218,24 +282,12 @@ int sdq_shutdown(void) {
       cudaFree(const_cast<int8_t*>(w.q)); cudaFree(const_cast<float*>(w.scale));
       cudaFree(const_cast<float*>(w.f_hi)); cudaFree(const_cast<float*>(w.f_lo));
     }
-  for (auto& kv : g_ctx->ws) {
-    cudaFree(kv.second.aq); cudaFree(kv.second.a_scale);
-    cudaFree(kv.second.a_stage); cudaFree(kv.second.out_stage); cudaFree(kv.second.acc);
-    cudaFree(kv.second.ln_stats); cudaFree(kv.second.f_split); cudaFree(kv.second.attn);
-  }
-  for (int i = 0; i < 2; i++) {
-    cudaFree(g_ctx->pa[i]); cudaFree(g_ctx->py[i]);
-    if (g_ctx->ev_in[i]) { cudaEventDestroy(g_ctx->ev_in[i]); cudaEventDestroy(g_ctx->ev_a_free[i]);
-                           cudaEventDestroy(g_ctx->ev_comp[i]); cudaEventDestroy(g_ctx->ev_out_done[i]); }
-  }
-  cudaFree(g_ctx->ph);
+  for (auto& kv : g_ctx->ws) release_workspace(kv.second);
   for (int i = 0; i < 2; i++) {
     if (g_ctx->up_buf[i]) cudaFreeHost(g_ctx->up_buf[i]);
     if (g_ctx->up_done[i]) cudaEventDestroy(g_ctx->up_done[i]);
   }
   if (g_ctx->up_stream) cudaStreamDestroy(g_ctx->up_stream);
-  if (g_ctx->copy_in) cudaStreamDestroy(g_ctx->copy_in);
-  if (g_ctx->copy_out) cudaStreamDestroy(g_ctx->copy_out);
   cudaFree(g_ctx->status);
   delete g_ctx;
   g_ctx = nullptr;
@@ -320,8 +372,7 @@ int sdq_stream_destroy(void* stream) {
     std::lock_guard<std::mutex> lk(g_ctx->mu);
     auto it = g_ctx->ws.find(s);
     if (it != g_ctx->ws.end()) {
-      cudaFree(it->second.aq); cudaFree(it->second.a_scale); cudaFree(it->second.a_stage);
-      cudaFree(it->second.out_stage); cudaFree(it->second.acc);
+      release_workspace(it->second);
       g_ctx->ws.erase(it);
     }
   }
@@ -434,7 +485,7 @@ int sdq_weight_lookup(const void* q_host, sdq_weight_t* out) {
 int sdq_weight_info(sdq_weight_t h, int64_t* N, int64_t* K, const int8_t** q_dev,
                     const float** scale_dev) {
   if (int rc = need_ctx()) return rc;
-  Weight* w = get_weight(h);
+  WeightRef w = get_any_weight(h);  // an fp32 weight reports q_dev = scale_dev = NULL
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_weight_info: bad weight handle");
   if (N) *N = w->N;
   if (K) *K = w->K;
@@ -446,7 +497,7 @@ int sdq_weight_info(sdq_weight_t h, int64_t* N, int64_t* K, const int8_t** q_dev
 int sdq_weight_release(sdq_weight_t h) {
   if (int rc = need_ctx()) return rc;
   std::lock_guard<std::mutex> lk(g_ctx->mu);
-  Weight* w = get_any_weight(h);
+  Weight* w = slot_locked(h);
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_weight_release: bad weight handle");
   if (w->owned) {
     cudaFree(const_cast<int8_t*>(w->q)); cudaFree(const_cast<float*>(w->scale));
@@ -508,7 +559,7 @@ int sdq_qgemm_prequantized(sdq_weight_t h, const int8_t* aq_dev, const float* a_
                            int64_t M, float* out_dev, const float* bias_dev,
                            int32_t* acc_dump_dev, uint32_t flags, void* stream) {
   if (int rc = need_ctx()) return rc;
-  Weight* w = get_weight(h);
+  WeightRef w = get_weight(h);
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm_prequantized: bad weight handle");
   if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_qgemm_prequantized: negative M");
   if (M == 0) return SDQ_OK;
@@ -521,7 +572,7 @@ int sdq_qgemm_prequantized(sdq_weight_t h, const int8_t* aq_dev, const float* a_
 int sdq_qgemm(sdq_weight_t h, const float* A, int64_t M, float* out, const float* bias,
               uint32_t flags, void* stream) {
   if (int rc = need_ctx()) return rc;
-  Weight* w = get_weight(h);
+  WeightRef w = get_weight(h);
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm: bad weight handle");
   if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_qgemm: negative M");
   if (M == 0) return SDQ_OK;
@@ -588,7 +639,7 @@ int sdq_fweight_upload(const float* w, int64_t K, int64_t N, uint32_t flags, sdq
 int sdq_fmatmul(sdq_weight_t h, const float* A, int64_t M, float* out, const float* bias_dev,
                 uint32_t flags, void* stream) {
   if (int rc = need_ctx()) return rc;
-  Weight* w = get_fweight(h);
+  WeightRef w = get_fweight(h);
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_fmatmul: bad weight handle (not an fp32 weight)");
   if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_fmatmul: negative M");
   if (M == 0) return SDQ_OK;
@@ -652,7 +703,7 @@ int sdq_qgemm_residual(sdq_weight_t h, const float* A_dev, int64_t M, const floa
                        const float* gate_dev, float* out_dev, const float* bias_dev,
                        uint32_t flags, void* stream) {
   if (int rc = need_ctx()) return rc;
-  Weight* w = get_weight(h);
+  WeightRef w = get_weight(h);
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm_residual: bad weight handle");
   if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_qgemm_residual: negative M");
   if (flags & (SDQ_A_HOST | SDQ_OUT_HOST))
@@ -703,7 +754,7 @@ int sdq_qgemm_colsplit(sdq_weight_t h, const float* A_dev, int64_t M, int64_t co
                        float* const* outs_dev, int n_outs, const float* bias_dev, uint32_t flags,
                        void* stream) {
   if (int rc = need_ctx()) return rc;
-  Weight* w = get_weight(h);
+  WeightRef w = get_weight(h);
   if (!w) return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: bad weight handle");
   if (M < 0 || col0 < 0 || N_total < col0 + w->N || n_outs < 1 || n_outs > 8 || !outs_dev)
     return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: bad shape or destination count (1..8)");
@@ -731,8 +782,11 @@ int sdq_qgemm_colsplit(sdq_weight_t h, const float* A_dev, int64_t M, int64_t co
     if (!outs_dev[i]) return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: null destination");
     g.out_all[i] = outs_dev[i];
   }
-  if (!qgemm_tc_supported(g) || !qgemm_tc2_wanted(g, g_ctx->sm_count))
-    return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: destinations must be 16-byte aligned");
+  if (!qgemm_tc_supported(g))
+    return fail(SDQ_ERR_INVALID, "sdq_qgemm_colsplit: the tensor-core kernel cannot take this problem (K % 16 != 0, "
+                                 "an operand that is not 16-byte aligned, or a dimension of 2^31 or more)");
+  if (const char* unfit = qgemm_tc2_unfit(g))
+    return fail(SDQ_ERR_INVALID, std::string("sdq_qgemm_colsplit: ") + unfit);
   std::string why;
   cudaError_t e = launch_qgemm_tc2(g, g_ctx->sm_count, s, &why);
   if (e != cudaSuccess) return fail(SDQ_ERR_CUDA, why.empty() ? std::string("column-split GEMM launch: ") + cudaGetErrorString(e) : why);
@@ -756,8 +810,8 @@ int sdq_ffn_pair(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, const
                  const float* x, int64_t M, float* hidden_dev, float* y, uint32_t flags,
                  void* stream) {
   if (int rc = need_ctx()) return rc;
-  Weight* w1 = get_weight(h1);
-  Weight* w2 = get_weight(h2);
+  WeightRef w1 = get_weight(h1);
+  WeightRef w2 = get_weight(h2);
   if (!w1 || !w2) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: bad weight handle");
   if (w2->K != w1->N) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: fc2 input width differs from fc1 output width");
   if (M < 0) return fail(SDQ_ERR_INVALID, "sdq_ffn_pair: negative M");
@@ -785,7 +839,9 @@ int sdq_ffn_pair(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, const
   // Host x and y: rows are independent, so the pair is run chunk by chunk with the
   // copies of neighbouring chunks overlapping the arithmetic:
   //   copy_in : H2D x[i+1]   |  stream : quant, fc1, quant, fc2 on chunk i  |  copy_out : D2H y[i-1]
-  Context* c = g_ctx;
+  // The pipeline's streams, events and chunk buffers belong to the caller's stream, like the
+  // rest of its scratch: calls on different streams share nothing.
+  Workspace* c = ws;
   if (!c->copy_in) {
     SDQ_CUDA(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
     SDQ_CUDA(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
@@ -840,8 +896,8 @@ int sdq_ffn_block(sdq_weight_t h1, const float* bias1_dev, sdq_weight_t h2, cons
                   float* x_dev, int64_t M, const float* shift_dev, const float* scale_dev,
                   const float* gate_dev, float eps, uint32_t flags, void* stream) {
   if (int rc = need_ctx()) return rc;
-  Weight* w1 = get_weight(h1);
-  Weight* w2 = get_weight(h2);
+  WeightRef w1 = get_weight(h1);
+  WeightRef w2 = get_weight(h2);
   if (!w1 || !w2) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: bad weight handle");
   if (w2->K != w1->N) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: fc2 input width differs from fc1 output width");
   if (w2->N != w1->K) return fail(SDQ_ERR_INVALID, "sdq_ffn_block: fc2 output width differs from the width of x");

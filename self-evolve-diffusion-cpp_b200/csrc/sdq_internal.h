@@ -64,7 +64,26 @@ struct GemmArgs {
   const float* gate = nullptr;    // [N] or null; only read when residual is set
   int32_t* splitk_acc = nullptr;  // [M,N] zeroed int32 sums when K is split, else null
   int k_splits = 1;               // >1 only together with splitk_acc
+  // 2-CTA kernel: all-zero int32 scratch of tail_cap_tiles x 256 x 256 for the partial sums of
+  // the last, partial wave's tiles (null: every tile is computed by one CTA pair).  The launch
+  // leaves it all zero again.  Filled in by the caller; the launcher decides whether to use it.
+  int32_t* tail_acc = nullptr;
+  int tail_cap_tiles = 0;
+  // 2-CTA kernel, set by the launcher: height of a band of the tile walk in 256-row pairs, and
+  // the L2 eviction classes of the operand loads (see launch_qgemm_tc2).
+  int group_pairs = 0;
+  int a_policy = 0, b_policy = 0;
 };
+
+
+// The bulk-store epilogues of the tcgen05 kernels read b_scale, bias and gate four floats at a
+// time: true when those pointers allow it (16-byte aligned).  Otherwise the per-thread scalar
+// epilogue has to be used.
+inline bool epilogue_vectors_aligned(const GemmArgs& g) {
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return aligned(g.b_scale) && (!g.bias || aligned(g.bias)) &&
+         (!g.residual || !g.gate || aligned(g.gate));
+}
 
 // Portable CUDA-core kernel (any M, N, K): qgemm_simt.cu
 cudaError_t launch_qgemm_simt(const GemmArgs& g, cudaStream_t s);
@@ -82,6 +101,11 @@ int qgemm_tc_setup(std::string* why);
 // 2-CTA (cta_group::2) variant for large problems: qgemm_tcgen05_2cta.cu.
 int qgemm_tc2_setup(std::string* why);
 bool qgemm_tc2_wanted(const GemmArgs& g, int sm_count);  // call only if qgemm_tc_supported(g)
+// Tiles of the last, partial wave the 2-CTA launcher would share between all CTA pairs if
+// GemmArgs::tail_acc holds that many zeroed 256 x 256 int32 tiles (0: no scratch needed).
+int qgemm_tc2_tail_tiles(const GemmArgs& g, int sm_count);
+// Why the 2-CTA kernel cannot take this problem at all (null: it can).
+const char* qgemm_tc2_unfit(const GemmArgs& g);
 cudaError_t launch_qgemm_tc2(const GemmArgs& g, int sm_count, cudaStream_t s, std::string* why);
 
 // ---- fp32 matmul on tcgen05, three tf32 products per fp32 product: fgemm_tcgen05.cu ----

@@ -203,3 +203,86 @@ def test_concurrent_host_threads_and_streams(sdq, pkg, oracle):
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+def test_two_threads_run_the_host_pointer_ffn_pipeline(sdq, pkg, oracle):
+    """sdq_ffn_pair with host x and y keeps its copy streams, events and chunk buffers with the
+    caller's stream: two host threads on two streams run the chunked pipeline at the same time
+    and both get the bits of the two-call form."""
+    import ctypes as C
+    import threading
+    rng = np.random.default_rng(99)
+    D, F = 512, 1024
+    w1q, w1s = packed_weights(rng, F, D, oracle)
+    w2q, w2s = packed_weights(rng, D, F, oracle)
+    w1, w2 = sdq.weight_upload(w1q, w1s), sdq.weight_upload(w2q, w2s)
+    jobs = []
+    for M in (5000, 6100):                                # 3 chunks of 2048 rows each, different tails
+        x = (rng.standard_normal((M, D)) * 0.5).astype(np.float32)
+        h = sdq.qgemm_host(w1, x, gelu=True)
+        jobs.append((x, sdq.qgemm_host(w2, h)))
+    errors = []
+
+    def run(job):
+        try:
+            x, want = job
+            M = x.shape[0]
+            y = np.empty((M, D), np.float32)
+            st = sdq.stream_create()
+            for _ in range(6):
+                y[:] = 0
+                sdq._ck(sdq.lib.sdq_ffn_pair(w1, None, w2, None, x.ctypes.data_as(C.c_void_p), M, None,
+                                             y.ctypes.data_as(C.c_void_p), pkg.sdq.A_HOST | pkg.sdq.OUT_HOST, st))
+                if not bits_equal(y, want):
+                    errors.append(M)
+            sdq.stream_destroy(st)
+        except Exception as e:  # pragma: no cover
+            errors.append(repr(e))
+    threads = [threading.Thread(target=run, args=(j,)) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    sdq.weight_release(w1)
+    sdq.weight_release(w2)
+    assert not errors, errors
+
+
+def test_stream_destroy_returns_all_scratch(sdq, pkg, oracle):
+    """Every buffer a stream's calls grew -- quantized activations, split-K sums, layernorm
+    statistics, the tf32 planes of sdq_fmatmul, the fp16 planes of sdq_sdpa, the chunk buffers of the
+    host-pointer FFN pipeline -- goes back to the device when the stream is destroyed."""
+    import torch
+    rng = np.random.default_rng(3)
+    wq, ws = packed_weights(rng, 384, 512, oracle)
+    w = sdq.weight_upload(wq, ws)
+    fw = sdq.fweight_upload((rng.standard_normal((512, 256)) * 0.05).astype(np.float32))
+    A = rng.standard_normal((1000, 512)).astype(np.float32)
+    dA, dout = sdq.to_device(A), sdq.alloc(1000 * 512 * 4)
+    q = sdq.to_device(rng.standard_normal((2048, 1024)).astype(np.float32))
+    o = sdq.alloc(2048 * 1024 * 4)
+    sh = sdq.to_device(np.zeros(512, np.float32))
+    daq, dsc = sdq.alloc(1000 * 512), sdq.alloc(4000)
+
+    def use(st):
+        sdq.qgemm(w, dA.ptr, 1000, dout.ptr, None, 0, st)
+        sdq._ck(sdq.lib.sdq_fmatmul(fw, dA.ptr, 1000, dout.ptr, None, 0, st))
+        sdq._ck(sdq.lib.sdq_sdpa(q.ptr, q.ptr, q.ptr, 2048, 2048, 1024, 8, o.ptr, 0, st))
+        sdq._ck(sdq.lib.sdq_layernorm_mod_quantize(dA.ptr, 1000, 512, sh.ptr, sh.ptr, 1e-6, daq.ptr, dsc.ptr,
+                                                   None, 0, st))
+        sdq.sync(st)
+    st = sdq.stream_create()
+    use(st)                                               # first use also pays one-time driver allocations
+    sdq.stream_destroy(st)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    st = sdq.stream_create()
+    use(st)
+    held = free0 - torch.cuda.mem_get_info()[0]
+    assert held > (16 << 20), held                        # the scratch is really there (k / v^T planes alone: 16 MiB) ...
+    sdq.stream_destroy(st)
+    torch.cuda.synchronize()
+    # ... and it comes back (2 MiB of slack for what the driver keeps per stream)
+    assert torch.cuda.mem_get_info()[0] >= free0 - (2 << 20), (free0, torch.cuda.mem_get_info()[0])
+    sdq.weight_release(w)
+    sdq.weight_release(fw)

@@ -88,8 +88,12 @@ def test_shard_arithmetic(pkg):
             spans = [sh.row_shard(M, world, r) for r in range(world)]
             assert spans[0][0] == 0 and spans[-1][1] == M
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
-            assert all(b % 128 == 0 or b == M for b, _ in spans)
-    assert sh.row_shard(27280, 8, 0) == (0, 3456) and sh.row_shard(27280, 8, 7) == (24192, 27280)
+            assert all(b % 256 == 0 or b == M for b, _ in spans)
+            # balanced in whole 256-row tiles: nobody carries more than ceil(tiles / world)
+            tiles = [-(-(e - b) // 256) for b, e in spans]
+            assert max(tiles) == -(-(-(-M // 256)) // world) and max(tiles) - min(tiles) <= 1
+    assert sh.row_shard(27280, 8, 0) == (0, 3584) and sh.row_shard(27280, 8, 3) == (10752, 14080)
+    assert sh.row_shard(27280, 8, 7) == (24064, 27280)
     for N in (13, 192, 3072, 14336, 18432):
         for world in (1, 2, 4, 8):
             spans = [sh.col_shard(N, world, r) for r in range(world)]

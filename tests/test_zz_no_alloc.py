@@ -72,3 +72,32 @@ def test_static_scratch_rejects_oversize_and_host_pointers(sdq, pkg, oracle):
         sdq.qgemm_static_scratch(wq_ptr, ws_ptr, 32, 64, d.ptr, 4, d.ptr, None, pkg.sdq.A_HOST)
     assert e.value.code == 1
     sdq.weight_release(w)
+
+
+@pytest.mark.parametrize("M,K,N", [(32768, 1024, 256),      # M at its limit AND M*K at its limit: the array's last byte is used
+                                   (16384, 2048, 512),      # M*K at its limit with fewer rows
+                                   (32768, 16, 32)])        # M at its limit, one k-block
+def test_static_scratch_at_its_limits(sdq, pkg, oracle, M, K, N):
+    """Exactly at SDQ_STATIC_MAX_ROWS and SDQ_STATIC_MAX_AQ_BYTES (where an off-by-one in the
+    array's size or in the offsets of its parts would show), through the 2-CTA kernel where the
+    shape has enough tiles: the CPU oracle's bits on sampled rows including the last one, and
+    sdq_qgemm's bits everywhere; one row or one byte more is refused."""
+    assert M <= pkg.sdq.STATIC_MAX_ROWS and M * K <= pkg.sdq.STATIC_MAX_AQ_BYTES
+    assert M == pkg.sdq.STATIC_MAX_ROWS or M * K == pkg.sdq.STATIC_MAX_AQ_BYTES
+    rng = np.random.default_rng(M + K)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    wq, ws = packed_weights(rng, N, K, oracle)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    w = sdq.weight_upload(wq, ws)
+    _, _, wq_ptr, ws_ptr = sdq.weight_info(w)
+    for flags in (0, 0):                           # twice: the second call finds the first one's bytes in the array
+        a, b = _both(sdq, pkg, w, wq_ptr, ws_ptr, N, K, A, bias, flags)
+        assert bits_equal(a, b)
+    rows = np.unique(np.concatenate([[0, M - 1, M - 2, M // 2], rng.choice(M, 61, replace=False)]))
+    assert bits_equal(b[rows], oracle.bias_add(oracle.qgemm(A[rows], wq, ws), bias))
+    dA = sdq.to_device(A[:8])
+    d = sdq.alloc(1024)
+    with pytest.raises(pkg.SdqError) as e:         # one row more
+        sdq.qgemm_static_scratch(wq_ptr, ws_ptr, N, K, dA.ptr, M + 1, d.ptr)
+    assert e.value.code == 1 and "exceeds the fixed scratch" in e.value.msg
+    sdq.weight_release(w)
