@@ -392,7 +392,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
 // Second step for the tiles of a shared last wave: fp32 outputs from the summed int32
 // partial sums, which are cleared on the way so that the scratch is all zero again.
-// grid = (tail tiles, 8); a thread takes 4 consecutive columns of one row at a time.
+// grid = (tail tiles, 64): one group of 4 consecutive columns per thread, so that the pass is
+// one round of independent 16-byte loads and stores (it sits between two dependent launches).
 template <bool kResidual>
 __global__ void __launch_bounds__(256) tail_finalize_kernel(GemmArgs g, int first_tail, int group_pairs) {
   const int num_m_pairs = (int)((g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M));
@@ -451,7 +452,7 @@ int env_int(const char* name, int dflt) {
 // k-block at the sustained int8 rate) and costs one more launch plus a pass over the
 // scratch (~0.2 us per tile).
 int plan_tail(const GemmArgs& g, int64_t tiles, int64_t clusters) {
-  static const int mode = env_int("SDQ_TC2_TAIL", 1);  // 0: never, 1: when it pays, 2: whenever possible
+  const int mode = env_int("SDQ_TC2_TAIL", 1);  // 0: never, 1: when it pays, 2: whenever possible
   if (mode == 0 || g.out_copies > 0) return 0;
   const int64_t tail = tiles % clusters;
   if (tail == 0) return 0;
@@ -460,16 +461,14 @@ int plan_tail(const GemmArgs& g, int64_t tiles, int64_t clusters) {
   const double saved_us = (1.0 - (double)tail / (double)clusters) * kblocks * 0.40 - (4.0 + 0.2 * (double)tail);
   return saved_us > 1.0 ? (int)tail : 0;
 }
-// Height of a band of the tile walk, in 256-row pairs.  A band's rows of aq are fetched from
-// HBM once and then served from L2 to every column block; the weight matrix is re-read once
-// per band, so taller bands mean fewer weight re-reads as long as the band still fits in L2
-// beside the weights in flight: the target is ~24 MB of aq per band.
-int plan_group(const GemmArgs& g) {
-  static const int forced = env_int("SDQ_TC2_GROUP", 0);
-  if (forced > 0) return forced;
-  const double band_bytes_per_pair = 2.0 * BLOCK_M * (double)g.K;
-  int pairs = (int)(24.0e6 / band_bytes_per_pair);
-  return pairs < 4 ? 4 : (pairs > 37 ? 37 : pairs);
+// Height of a band of the tile walk, in 256-row pairs.  The 74 tiles in flight cover
+// (band height) row pairs x (74 / band height) column blocks; the weight matrix is re-read
+// from HBM once per band and a band's rows of aq once.  Measured on the 720p FFN shapes
+// (alternating loops, both GEMMs): 12..30 pairs are within 2 % of each other, 24 is the
+// fastest for both, 4..8 and 54 are 5-8 % slower.
+int plan_group(const GemmArgs&) {
+  const int forced = env_int("SDQ_TC2_GROUP", 0);
+  return forced > 0 ? forced : 24;
 }
 }  // namespace
 
@@ -556,9 +555,8 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g_in, int sm_count, cudaStream_t s,
     if (tiles < clusters) clusters = tiles;
   }
   g.group_pairs = plan_group(g);
-  static const int a_policy = env_int("SDQ_TC2_APOLICY", 0), b_policy = env_int("SDQ_TC2_BPOLICY", 0);
-  g.a_policy = a_policy;
-  g.b_policy = b_policy;
+  g.a_policy = env_int("SDQ_TC2_APOLICY", 0);
+  g.b_policy = env_int("SDQ_TC2_BPOLICY", 0);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(clusters * 2));
   cfg.blockDim = dim3(kNumThreads);
@@ -586,8 +584,8 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g_in, int sm_count, cudaStream_t s,
   if (e == cudaSuccess && tail > 0) {
     const int first_tail = (int)(tiles - tail);
     count_launch();
-    if (g.residual) tail_finalize_kernel<true><<<dim3((unsigned)tail, 8), 256, 0, s>>>(g, first_tail, g.group_pairs);
-    else tail_finalize_kernel<false><<<dim3((unsigned)tail, 8), 256, 0, s>>>(g, first_tail, g.group_pairs);
+    if (g.residual) tail_finalize_kernel<true><<<dim3((unsigned)tail, 64), 256, 0, s>>>(g, first_tail, g.group_pairs);
+    else tail_finalize_kernel<false><<<dim3((unsigned)tail, 64), 256, 0, s>>>(g, first_tail, g.group_pairs);
     e = cudaGetLastError();
   }
   return e;

@@ -53,26 +53,84 @@ namespace {
 
 using sdq::fail;
 
-struct Cursor {
-  const uint8_t* p;
-  const uint8_t* end;
-  bool ok = true;
-  bool need(size_t n) {
-    if ((size_t)(end - p) < n) ok = false;
-    return ok;
+// The unread part of the mapped file.  take() hands out the next n bytes, or nothing when
+// fewer are left; nothing is ever read past the end of the mapping.
+class Bytes {
+ public:
+  Bytes(const uint8_t* begin, size_t n) : at_(begin), left_(n) {}
+  const uint8_t* take(size_t n) {
+    if (n > left_) return nullptr;
+    const uint8_t* p = at_;
+    at_ += n;
+    left_ -= n;
+    return p;
   }
-  uint32_t u32() { uint32_t v = 0; if (need(4)) { memcpy(&v, p, 4); p += 4; } return v; }
-  uint64_t u64() { uint64_t v = 0; if (need(8)) { memcpy(&v, p, 8); p += 8; } return v; }
-  uint8_t u8() { uint8_t v = 0; if (need(1)) v = *p++; return v; }
+  template <typename T>
+  bool read(T* v) {  // little-endian scalar, any alignment
+    const uint8_t* p = take(sizeof(T));
+    if (p) memcpy(v, p, sizeof(T));
+    return p != nullptr;
+  }
+  const uint8_t* here() const { return at_; }
+  size_t left() const { return left_; }
+
+ private:
+  const uint8_t* at_;
+  size_t left_;
 };
 
-struct RawEntry {
+// What can be wrong with one directory record; the texts are the reference loader's
+// (src/serde/sdcpp.cpp:78-101), and so is the order in which the conditions are tested.
+enum class Flaw { None, Truncated, DtypeCode, Rank, NegativeDim, Size, NoLastDim };
+const char* flaw_text(Flaw f) {
+  switch (f) {
+    case Flaw::Truncated: return "truncated file";
+    case Flaw::DtypeCode: return "bad dtype code";
+    case Flaw::Rank: return "ndim too large";
+    case Flaw::NegativeDim: return "negative dim";
+    case Flaw::Size: return "tensor too large";
+    case Flaw::NoLastDim: return "quantized tensor needs a last dim";
+    default: return "";
+  }
+}
+
+// One directory record: a tensor's name, storage kind, shape and place in the blob.
+struct Record {
   std::string name;
-  uint8_t code;
-  std::vector<int64_t> dims;
-  uint64_t off;
-  int64_t numel, rows, blob;
+  bool quantized = false;       // int8 rows + one fp32 scale per row; otherwise raw fp32
+  std::vector<int64_t> shape;
+  uint64_t where = 0;           // offset of its bytes from the start of the blob
+  uint64_t elements = 0;
+  uint64_t scale_count() const { return quantized ? elements / (uint64_t)shape.back() : 0; }
+  uint64_t span() const { return quantized ? elements + 4 * scale_count() : 4 * elements; }
 };
+
+constexpr uint32_t kMaxRank = 8;
+constexpr uint64_t kMaxElements = uint64_t(1) << 40;
+
+Flaw decode_record(Bytes& in, Record* r) {
+  uint32_t name_bytes = 0, rank = 0;
+  uint8_t kind = 0;
+  const uint8_t* name = in.read(&name_bytes) ? in.take(name_bytes) : nullptr;
+  if (!name) return Flaw::Truncated;
+  r->name.assign(reinterpret_cast<const char*>(name), name_bytes);
+  if (!in.read(&kind)) return Flaw::Truncated;
+  if (kind > 1) return Flaw::DtypeCode;
+  r->quantized = kind == 0;
+  if (!in.read(&rank)) return Flaw::Truncated;
+  if (rank > kMaxRank) return Flaw::Rank;
+  r->shape.assign(rank, 0);
+  r->elements = 1;
+  for (int64_t& extent : r->shape) {
+    if (!in.read(&extent)) return Flaw::Truncated;
+    if (extent < 0) return Flaw::NegativeDim;
+    if (extent != 0 && r->elements > kMaxElements / (uint64_t)extent) return Flaw::Size;
+    r->elements *= (uint64_t)extent;
+  }
+  if (!in.read(&r->where)) return Flaw::Truncated;
+  if (r->quantized && (rank == 0 || r->shape.back() < 1)) return Flaw::NoLastDim;
+  return Flaw::None;
+}
 
 void fill_entry(const sdq_pack::Item& it, const sdq_pack* p, sdq_entry* out) {
   out->name = it.name.c_str();
@@ -111,70 +169,44 @@ int sdq_pack_open(const char* path, uint32_t flags, sdq_pack** out) {
     munmap(base, size);
     return fail(SDQ_ERR_FORMAT, std::string("sdcpp: ") + m);
   };
-  const uint8_t* b = (const uint8_t*)base;
-  Cursor c{b, b + size};
-  if (memcmp(c.p, "SDCP", 4) != 0) return bad("bad magic");
-  c.p += 4;
-  if (c.u32() != 1) return bad("unsupported version");
-  const uint32_t count = c.u32();
-  std::vector<RawEntry> es;
-  es.reserve(std::min<uint32_t>(count, 1u << 20));
+  // header: magic, version, record count, then the directory; the blob is whatever follows it
+  Bytes in(static_cast<const uint8_t*>(base), size);
+  uint32_t version = 0, count = 0;
+  if (memcmp(in.take(4), "SDCP", 4) != 0) return bad("bad magic");   // size >= 16 was checked above
+  in.read(&version);
+  if (version != 1) return bad("unsupported version");
+  in.read(&count);
+  std::vector<Record> directory;
+  directory.reserve(std::min<uint32_t>(count, 1u << 20));
   for (uint32_t i = 0; i < count; i++) {
-    RawEntry e;
-    const uint32_t nl = c.u32();
-    if (!c.ok || !c.need(nl)) return bad("truncated file");
-    e.name.assign((const char*)c.p, nl);
-    c.p += nl;
-    e.code = c.u8();
-    if (!c.ok) return bad("truncated file");
-    if (e.code > 1) return bad("bad dtype code");
-    const uint32_t nd = c.u32();
-    if (!c.ok) return bad("truncated file");
-    if (nd > 8) return bad("ndim too large");
-    e.dims.resize(nd);
-    int64_t numel = 1;
-    for (auto& d : e.dims) {
-      d = (int64_t)c.u64();
-      if (!c.ok) return bad("truncated file");
-      if (d < 0) return bad("negative dim");
-      if (d && numel > (int64_t{1} << 40) / d) return bad("tensor too large");
-      numel *= d;
-    }
-    e.numel = numel;
-    e.off = c.u64();
-    if (!c.ok) return bad("truncated file");
-    if (e.code == 0) {
-      if (nd == 0 || e.dims.back() < 1) return bad("quantized tensor needs a last dim");
-      e.rows = numel / e.dims.back();
-      e.blob = numel + e.rows * 4;
-    } else {
-      e.rows = 0;
-      e.blob = numel * 4;
-    }
-    es.push_back(std::move(e));
+    directory.emplace_back();
+    const Flaw f = decode_record(in, &directory.back());
+    if (f != Flaw::None) return bad(flaw_text(f));
   }
-  const uint64_t data_size = (uint64_t)(c.end - c.p);
-  for (const RawEntry& e : es)
-    if (e.off > data_size || (uint64_t)e.blob > data_size - e.off) return bad("data out of bounds");
+  const uint8_t* blob = in.here();
+  const uint64_t blob_bytes = in.left();
+  for (const Record& r : directory)
+    if (r.where > blob_bytes || r.span() > blob_bytes - r.where) return bad("data out of bounds");
 
+  // entries, as the reference's map presents them: a quantized tensor as `name` (int8, its own
+  // shape) and `name.scale` (fp32, one per row) right behind its bytes; a raw tensor as `name`
   sdq_pack* p = new sdq_pack;
   p->base = base;
   p->size = size;
-  auto add = [&](std::string name, int32_t dt, std::vector<int64_t> dims, const uint8_t* data,
-                 uint64_t nbytes) {
-    if (p->index.count(name)) return;  // the reference's map keeps the first of equal names
-    p->index[name] = p->items.size();
+  auto present = [&](const std::string& name, int32_t dt, std::vector<int64_t> dims, const uint8_t* data,
+                     uint64_t nbytes) {
+    if (!p->index.emplace(name, p->items.size()).second) return;  // the first of equal names stays
     sdq_pack::Item it;
-    it.name = std::move(name); it.dtype = dt; it.dims = std::move(dims); it.data = data; it.nbytes = nbytes;
+    it.name = name; it.dtype = dt; it.dims = std::move(dims); it.data = data; it.nbytes = nbytes;
     p->items.push_back(std::move(it));
   };
-  for (RawEntry& e : es) {
-    const uint8_t* w = c.p + e.off;
-    if (e.code == 0) {
-      add(e.name, SDQ_DT_I8, e.dims, w, (uint64_t)e.numel);
-      add(e.name + ".scale", SDQ_DT_F32, {e.rows}, w + e.numel, (uint64_t)e.rows * 4);
+  for (const Record& r : directory) {
+    const uint8_t* bytes = blob + r.where;
+    if (r.quantized) {
+      present(r.name, SDQ_DT_I8, r.shape, bytes, r.elements);
+      present(r.name + ".scale", SDQ_DT_F32, {(int64_t)r.scale_count()}, bytes + r.elements, 4 * r.scale_count());
     } else {
-      add(e.name, SDQ_DT_F32, e.dims, w, (uint64_t)e.blob);
+      present(r.name, SDQ_DT_F32, r.shape, bytes, r.span());
     }
   }
 

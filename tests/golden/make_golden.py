@@ -20,7 +20,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("REF", "/root/reference")
+REF = os.environ.get("REF") or os.path.join(os.path.dirname(ROOT), "reference")   # beside this repository
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(REF, "tools", "quantize"))
 

@@ -32,7 +32,8 @@ def test_dropin_on_gpu():
 def test_tensor_layout_matches_reference_header(tmp_path):
     """Where the reference tree is mounted: sd::Tensor here and there have the same layout,
     so objects compiled against the reference's header can link against this library."""
-    ref = os.environ.get("REF", "/root/reference")
+    from util import reference_tree
+    ref = reference_tree()
     if not os.path.exists(os.path.join(ref, "src/core/tensor.h")):
         pytest.skip("reference tree not mounted")
     src = tmp_path / "layout.cpp"

@@ -216,7 +216,8 @@ def test_pack_restatement_matches_reference_packer_on_random_checkpoints(oracle,
     import subprocess
     import sys
     from util import random_safetensors
-    ref_packer = os.path.join(os.environ.get("REF", "/root/reference"), "tools", "quantize", "pack_sdcpp.py")
+    from util import reference_tree
+    ref_packer = os.path.join(reference_tree(), "tools", "quantize", "pack_sdcpp.py")
     if not os.path.exists(ref_packer):
         pytest.skip("reference tree not mounted")
     rng = np.random.default_rng(404)

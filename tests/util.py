@@ -1,7 +1,14 @@
 """Shared helpers of the tests: seeded inputs and comparison metrics."""
 import hashlib
+import os
 
 import numpy as np
+
+
+def reference_tree():
+    """The reference checkout: $REF, else a directory `reference` beside this repository."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    return os.environ.get("REF") or os.path.join(os.path.dirname(os.path.dirname(here)), "reference")
 
 
 def sha(a):
