@@ -37,10 +37,11 @@ using namespace tc;
 
 constexpr int kBlockN2 = 256;
 constexpr int kHalfBytes = BLOCK_M * BLOCK_K;         // 16 KiB: 128 rows x 128 B
-constexpr int kStageBytes2 = 2 * kHalfBytes;          // per CTA: A half + B half
 constexpr int kTmemCols2 = 2 * kBlockN2;
 // dynamic shared memory: pipeline stages + epilogue staging boxes + barriers + realignment slack
-constexpr int smem_bytes2(int stages, int boxes) { return stages * kStageBytes2 + 8 * 4096 * boxes + 256 + 1024; }
+constexpr int smem_bytes2(int stages, int boxes, int a_copies = 1) {
+  return stages * (a_copies * kHalfBytes + kHalfBytes) + 8 * 4096 * boxes + 256 + 1024;
+}
 // D=s32, A=B=s8, K-major both, N=256 (>>3 at bit 17), M=256 (>>4 at bit 24)
 constexpr uint32_t kIdesc2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN2 >> 3) << 17) |
                              ((uint32_t)(256 >> 4) << 24);
@@ -159,7 +160,13 @@ struct OutMaps {
 
 // kStages2: depth of the operand ring; kBoxes: staging boxes per epilogue warp (with two, a
 // warp fills one box while the bulk store of the other is still reading shared memory).
-template <int kStages2, int kBoxes, bool kResidual>
+// kACopies > 1 is a measuring variant, not a product path: every k-block's A tile is fetched
+// kACopies times into that many slots of the stage (the MMAs read the first).  With 4 copies a
+// stage carries the bytes an fp32 A tile would -- what a GEMM that quantized its activations in
+// its own prologue would have to move through shared memory -- at the ring depth that then still
+// fits (2 stages of 80 KiB); the conversion itself (another shared-memory round trip per tile)
+// is not even included.  Results are unchanged; only the time is of interest.
+template <int kStages2, int kBoxes, bool kResidual, int kACopies = 1>
 __global__ void __launch_bounds__(kNumThreads, 1)
     qgemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
@@ -172,9 +179,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   uint8_t* smem = smem_raw + (base - raw);
 
   const uint32_t smem_a = base;
-  const uint32_t smem_b = base + kStages2 * kHalfBytes;
-  const uint32_t smem_staging = base + kStages2 * kStageBytes2;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes2 + kStagingBytes2);
+  constexpr int kAStage = kACopies * kHalfBytes;       // bytes of A per stage
+  constexpr int kStageBytes = kAStage + kHalfBytes;    // per CTA: A half (x copies) + B half
+  const uint32_t smem_b = base + kStages2 * kAStage;
+  const uint32_t smem_staging = base + kStages2 * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes + kStagingBytes2);
   const uint32_t bar_full = smem_u32(bars);            // used in the leader only
   const uint32_t bar_empty = bar_full + 8 * kStages2;  // one per CTA, signalled by multicast commit
   const uint32_t bar_tfull = bar_empty + 8 * kStages2; // one per CTA, multicast commit
@@ -239,9 +248,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 0x1100 | 1);
           if (!ok) break;
           const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
-          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes2);
-          tma_load_2d_pair(smem_a + stage * kHalfBytes, &tmap_a, full_leader, kb * BLOCK_K, row0,
-                           a_policy);
+          if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes);
+#pragma unroll
+          for (int copy = 0; copy < kACopies; copy++)
+            tma_load_2d_pair(smem_a + stage * kAStage + copy * kHalfBytes, &tmap_a, full_leader,
+                             kb * BLOCK_K, row0, a_policy);
           tma_load_2d_pair(smem_b + stage * kHalfBytes, &tmap_b, full_leader, kb * BLOCK_K, wrow0,
                            b_policy);
           if (++stage == kStages2) { stage = 0; phase ^= 1u; }
@@ -263,7 +274,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 0x1200 | 2);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t adesc = make_smem_desc(smem_a + stage * kHalfBytes);
+          const uint64_t adesc = make_smem_desc(smem_a + stage * kAStage);
           const uint64_t bdesc = make_smem_desc(smem_b + stage * kHalfBytes);
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; k++)
@@ -474,6 +485,10 @@ int plan_group(const GemmArgs&) {
 
 int qgemm_tc2_setup(std::string* why) {
   cudaError_t a = cudaSuccess;
+  cudaFuncSetAttribute((const void*)qgemm_tc2_kernel<2, 1, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       smem_bytes2(2, 1, 4));
+  cudaFuncSetAttribute((const void*)qgemm_tc2_kernel<2, 1, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       smem_bytes2(2, 1, 1));
   const void* kernels[4] = {(const void*)qgemm_tc2_kernel<6, 1, false>, (const void*)qgemm_tc2_kernel<6, 1, true>,
                             (const void*)qgemm_tc2_kernel<5, 2, false>, (const void*)qgemm_tc2_kernel<5, 2, true>};
   for (int i = 0; i < 4 && a == cudaSuccess; i++)
@@ -571,10 +586,19 @@ cudaError_t launch_qgemm_tc2(const GemmArgs& g_in, int sm_count, cudaStream_t s,
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see grid_dependency_wait()
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 2;
+  cfg.numAttrs = env_int("SDQ_TC2_PDL", 1) ? 2 : 1;
   count_launch();
   cudaError_t e;
-  if (g.residual) {
+  // SDQ_TC2_PROBE=wideA: 4 x the A bytes per stage, 2 stages; =shallow: the same 2 stages with
+  // the ordinary bytes (to separate the effect of the ring depth from that of the bytes)
+  const char* probe = getenv("SDQ_TC2_PROBE");
+  if (probe && !g.residual && probe[0] == 'w') {
+    cfg.dynamicSmemBytes = smem_bytes2(2, 1, 4);
+    e = cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<2, 1, false, 4>, ta, tb, outs, num_outs, ttail, g);
+  } else if (probe && !g.residual && probe[0] == 's') {
+    cfg.dynamicSmemBytes = smem_bytes2(2, 1, 1);
+    e = cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<2, 1, false, 1>, ta, tb, outs, num_outs, ttail, g);
+  } else if (g.residual) {
     e = deep ? cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<6, 1, true>, ta, tb, outs, num_outs, ttail, g)
              : cudaLaunchKernelEx(&cfg, qgemm_tc2_kernel<5, 2, true>, ta, tb, outs, num_outs, ttail, g);
   } else {
