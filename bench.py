@@ -1142,12 +1142,21 @@ def run_fp32(args):
     att_clocks = {}
     t_att = timed(lambda: s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), 0, sp)), att_clocks)
     att_launches = (s.launches() - n0) // (args.steps + max(args.warmup, 1))
-    t_att_v16 = timed(lambda: s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), pkg.sdq.SDPA_V_FP16, sp)))
-    s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), 0, sp))      # (out: the full-precision result again)
     rows = min(L, 1024)                                   # float64 check: two heads, the first rows
     q64, k64, v64 = [x.view(L, H, 128).transpose(0, 1)[:2].double() for x in (q, k, v)]
     ref = torch.softmax(q64[:, :rows] @ k64.transpose(1, 2) / 128 ** 0.5, -1) @ v64
-    err_att = float((out.view(L, H, 128).transpose(0, 1)[:2, :rows].double() - ref).abs().max() / ref.abs().max())
+
+    def err_now():
+        return float((out.view(L, H, 128).transpose(0, 1)[:2, :rows].double() - ref).abs().max() / ref.abs().max())
+    variants = {}
+    for name, fl in (("v_as_one_fp16", pkg.sdq.SDPA_V_FP16), ("k_as_one_fp16", pkg.sdq.SDPA_K_FP16),
+                     ("k_and_v_as_one_fp16", pkg.sdq.SDPA_K_FP16 | pkg.sdq.SDPA_V_FP16)):
+        t_var = timed(lambda: s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), fl, sp)))
+        variants[name] = {"ms": t_var, "max_err_over_max_abs_vs_float64": err_now()}
+    t_att_v16 = variants["v_as_one_fp16"]["ms"]
+    s._ck(lib.sdq_sdpa(p(q), p(k), p(v), L, L, Cc, H, p(out), 0, sp))      # (out: the full-precision result again)
+    torch.cuda.synchronize()
+    err_att = err_now()
     torch.backends.cuda.matmul.allow_tf32 = False
     tq, tk, tv = [x.view(1, L, H, 128).transpose(1, 2) for x in (q, k, v)]
     t_att_torch = timed(lambda: torch.nn.functional.scaled_dot_product_attention(tq, tk, tv))
@@ -1174,7 +1183,7 @@ def run_fp32(args):
                       "gpu_launches": att_launches * args.steps, "clocks": att_clocks,
                       "attention": {"ms": t_att, "tflops": att_flop / (t_att * 1e-3) / 1e12,
                                     "max_err_over_max_abs_vs_float64": err_att, "torch_fp32_sdpa_ms": t_att_torch,
-                                    "ms_with_v_as_one_fp16": t_att_v16,
+                                    "ms_with_v_as_one_fp16": t_att_v16, "reduced_operand_variants": variants,
                                     "frac_of_measured_bf16_peak": att_flop / (t_att * 1e-3) / 1e12 / bf16, "of": pk_kind,
                                     # 48 fp16 MMAs of 128x128x16 per 128 keys against 16 of plain fp16 attention
                                     "issued_fp16_tflops": 3.0 * att_flop / (t_att * 1e-3) / 1e12},

@@ -65,6 +65,12 @@ typedef uint64_t sdq_weight_t;
                                * product instead of three and half the v^T traffic; outputs move by
                                * up to ~2.5e-4 of the largest (inside the reference's 1e-3 bound) */
 
+#define SDQ_SDPA_K_FP16 0x100u /* sdq_sdpa: k enters the scores as one fp16 number per element (q keeps
+                                * both of its planes): two MMAs per product instead of three and half the
+                                * k traffic.  The scores then carry k's 2^-12 rounding, which the softmax
+                                * turns into a relative error of the same size on every weight; see the
+                                * measured figures beside SDQ_SDPA_V_FP16 in the description of sdq_sdpa */
+
 /* source element types of sdq_quantize_rows (the packer's SRC table,
  * tools/quantize/pack_sdcpp.py:26-35) */
 #define SDQ_F32 0

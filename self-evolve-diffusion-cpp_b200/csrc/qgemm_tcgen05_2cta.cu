@@ -473,13 +473,18 @@ int plan_tail(const GemmArgs& g, int64_t tiles, int64_t clusters) {
   return saved_us > 1.0 ? (int)tail : 0;
 }
 // Height of a band of the tile walk, in 256-row pairs.  The 74 tiles in flight cover
-// (band height) row pairs x (74 / band height) column blocks; the weight matrix is re-read
-// from HBM once per band and a band's rows of aq once.  Measured on the 720p FFN shapes
-// (alternating loops, both GEMMs): 12..30 pairs are within 2 % of each other, 24 is the
-// fastest for both, 4..8 and 54 are 5-8 % slower.
-int plan_group(const GemmArgs&) {
+// (band height) row pairs x (74 / band height) column blocks.  A band's rows of aq are fetched
+// from HBM once if the band stays in L2 while its column blocks pass (otherwise once per wave),
+// and the weight matrix is re-read once per band: so the band is made as tall as ~32 MB of aq
+// allow, and no taller than 24 pairs.  Measured on the 720p FFN shapes (alternating loops):
+// K = 3072: 12..30 pairs within 2 % of each other and 4..8 or 54 pairs 5-8 % slower, DRAM reads
+// per launch 688 MB at 8 pairs, 365 MB at 24; K = 14336: all of 6..24 within 2 %, DRAM reads
+// 1.35 GB at 8 pairs (29 MB of aq per band) against 1.93 GB at 24 (88 MB: re-read every wave).
+int plan_group(const GemmArgs& g) {
   const int forced = env_int("SDQ_TC2_GROUP", 0);
-  return forced > 0 ? forced : 24;
+  if (forced > 0) return forced;
+  const int pairs = (int)(32.0e6 / (2.0 * BLOCK_M * (double)g.K));
+  return pairs < 4 ? 4 : (pairs > 24 ? 24 : pairs);
 }
 }  // namespace
 

@@ -142,6 +142,7 @@ struct SdpaArgs {
   int64_t Lq, Lk, C;
   int heads;
   int v_lo;          // 1: P*V uses both planes of v^T (three MMAs per product), 0: the hi plane only (two)
+  int k_lo;          // 1: the scores use both planes of k (three MMAs per product), 0: the hi plane only (two)
   float scale_log2e;  // (1 / sqrt(head_dim)) * log2(e)
   int* status;
 };
@@ -234,9 +235,10 @@ __global__ void __launch_bounds__(kAThreads, 1)
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const int h = item / nqt;
-        for (int n = 0; n < 2 * nblk; n++) {
-          const int j = n >> 1;
-          const bool lo = n & 1;
+        const int planes = g.k_lo ? 2 : 1;  // ring slots per key block
+        for (int n = 0; n < planes * nblk; n++) {
+          const int j = g.k_lo ? n >> 1 : n;
+          const bool lo = g.k_lo && (n & 1);
           ok = mbar_wait(bar_kempty + 8 * slot, phase ^ 1u, abort_flag, g.status, 0x800 | 1);
           if (!ok) break;
           const uint32_t full = bar_kfull + 8 * slot;
@@ -294,12 +296,14 @@ __global__ void __launch_bounds__(kAThreads, 1)
         // weights; the k slots are released as soon as the scores that read them are done.
         bool any = false;
         for (int j = (int)par; j < nblk; j += 2) {
-          const uint32_t seq = seq0 + (uint32_t)(2 * j);
+          const uint32_t seq = seq0 + (uint32_t)(g.k_lo ? 2 * j : j);
           const uint32_t slot_hi = seq & 3u, slot_lo = (seq + 1) & 3u;
           ok = mbar_wait_spin(bar_kfull + 8 * slot_hi, (seq >> 2) & 1u, abort_flag, g.status, 0x900 | 7);
           if (!ok) break;
-          ok = mbar_wait_spin(bar_kfull + 8 * slot_lo, ((seq + 1) >> 2) & 1u, abort_flag, g.status, 0x900 | 6);
-          if (!ok) break;
+          if (g.k_lo) {
+            ok = mbar_wait_spin(bar_kfull + 8 * slot_lo, ((seq + 1) >> 2) & 1u, abort_flag, g.status, 0x900 | 6);
+            if (!ok) break;
+          }
           if (any) {
             ok = mbar_wait_spin(bar_pvdone + 8 * par, pv_ph, abort_flag, g.status, 0x900 | 8);
             if (!ok) break;
@@ -314,11 +318,11 @@ __global__ void __launch_bounds__(kAThreads, 1)
             const uint64_t k_hi = make_smem_desc(st_hi + off) + adv;
             const uint64_t k_lo = make_smem_desc(st_lo + off) + adv;
             umma_f16_ts(d2, tmem_base + kColQlo + ks * 8, k_hi, kIdescH, (uint32_t)(ks != 0));
-            umma_f16_ts(d2, tmem_base + kColQhi + ks * 8, k_lo, kIdescH, 1u);
+            if (g.k_lo) umma_f16_ts(d2, tmem_base + kColQhi + ks * 8, k_lo, kIdescH, 1u);
             umma_f16_ts(d2, tmem_base + kColQhi + ks * 8, k_hi, kIdescH, 1u);
           }
           umma_commit(bar_kempty + 8 * slot_hi);
-          umma_commit(bar_kempty + 8 * slot_lo);
+          if (g.k_lo) umma_commit(bar_kempty + 8 * slot_lo);
           umma_commit(bar_sfull + 8 * par);
           any = true;
         }
@@ -328,7 +332,7 @@ __global__ void __launch_bounds__(kAThreads, 1)
           pv_ph ^= 1u;
           if (!ok) break;
         }
-        seq0 += (uint32_t)(2 * nblk);
+        seq0 += (uint32_t)(g.k_lo ? 2 * nblk : nblk);
       }
     }
   } else if (warp == 11) {
@@ -811,6 +815,7 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
     return cudaErrorInvalidValue;
   SdpaArgs g;
   g.v_lo = (flags & SDQ_SDPA_V_FP16) ? 0 : 1;
+  g.k_lo = (flags & SDQ_SDPA_K_FP16) ? 0 : 1;
   g.q = q; g.out = out; g.absmax = absmax; g.redo = redo; g.Lq = Lq; g.Lk = Lk; g.C = C; g.heads = heads;
   g.scale_log2e = scale * 1.4426950408889634f;
   g.status = status;

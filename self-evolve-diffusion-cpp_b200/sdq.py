@@ -14,6 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # flags / codes of include/sdq.h
 A_HOST, OUT_HOST, GELU_TANH, FORCE_SIMT, SYNC, LN_TREE_SUMS, LN_AFFINE = 0x1, 0x2, 0x4, 0x8, 0x10, 0x20, 0x40
 SDPA_V_FP16 = 0x80
+SDPA_K_FP16 = 0x100
 F32, BF16, F16 = 0, 1, 2
 MODE_PACKER, MODE_ROWWISE = 0, 1
 SRC_HOST, DST_HOST = 0x1, 0x2
@@ -394,14 +395,15 @@ class Sdq:
                                       A_HOST | OUT_HOST | (FORCE_SIMT if force_simt else 0), None))
         return out
 
-    def sdpa_np(self, q, k, v, heads, force_simt=False, v_fp16=False):
+    def sdpa_np(self, q, k, v, heads, force_simt=False, v_fp16=False, k_fp16=False):
         """numpy in, numpy out through sdq_sdpa."""
         q, k, v = [np.ascontiguousarray(a, np.float32) for a in (q, k, v)]
         Lq, Cc = q.shape
         dq, dk, dv = self.to_device(q), self.to_device(k), self.to_device(v)
         dout = self.alloc(max(Lq * Cc * 4, 4))
         self._ck(self.lib.sdq_sdpa(dq.ptr, dk.ptr, dv.ptr, Lq, k.shape[0], Cc, heads, dout.ptr,
-                                   SYNC | (FORCE_SIMT if force_simt else 0) | (SDPA_V_FP16 if v_fp16 else 0),
+                                   SYNC | (FORCE_SIMT if force_simt else 0) | (SDPA_V_FP16 if v_fp16 else 0) |
+                                   (SDPA_K_FP16 if k_fp16 else 0),
                                    None))
         return dout.to_numpy(np.float32, (Lq, Cc))
 

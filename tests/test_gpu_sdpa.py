@@ -138,6 +138,27 @@ def test_v_as_one_fp16_number(sdq):
     assert 2e-5 < max_rel_err(fast, want) < 4e-4           # (the flag did something, and stayed in bounds)
 
 
+def test_k_as_one_fp16_number(sdq):
+    """SDQ_SDPA_K_FP16: two MMAs per score product (q keeps both planes, k only its leading one);
+    alone and together with SDQ_SDPA_V_FP16 the outputs stay inside the reference's 1e-3 bound,
+    also on rows peaked enough that one key carries most of the weight."""
+    rng = np.random.default_rng(13)
+    heads, Lq, Lk = 3, 500, 1111
+    q, k, v = [rng.standard_normal((n, heads * 128)).astype(np.float32) for n in (Lq, Lk, Lk)]
+    for qmul in (1.0, 3.0):
+        want = attention64(q * qmul, k, v, heads)
+        full = sdq.sdpa_np(q * qmul, k, v, heads)
+        fast = sdq.sdpa_np(q * qmul, k, v, heads, k_fp16=True)
+        both = sdq.sdpa_np(q * qmul, k, v, heads, k_fp16=True, v_fp16=True)
+        assert max_rel_err(full, want) < 2e-5
+        assert 2e-5 < max_rel_err(fast, want) < 1e-3
+        assert max_rel_err(both, want) < 1e-3
+    # an odd number of key blocks, fewer keys than one block, several work items per CTA
+    for Lq2, Lk2 in [(130, 129), (300, 77), (1000, 1600)]:
+        q2, k2, v2 = [rng.standard_normal((n, 128)).astype(np.float32) for n in (Lq2, Lk2, Lk2)]
+        assert max_rel_err(sdq.sdpa_np(q2, k2, v2, 1, k_fp16=True), attention64(q2, k2, v2, 1)) < 1e-3
+
+
 def test_other_head_sizes_take_the_cuda_core_kernel(sdq):
     rng = np.random.default_rng(2)
     for heads, hd, Lq, Lk in [(3, 64, 40, 77), (2, 96, 9, 130), (1, 20, 5, 3)]:
