@@ -208,6 +208,53 @@ static void test_pack(const std::string& golden) {
       ref[i * 384 + j] = (float)acc;
     }
   CHECK(cosine(out.ptr<float>(), ref.data(), 70 * 384) > 0.999);
+
+  // A view of the same bytes with another shape (the caller's i8view2d, src/model/ovi_dit.cpp:42-50,
+  // may reshape a pack tensor): [384, 256] seen as [768, 128] with one scale per new row.  The
+  // device copy made at load has the pack's own extents; the call must not run with those.
+  Tensor v;
+  v.shape = {768, 128};
+  v.dtype = DType::I8;
+  v.data = w.data;
+  v.nbytes = w.nbytes;
+  v.owning = false;
+  Tensor vs({768}, DType::F32), A2({9, 128}, DType::F32), out2;
+  for (int j = 0; j < 768; j++) vs.ptr<float>()[j] = 0.01f + 0.001f * (j % 7);
+  fill_uniform(A2, 4);
+  qgemm(A2, v, vs, out2);
+  CHECK(out2.rows() == 9 && out2.cols() == 768);
+  std::vector<float> ref2(9 * 768);
+  for (int i = 0; i < 9; i++)
+    for (int j = 0; j < 768; j++) {
+      double acc = 0;
+      for (int k = 0; k < 128; k++) acc += (double)A2.ptr<float>()[i * 128 + k] * (v.ptr<int8_t>()[j * 128 + k] * vs.ptr<float>()[j]);
+      ref2[i * 768 + j] = (float)acc;
+    }
+  CHECK(cosine(out2.ptr<float>(), ref2.data(), 9 * 768) > 0.999);
+}
+
+static void test_tensor_storage() {
+  // Once the device is in use, large owning tensors come from the page-locked pool: still
+  // 64-byte aligned, still zero-filled by the public constructor, and a released block that is
+  // handed out again is cleared again.
+  const int64_t n = 1 << 20;                       // 4 MiB
+  void* first = nullptr;
+  {
+    Tensor t({n}, DType::F32);
+    first = t.data;
+    CHECK(((uintptr_t)t.data & 63) == 0);
+    bool zero = true;
+    for (int64_t i = 0; i < n; i += 997) zero = zero && t.ptr<float>()[i] == 0.f;
+    CHECK(zero);
+    for (int64_t i = 0; i < n; i++) t.ptr<float>()[i] = 1.f;
+  }
+  Tensor u({n}, DType::F32);
+  bool zero = true;
+  for (int64_t i = 0; i < n; i += 997) zero = zero && u.ptr<float>()[i] == 0.f;
+  CHECK(zero);
+  std::printf("tensor storage: block %s\n", u.data == first ? "reused from the pool" : "fresh");
+  Tensor small({16}, DType::F32);                  // small tensors stay ordinary allocations
+  CHECK(small.owning && ((uintptr_t)small.data & 63) == 0);
 }
 
 int main(int argc, char** argv) {
@@ -230,6 +277,7 @@ int main(int argc, char** argv) {
     test_sdpa(70, 130, 2);
     test_sdpa(300, 257, 1);
     test_pack(golden);
+    test_tensor_storage();
   }
   if (g_fail) std::printf("test_dropin: %d FAILED\n", g_fail);
   else std::printf("test_dropin: all passed%s\n", cpu_only ? " (cpu part)" : "");
