@@ -799,35 +799,43 @@ def run_branch(args):
     orc = None
     results, load = [], None
     for (bname, linears, own_tokens, other_tokens) in branches:
-        weights, pack_ms, pack_elems, verified = [], 0.0, 0, 0
+        weights, pack_elems, verified = [], 0, 0
         sha_gpu, sha_cpu = hashlib.sha256(), hashlib.sha256()
+        # the branch's bf16 weights, then ONE timed sweep of the packer over all of them (launches
+        # back to back, as a packer run over a checkpoint makes them), then the comparison
+        srcs = []
         for b in range(blocks):
             for (name, K, N, rows) in linears:
                 wb = (torch.randn(N, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
                 q = torch.empty(N, K, device=dev, dtype=torch.int8)
                 sc = torch.empty(N, device=dev, dtype=torch.float32)
-                e0, e1 = ev(), ev()
-                e0.record(stream)
-                s._ck(lib.sdq_quantize_rows(wb.data_ptr(), S.BF16, N, K, S.MODE_PACKER, q.data_ptr(), sc.data_ptr(), 0, sp))
-                e1.record(stream)
-                torch.cuda.synchronize()
-                pack_ms += e0.elapsed_time(e1)
+                srcs.append((b, name, K, N, rows, wb, q, sc))
                 pack_elems += N * K
-                if rank == 0 and b < args.verify_blocks:
-                    if orc is None:
-                        from oracle.binding import Oracle
-                        orc = Oracle()
-                    bits = wb.view(torch.int16).cpu().numpy().view(np.uint16)
-                    q_c, s_c = orc.quant_rows_packer(orc.bf16_to_f32(bits))
-                    q_g, s_g = q.cpu().numpy().tobytes(), sc.cpu().numpy().tobytes()
-                    if q_g != q_c.tobytes() or s_g != s_c.tobytes():
-                        raise SystemExit("packed bytes of %s block %d %s differ from the CPU packer" % (bname, b, name))
-                    for h, parts in ((sha_gpu, (q_g, s_g)), (sha_cpu, (q_c.tobytes(), s_c.tobytes()))):
-                        for part in parts:
-                            h.update(part)
-                    verified += 1
-                weights.append((K, N, rows, q, sc, s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), N, K)))
-                del wb
+        torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record(stream)
+        for (b, name, K, N, rows, wb, q, sc) in srcs:
+            s._ck(lib.sdq_quantize_rows(wb.data_ptr(), S.BF16, N, K, S.MODE_PACKER, q.data_ptr(), sc.data_ptr(), 0, sp))
+        e1.record(stream)
+        torch.cuda.synchronize()
+        pack_ms = e0.elapsed_time(e1)
+        for (b, name, K, N, rows, wb, q, sc) in srcs:
+            if rank == 0 and b < args.verify_blocks:
+                if orc is None:
+                    from oracle.binding import Oracle
+                    orc = Oracle()
+                bits = wb.view(torch.int16).cpu().numpy().view(np.uint16)
+                q_c, s_c = orc.quant_rows_packer(orc.bf16_to_f32(bits))
+                q_g, s_g = q.cpu().numpy().tobytes(), sc.cpu().numpy().tobytes()
+                if q_g != q_c.tobytes() or s_g != s_c.tobytes():
+                    raise SystemExit("packed bytes of %s block %d %s differ from the CPU packer" % (bname, b, name))
+                for h, parts in ((sha_gpu, (q_g, s_g)), (sha_cpu, (q_c.tobytes(), s_c.tobytes()))):
+                    for part in parts:
+                        h.update(part)
+                verified += 1
+            weights.append((K, N, rows, q, sc, s.weight_wrap_device(q.data_ptr(), sc.data_ptr(), N, K)))
+        del srcs, wb
+        torch.cuda.empty_cache()
         # optional: write the first blocks as a .sdcpp file and time open + validate + upload
         if rank == 0 and args.pack_file_blocks > 0 and load is None:
             import struct

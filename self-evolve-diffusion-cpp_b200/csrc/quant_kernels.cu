@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 
 #include <climits>
+#include <cstdlib>
 
 #include "sdq_internal.h"
 
@@ -581,7 +582,12 @@ cudaError_t launch_act_quant(const float* A, int64_t M, int64_t K, int8_t* aq, f
                    ((reinterpret_cast<uintptr_t>(aq) & 3) == 0);
   const int64_t per_thread = (K / 4 + kThreads - 1) / kThreads;  // float4 per thread
   count_launch();
-  if (vec && K <= 32 * 4 * 24 && M >= (int64_t)sm_count * 16) {
+  // One warp per row pays off once there are many rows per SM (measured at K = 3072: 98 vs 109 us
+  // at 27280 rows, equal at 13824, 17.5 vs 15.1 us at 3584 rows, where one block per row spreads
+  // the few rows better); SDQ_ACTQ_WARP_MIN_ROWS overrides the threshold for measurements.
+  const char* wmin_env = getenv("SDQ_ACTQ_WARP_MIN_ROWS");
+  const int64_t warp_min_rows = wmin_env ? atoll(wmin_env) : (int64_t)sm_count * 80;
+  if (vec && K <= 32 * 4 * 24 && M >= warp_min_rows) {
     int64_t wblocks = (M + kThreads / 32 - 1) / (kThreads / 32);
     if (wblocks > (int64_t)sm_count * 4) wblocks = (int64_t)sm_count * 4;
     if (K <= 32 * 4 * 8)
