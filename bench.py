@@ -526,7 +526,8 @@ def run_b200(args):
     value = ffn_ops(M_total) / (ms_step * 1e-3) / 1e12
     hbm = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
     roofline = {"bound": "tensor", "kernel": "qgemm_tc2_kernel " + dom, "achieved": achieved, "peak": peak,
-                "unit": "TOPS", "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
+                "unit": "TFLOP/s", "unit_note": "tera int8 operations per second (2*M*N*K), i.e. TOPS",
+                "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
                 "peak_kind": peak_kind,
                 "step_frac": value / world / peak,
                 "step_frac_what": "the whole FFN pair per GPU (both quantize launches included) over the same peak",
