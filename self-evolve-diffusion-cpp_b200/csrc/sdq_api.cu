@@ -163,7 +163,7 @@ int run_gemm(const Weight& w, const int8_t* aq, const float* a_scale, int64_t M,
   if (!(flags & SDQ_FORCE_SIMT) && qgemm_tc_supported(g)) {
     std::string why;
     if (qgemm_tc2_wanted(g, g_ctx->sm_count)) {
-      if (const int tail = qgemm_tc2_tail_tiles(g, g_ctx->sm_count)) {
+      if (qgemm_tc2_tail_tiles(g, g_ctx->sm_count) > 0) {
         // scratch for the partial sums of the shared last wave: zero when first made (and again
         // after a kernel gave up mid-way); every launch that uses it leaves it zero
         Workspace* ws;
@@ -181,7 +181,6 @@ int run_gemm(const Weight& w, const int8_t* aq, const float* a_scale, int64_t M,
         }
         g.tail_acc = ws->tail_acc;
         g.tail_cap_tiles = (int)cap_tiles;
-        (void)tail;
       }
     }
     const int splits = qgemm_tc_plan_splits(g, g_ctx->sm_count);
