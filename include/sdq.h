@@ -104,6 +104,18 @@ SDQ_API int64_t sdq_launch_count(void);
  * is what the GEMM kernels' tensor rooflines are compared with.  Synchronous. */
 SDQ_API int sdq_int8_mma_probe(int iters, double* seconds, double* tera_ops_per_s);
 
+/* Self-test of the time-out path (no counterpart in the reference).  Launches, on `stream`, one
+ * warp that waits -- through the bounded wait every tensor-core kernel of the library uses -- on
+ * a barrier nothing ever arrives on, with a limit of `limit_ms` milliseconds (1..1000) instead of
+ * the kernels' 2 s.  The wait runs out, the kernel records SDQ_SELFTEST_WAIT_CODE in the
+ * library's status word, raises its abort flag and returns; *outcome_dev (device memory)
+ * receives bit 0 = "the wait was satisfied" (never), bit 1 = "the abort flag was seen raised".
+ * Asynchronous: the next sdq_stream_sync (or SDQ_SYNC call) returns SDQ_ERR_DEVICE_TIMEOUT
+ * naming the code, exactly once; the context stays usable and later calls are unaffected.
+ * Nothing hangs or faults: the kernel ends by itself a few milliseconds after the limit. */
+#define SDQ_SELFTEST_WAIT_CODE 0x7e01
+SDQ_API int sdq_selftest_wait_expiry(int limit_ms, int* outcome_dev, void* stream);
+
 /* Device / pinned-host memory and copies for callers that do not link the CUDA
  * runtime themselves.  `stream` is a cudaStream_t (NULL = default stream). */
 SDQ_API int sdq_malloc(void** dptr, size_t bytes);

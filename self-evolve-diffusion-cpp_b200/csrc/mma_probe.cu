@@ -82,7 +82,36 @@ __global__ void __launch_bounds__(kProbeThreads, 1) i8_mma_probe_kernel(int iter
   }
 }
 
+// Self-test of the time-out path: one warp waits on a barrier that nothing ever arrives on,
+// through the same bounded wait the GEMM kernels use, with a limit of `limit_ns`.  The wait runs
+// out, the status word receives the code, the abort flag is raised and the kernel returns: what
+// a GEMM does when one of its waits gives up, without anything being stuck.
+__global__ void __launch_bounds__(32, 1) wait_expiry_kernel(uint64_t limit_ns, int code, int* status,
+                                                            int* outcome) {
+  __shared__ __align__(8) uint64_t bar_mem;
+  __shared__ int abort_word;
+  const uint32_t bar = smem_u32(&bar_mem);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait(bar, 0, &abort_word, status, code, limit_ns);
+  __syncwarp();
+  // every lane sees the flag the waiting lane raised, as the other roles of a GEMM CTA would
+  if (threadIdx.x == 0) *outcome = (ok ? 1 : 0) | (*(volatile int*)&abort_word ? 2 : 0);
+}
+
 }  // namespace
+
+int wait_expiry_selftest(int limit_ms, int code, int* status_dev, int* outcome_dev, cudaStream_t s) {
+  count_launch();
+  wait_expiry_kernel<<<1, 32, 0, s>>>((uint64_t)limit_ms * 1000000ull, code, status_dev, outcome_dev);
+  SDQ_CUDA(cudaGetLastError());
+  return SDQ_OK;
+}
 
 // Runs the probe on every SM; *seconds receives the device time of the launch.
 int int8_mma_probe(int sm_count, int iters, int* status_dev, double* seconds, double* ops) {

@@ -337,6 +337,14 @@ int sdq_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream) {
   if (bytes) SDQ_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
   return SDQ_OK;
 }
+int sdq_selftest_wait_expiry(int limit_ms, int* outcome_dev, void* stream) {
+  if (int rc = need_ctx()) return rc;
+  if (limit_ms < 1 || limit_ms > 1000)
+    return fail(SDQ_ERR_INVALID, "sdq_selftest_wait_expiry: limit_ms must be in 1..1000");
+  if (!outcome_dev) return fail(SDQ_ERR_INVALID, "sdq_selftest_wait_expiry: null outcome pointer");
+  return wait_expiry_selftest(limit_ms, SDQ_SELFTEST_WAIT_CODE, g_ctx->status, outcome_dev, (cudaStream_t)stream);
+}
+
 int sdq_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream) {
   if (int rc = need_ctx()) return rc;
   if (bytes) SDQ_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));

@@ -129,5 +129,6 @@ cudaError_t launch_sdpa(const float* q, const float* k, const float* v, int64_t 
 
 // MMA-issue-bound int8 rate of the device (mma_probe.cu).
 int int8_mma_probe(int sm_count, int iters, int* status_dev, double* seconds, double* ops);
+int wait_expiry_selftest(int limit_ms, int code, int* status_dev, int* outcome_dev, cudaStream_t s);
 
 }  // namespace sdq

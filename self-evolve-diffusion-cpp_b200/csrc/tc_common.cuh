@@ -52,7 +52,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 // Bounded wait.  Returns false when it gave up (or another role already did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -61,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         __threadfence_system();

@@ -21,6 +21,7 @@ SRC_HOST, DST_HOST = 0x1, 0x2
 PACK_UPLOAD = 0x1
 DT_F32, DT_I8 = 0, 2
 ERR_DEVICE_TIMEOUT = 6
+SELFTEST_WAIT_CODE = 0x7e01
 STATIC_MAX_ROWS, STATIC_MAX_AQ_BYTES = 32768, 33554432
 
 
@@ -58,6 +59,7 @@ _SIGS = {
     "sdq_last_error": (C.c_char_p, []),
     "sdq_launch_count": (C.c_int64, []),
     "sdq_int8_mma_probe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "sdq_selftest_wait_expiry": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p]),
     "sdq_malloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "sdq_free": (C.c_int, [C.c_void_p]),
     "sdq_malloc_host": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
@@ -240,6 +242,13 @@ class Sdq:
         sec, tops = C.c_double(), C.c_double()
         self._ck(self.lib.sdq_int8_mma_probe(iters, C.byref(sec), C.byref(tops)))
         return sec.value, tops.value
+
+    def selftest_wait_expiry(self, limit_ms, stream=None):
+        """Launches the warp that waits on a barrier nothing arrives on; returns the device word
+        that receives its outcome.  The next sync raises SdqError(ERR_DEVICE_TIMEOUT)."""
+        out = self.to_device(np.full(1, -1, np.int32))
+        self._ck(self.lib.sdq_selftest_wait_expiry(limit_ms, out.ptr, stream))
+        return out
 
     # ---- memory ----
     def alloc(self, nbytes):
