@@ -531,6 +531,8 @@ def run_b200(args):
                 "peak_kind": peak_kind,
                 "step_frac": value / world / peak,
                 "step_frac_what": "the whole FFN pair per GPU (both quantize launches included) over the same peak",
+                "frac_of_2x_bf16_sustained": achieved / (2.0 * float(pk.get("bf16_tflops_sustained",
+                                                                            FALLBACK_PEAKS["bf16_tflops_sustained"]))),
                 "frac_of_nominal_int8_4500": achieved / INT8_NOMINAL_TOPS,
                 "step_frac_of_nominal_int8_4500": value / world / INT8_NOMINAL_TOPS,
                 "algorithmic_bytes": gemm_bytes(M, D_MODEL, D_FFN),
